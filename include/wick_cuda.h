@@ -1,0 +1,191 @@
+/*
+ * wick_cuda.h -- C ABI of libwick_cuda, a CUDA (sm_100a) backend for the LFM2
+ * decode / prefill hot path of the wick inference engine.
+ *
+ * The entry points are what a `wick/src/backend/cuda.rs` + `wick/src/model/cuda_lfm2.rs`
+ * pair would bind with `extern "C"`: one opaque model handle that plays the role
+ * MetalLfm2Model plays for `--device metal` (wick/src/model/metal_lfm2.rs:170-277),
+ * i.e. weights, KV cache, conv state and scratch are resident on the GPU and ONE
+ * sequence lives in the model.  Each function cites the wick interface it stands
+ * in for (path:line inside the wick repository).
+ *
+ * Conventions
+ *  - every function returns a status code (0 = ok, negative = error) and never
+ *    throws or aborts; wick_cuda_last_error() returns the calling thread's last
+ *    message.  wick's trait methods are infallible (they assert), so the Rust side
+ *    panics after a non-zero status; load failures map to anyhow errors.
+ *  - pointers named *_host are host memory, *_dev are device memory on the
+ *    model's / current device.  The caller owns every buffer it passes.
+ *  - calls on one handle must not overlap (the Rust side holds `infer_lock`,
+ *    metal_lfm2.rs:254-267); different handles may be used from different threads.
+ *  - functions that return results in host memory block until they are there.
+ */
+#ifndef WICK_CUDA_H
+#define WICK_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define WICK_CUDA_OK 0
+#define WICK_CUDA_ERR_BAD_ARG (-1)
+#define WICK_CUDA_ERR_CUDA (-2)
+#define WICK_CUDA_ERR_OOM (-3)
+#define WICK_CUDA_ERR_UNSUPPORTED_DTYPE (-4)
+#define WICK_CUDA_ERR_CONTEXT_FULL (-5)
+#define WICK_CUDA_ERR_TIMEOUT (-6)
+#define WICK_CUDA_ERR_BAD_GGUF (-7)
+
+/* GGML tensor type ids of the two supported weight formats (wick/src/gguf.rs:38, :42). */
+#define WICK_DTYPE_Q4_0 2
+#define WICK_DTYPE_Q8_0 8
+
+typedef struct wick_cuda_model wick_cuda_model;
+typedef struct wick_cuda_weight wick_cuda_weight;
+
+/* Mirror of wick::model::ModelConfig (wick/src/model/mod.rs:28-46). */
+typedef struct wick_cuda_config {
+    uint32_t n_layers;
+    uint32_t hidden_size;
+    uint32_t intermediate_size;
+    uint32_t n_heads;
+    uint32_t n_kv_heads;       /* max over layers */
+    uint32_t vocab_size;
+    uint32_t max_seq_len;      /* min(context_size, gguf context_length), lfm2.rs:120-127 */
+    uint32_t conv_kernel_size;
+    float rope_theta;
+    float rms_norm_eps;
+} wick_cuda_config;
+
+/* ---- library ---------------------------------------------------------- */
+
+/* Number of CUDA devices; backs `--device cuda[:N]` (wick/src/engine.rs:65-89). */
+int32_t wick_cuda_device_count(int32_t* count);
+/* Last error message of the calling thread (valid until its next failing call). */
+const char* wick_cuda_last_error(void);
+
+/* ---- model lifetime: load_model_metal / MetalLfm2Model::from_gguf
+ *      (wick/src/model/mod.rs:386-403, metal_lfm2.rs:280-610) --------------- */
+
+/* Parses a GGUF v3 image (the bytes of GgufFile::mmap_data(), gguf.rs:662), uploads and
+ * re-lays-out the weights, allocates KV cache / conv state / scratch for
+ * min(context_size, lfm2.context_length) positions.  The image may be freed on return. */
+int32_t wick_cuda_model_create(const uint8_t* gguf_host, size_t gguf_len, uint32_t context_size,
+                               int32_t device, wick_cuda_model** out);
+/* Same, reading the file itself (GgufFile::open, gguf.rs:336-360). */
+int32_t wick_cuda_model_create_from_file(const char* path, uint32_t context_size, int32_t device,
+                                         wick_cuda_model** out);
+/* Drop. NULL is allowed. */
+void wick_cuda_model_destroy(wick_cuda_model* m);
+
+/* Model::config (model/mod.rs:143). */
+int32_t wick_cuda_model_config(const wick_cuda_model* m, wick_cuda_config* out);
+/* ModelConfig::block_types / kv_heads_per_layer: out[i] = 0 for a gated-conv layer, else
+ * that attention layer's KV head count.  `n` must equal n_layers. */
+int32_t wick_cuda_model_kv_heads_per_layer(const wick_cuda_model* m, uint32_t* out, uint32_t n);
+/* Model::gpu_memory_bytes (model/mod.rs:280). */
+int32_t wick_cuda_gpu_memory_bytes(const wick_cuda_model* m, uint64_t* out);
+
+/* ---- the Model trait (model/mod.rs:72-323) ---------------------------- */
+
+/* Model::forward (mod.rs:74; Metal precedent metal_lfm2.rs:2078-2148): one token in, logits
+ * [vocab_size] out.  As in the Metal backend the position is the model's own counter; `pos`
+ * is checked against it and a mismatch is WICK_CUDA_ERR_BAD_ARG.  CONTEXT_FULL once
+ * seq_len == max_seq_len. */
+int32_t wick_cuda_forward(wick_cuda_model* m, uint32_t token, uint32_t pos, float* logits_host);
+/* Model::forward_greedy (mod.rs:274; metal_lfm2.rs:2151-2203): same step, argmax on the GPU
+ * with cpu_argmax's rule (sampler.rs:8-19: NaN = -inf, last of equal maxima), 4-byte readback. */
+int32_t wick_cuda_forward_greedy(wick_cuda_model* m, uint32_t token, uint32_t pos, uint32_t* next_token);
+/* Model::forward_prefill (mod.rs:79; lfm2.rs:2351, metal_lfm2.rs:2350): n >= 1 tokens at
+ * positions start_pos.., logits of the LAST token out.  start_pos == 0 starts a new sequence
+ * (resets seq_len, zeroes conv state); otherwise start_pos must equal seq_len.  Like the CPU
+ * path, a call with n >= 256 uses the tiled online-softmax attention and a shorter one the
+ * per-token attention (lfm2.rs:1646-1647).  Callers chunk long prompts themselves
+ * (forward_prefill_chunked, mod.rs:111-140). */
+int32_t wick_cuda_forward_prefill(wick_cuda_model* m, const uint32_t* tokens_host, uint32_t n,
+                                  uint32_t start_pos, float* logits_host);
+/* Greedy decode loop of Session::generate (wick/src/session.rs:1186-1257) kept on the GPU:
+ * feeds `first_token`, then each step's argmax, for n_steps steps; out_tokens_host[i] is the
+ * token chosen by step i.  Equivalent to n_steps wick_cuda_forward_greedy calls without the
+ * per-token host round trip. */
+int32_t wick_cuda_generate_greedy(wick_cuda_model* m, uint32_t first_token, uint32_t n_steps,
+                                  uint32_t* out_tokens_host);
+/* New sequence without a prefill (InferenceState::from_config, kv_cache.rs:183). */
+int32_t wick_cuda_reset(wick_cuda_model* m);
+/* InferenceState::seq_len (kv_cache.rs:115-130). */
+int32_t wick_cuda_seq_len(const wick_cuda_model* m, uint32_t* out);
+
+/* Model::snapshot_state / restore_state (mod.rs:301-313; metal_lfm2.rs:2535-2650): KV rows
+ * [0, seq_len) of every attention layer, conv rolling buffers and seq_len as one byte image. */
+int32_t wick_cuda_snapshot_size(const wick_cuda_model* m, uint64_t* bytes);
+int32_t wick_cuda_snapshot(wick_cuda_model* m, uint8_t* out_host, uint64_t capacity);
+int32_t wick_cuda_restore(wick_cuda_model* m, const uint8_t* snap_host, uint64_t len);
+
+/* Debug / parity taps: f32 K and V rows [0, seq_len) x kv_dim of an attention layer
+ * (LayerState::Attention, kv_cache.rs:62-70) or the [d_conv][hidden] rolling buffer of a conv
+ * layer (LayerState::Conv, kv_cache.rs:72-74). */
+int32_t wick_cuda_read_kv(wick_cuda_model* m, uint32_t layer, float* k_host, float* v_host);
+int32_t wick_cuda_read_conv_state(wick_cuda_model* m, uint32_t layer, float* out_host);
+
+/* ---- operators on device buffers ------------------------------------------
+ * The free functions of wick/src/backend/{simd,cpu}.rs that the model is built
+ * from, exposed so each kernel can be checked on its own.  All pointers are device
+ * pointers; `stream` is a cudaStream_t (NULL = default stream); calls are
+ * asynchronous on that stream. */
+
+/* Uploads GGUF-layout quantised rows [m][k/32 blocks] (host memory) into the library's device
+ * layout (quants plane + f16 scale plane, same byte count).  WeightRef, lfm2.rs:19-25. */
+int32_t wick_cuda_weight_create(int32_t dtype, const uint8_t* raw_host, uint32_t m, uint32_t k,
+                                wick_cuda_weight** out);
+void wick_cuda_weight_destroy(wick_cuda_weight* w);
+
+/* quantize_f32_to_q8_0_neon over n rows of k (simd.rs:255-323; quantize_columns lfm2.rs:571-592):
+ * scales [n][k/32] f32 (f16-rounded), quants [n][k] i8. */
+int32_t wick_cuda_quantize_q8_0(const float* x_dev, uint32_t n, uint32_t k, float* scales_dev,
+                                int8_t* quants_dev, void* stream);
+/* gemv_q4_0_q8_0_neon / gemv_q8_0_q8_0_neon (simd.rs:328-415, :440-524): y[m]. */
+int32_t wick_cuda_gemv_q8(const wick_cuda_weight* w, const float* xs_dev, const int8_t* xq_dev,
+                          float* y_dev, void* stream);
+/* gemm_q4_0_q8_0_neon / gemm_q8_0_q8_0_neon (simd.rs:696-925, :937-1019) over n pre-quantised
+ * columns; the result is token-major out[j*m + i] (the reference writes out[i*n + j]). */
+int32_t wick_cuda_gemm_q8(const wick_cuda_weight* w, const float* bs_dev, const int8_t* bq_dev,
+                          uint32_t n, float* out_dev, void* stream);
+/* int32 block dot sums S[i][b] = sum over the 32 elements of block b of row i (the vdotq_s32
+ * lanes of simd.rs:381-383 added up) against one quantised column. */
+int32_t wick_cuda_block_sums(const wick_cuda_weight* w, const int8_t* xq_dev, int32_t* s_dev, void* stream);
+/* cpu::rmsnorm over n rows of `dim` (cpu.rs:577-594), in place. */
+int32_t wick_cuda_rmsnorm(float* x_dev, const float* weight_dev, uint32_t n, uint32_t dim, float eps, void* stream);
+/* cpu::silu_mul_inplace (cpu.rs:668-673): gate = silu(gate) * up, `count` elements. */
+int32_t wick_cuda_silu_mul(float* gate_dev, const float* up_dev, uint64_t count, void* stream);
+/* ggml_expf (cpu.rs:602-642), element-wise. */
+int32_t wick_cuda_expf(const float* x_dev, float* y_dev, uint64_t count, void* stream);
+/* cpu::rope (cpu.rs:2113-2158) for one position; cos/sin are evaluated on the host with libm
+ * exactly as the reference does and uploaded by this call. */
+int32_t wick_cuda_rope(float* q_dev, float* k_dev, uint32_t pos, uint32_t n_heads, uint32_t n_kv_heads,
+                       uint32_t head_dim, float freq_base, void* stream);
+/* Single-query attention of forward_attn_block (lfm2.rs:980-1007): attn_scores, softmax_inplace,
+ * attn_values (cpu.rs:1320-1509, :715-731) for all heads over `seq` cached rows. */
+int32_t wick_cuda_attention_decode(const float* q_dev, const float* k_cache_dev, const float* v_cache_dev,
+                                   float* out_dev, uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim,
+                                   uint32_t seq, void* stream);
+/* Causal GQA prefill attention: query j of n attends rows [0, start_pos + j].  flash != 0 selects
+ * flash_attention_gqa_cpu (cpu.rs:1538-1850), else the per-token path (lfm2.rs:1857-1897).
+ * q / out are token-major [n][n_heads*head_dim]. */
+int32_t wick_cuda_attention_prefill(const float* q_dev, const float* k_cache_dev, const float* v_cache_dev,
+                                    float* out_dev, uint32_t n, uint32_t start_pos, uint32_t n_heads,
+                                    uint32_t n_kv_heads, uint32_t head_dim, int32_t flash, void* stream);
+/* The gated short-conv core of forward_conv_block (lfm2.rs:688-725) over n tokens: proj is
+ * token-major [n][3*hidden] (b, c, x thirds), state [d_conv][hidden] is read and updated,
+ * out [n][hidden] = c * conv(b * x). */
+int32_t wick_cuda_shortconv(const float* proj_dev, const float* conv_w_dev, float* state_dev, float* out_dev,
+                            uint32_t n, uint32_t hidden, uint32_t kernel_size, void* stream);
+/* cpu_argmax (sampler.rs:8-19) of `count` logits -> *out_dev. */
+int32_t wick_cuda_argmax(const float* logits_dev, uint32_t count, uint32_t* out_dev, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* WICK_CUDA_H */

@@ -1,0 +1,121 @@
+// Shared device helpers.  This library is compiled with --fmad=false: the CPU path
+// it must agree with bit for bit never contracts a*b+c, so every fused multiply-add
+// in these kernels is an explicit fmaf()/__fmaf_rn() that mirrors an explicit NEON
+// vfmaq_f32 in wick (wick/src/backend/cpu.rs:1440-1441, :1491, :1831).
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace wick {
+
+constexpr int QK = 32;         // elements per quantised block
+constexpr int DT_Q4_0 = 2;     // ggml type ids (wick/src/gguf.rs:38, :42)
+constexpr int DT_Q8_0 = 8;
+
+// A quantised matrix in the library's device layout: the 16 (Q4_0) or 32 (Q8_0)
+// quant bytes of every block in one plane, row-major [m][k/32], the f16 scales in
+// a second plane [m][k/32].  Same bytes as the GGUF blocks (wick/src/quant.rs:13-34),
+// but 16-byte aligned so they can be fetched with 128-bit loads / bulk copies.
+struct DevWeight {
+    const uint8_t* q = nullptr;
+    const __half* d = nullptr;
+    int m = 0, k = 0, dtype = 0;
+    __host__ __device__ int nb() const { return k / QK; }
+    __host__ __device__ int qrow_bytes() const { return dtype == DT_Q4_0 ? k / 2 : k; }
+    size_t q_bytes() const { return (size_t)m * qrow_bytes(); }
+    size_t d_bytes() const { return (size_t)m * nb() * 2; }
+};
+
+__device__ __forceinline__ int dp4a_ss(int a, int b, int c) { return __dp4a(a, b, c); }
+
+// ggml_expf, wick/src/backend/cpu.rs:602-642.  Plain f32 mul/add (the file is built
+// without FMA contraction).
+__device__ __forceinline__ float ggml_expf(float x) {
+    const float R = __uint_as_float(0x4B400000u);
+    const float LOG2E = __uint_as_float(0x3FB8AA3Bu);
+    const float LN2_HI = __uint_as_float(0x3F317200u);
+    const float LN2_LO = __uint_as_float(0x35BFBE8Eu);
+    const float C1 = __uint_as_float(0x3F7FFFF6u);
+    const float C2 = __uint_as_float(0x3EFFFEDBu);
+    const float C3 = __uint_as_float(0x3E2AAF33u);
+    const float C4 = __uint_as_float(0x3D2B9F17u);
+    const float C5 = __uint_as_float(0x3C072010u);
+    float z = __fadd_rn(R, __fmul_rn(x, LOG2E));
+    float n = __fsub_rn(z, R);
+    float b = __fsub_rn(__fsub_rn(x, __fmul_rn(n, LN2_HI)), __fmul_rn(n, LN2_LO));
+    uint32_t e = __float_as_uint(z) << 23;
+    float k = __uint_as_float(e + 0x3F800000u);
+    float u = __fmul_rn(b, b);
+    float t45 = __fadd_rn(C4, __fmul_rn(C5, b));
+    float t23 = __fadd_rn(__fadd_rn(C2, __fmul_rn(C3, b)), __fmul_rn(t45, u));
+    float j = __fadd_rn(__fmul_rn(C1, b), __fmul_rn(t23, u));
+    float abs_n = fabsf(n);
+    if (abs_n <= 126.0f) {
+        return __fadd_rn(k, __fmul_rn(j, k));
+    } else if (abs_n > 192.0f) {
+        return n > 0.0f ? __int_as_float(0x7F800000) : 0.0f;
+    } else {
+        uint32_t d = n <= 0.0f ? 0x82000000u : 0u;
+        float s1 = __uint_as_float(d + 0x7f000000u);
+        float s2 = __uint_as_float(e - d);
+        return __fmul_rn(__fadd_rn(s2, __fmul_rn(s2, j)), s1);
+    }
+}
+
+// silu_mul_inplace element, cpu.rs:668-673: g / (1 + expf(-g)) * u
+__device__ __forceinline__ float silu_mul_elem(float g, float u) {
+    float e = ggml_expf(-g);
+    return __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, e)), u);
+}
+
+// The Q8_0 activation quantiser for one 32-element block held one element per lane
+// (wick/src/backend/simd.rs:255-323).  Returns the quant; *scale is the f16-rounded d.
+__device__ __forceinline__ int8_t quantize_lane(float v, float* scale) {
+    float a = fabsf(v);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+    float d = __fdiv_rn(a, 127.0f);
+    float id = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+    *scale = __half2float(__float2half_rn(d));
+    return (int8_t)__float2int_rn(__fmul_rn(v, id));
+}
+
+// cpu_argmax ordering (wick/src/sampler.rs:8-19): total_cmp with NaN as -inf; packing the
+// index below the key makes "largest key, then largest index" a plain u64 max.
+__device__ __forceinline__ unsigned long long argmax_pack(float f, uint32_t idx) {
+    if (f != f) f = __int_as_float(0xFF800000);
+    int32_t b = __float_as_int(f);
+    b ^= (int32_t)(((uint32_t)(b >> 31)) >> 1);
+    uint32_t key = (uint32_t)b ^ 0x80000000u;
+    return ((unsigned long long)key << 32) | idx;
+}
+
+__device__ __forceinline__ double warp_sum_f64(double v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// Sum of squares of x[0..n) in f64 (cpu::rmsnorm, cpu.rs:583-586).  The reference adds
+// in element order; here each thread adds its strided share in order and the partials are
+// combined in a fixed tree, which can differ from the serial sum by a few f64 ulps (~1e-15
+// relative) -- far below the f32 rounding of the result it feeds.  All threads get the sum.
+__device__ __forceinline__ double block_sum_sq_f64(const float* x, int n, double* red /*>=32*/) {
+    double s = 0.0;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        double v = (double)x[i];
+        s += v * v;
+    }
+    s = warp_sum_f64(s);
+    int w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    if ((threadIdx.x & 31) == 0) red[w] = s;
+    __syncthreads();
+    double t = 0.0;
+    for (int i = 0; i < nw; i++) t += red[i];
+    __syncthreads();
+    return t;
+}
+
+}  // namespace wick

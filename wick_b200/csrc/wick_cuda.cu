@@ -1,0 +1,907 @@
+// Host side of libwick_cuda: GGUF -> device model, the decode / prefill drivers
+// and the C ABI of include/wick_cuda.h.  The structure follows the role
+// MetalLfm2Model plays in wick (wick/src/model/metal_lfm2.rs:170-277, :280-610):
+// one sequence lives in the model; weights, KV cache, conv state and scratch are
+// device resident; a decode step is one submission (here: one CUDA graph launch).
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <fstream>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "../../include/wick_cuda.h"
+#include "gguf.hpp"
+#include "kernels.cuh"
+
+using namespace wick;
+
+// ── errors ─────────────────────────────────────────────────────────────────
+static thread_local std::string g_last_error;
+
+static int32_t fail(int32_t code, const std::string& msg) {
+    g_last_error = msg;
+    return code;
+}
+#define CU_TRY(expr)                                                                              \
+    do {                                                                                          \
+        cudaError_t e__ = (expr);                                                                 \
+        if (e__ != cudaSuccess)                                                                   \
+            return fail(e__ == cudaErrorMemoryAllocation ? WICK_CUDA_ERR_OOM : WICK_CUDA_ERR_CUDA, \
+                        std::string(#expr) + ": " + cudaGetErrorString(e__));                     \
+    } while (0)
+#define W_TRY(expr)                  \
+    do {                             \
+        int32_t r__ = (expr);        \
+        if (r__ != WICK_CUDA_OK) return r__; \
+    } while (0)
+
+namespace {
+
+struct Layer {
+    bool is_attn = false;
+    int n_kv = 0;
+    float *attn_norm = nullptr, *ffn_norm = nullptr, *q_norm = nullptr, *k_norm = nullptr, *conv_w = nullptr;
+    DevWeight in_proj, out_proj, q, k, v, o, gate, up, down;
+    float *k_cache = nullptr, *v_cache = nullptr;  // [max_seq][kv_dim]
+    float* conv_state = nullptr;                   // [d_conv][hidden]
+};
+
+}  // namespace
+
+struct wick_cuda_weight {
+    DevWeight w;
+    int device = 0;
+};
+
+struct wick_cuda_model {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    wick_cuda_config cfg{};
+    int head_dim = 0;
+    std::vector<Layer> layers;
+    DevWeight embd;
+    float* output_norm = nullptr;
+    float *rope_cos = nullptr, *rope_sin = nullptr;
+    int max_chunk = 0;  // tokens of scratch
+    // scratch, token-major
+    float *hidden = nullptr, *block_out = nullptr, *ffn_out = nullptr, *proj = nullptr, *qbuf = nullptr, *kbuf = nullptr,
+          *vbuf = nullptr, *attn_out = nullptr, *gate = nullptr, *up = nullptr, *logits = nullptr;
+    float* q8s = nullptr;
+    int8_t* q8q = nullptr;
+    uint32_t* tokens_dev = nullptr;
+    DecodeCtl* ctl = nullptr;
+    uint32_t* argmax_tok = nullptr;
+    uint32_t* ring = nullptr;
+    int ring_len = 0;
+    // pinned host staging
+    uint32_t* h_u32 = nullptr;   // [ring_len] tokens in / out
+    float* h_logits = nullptr;   // [vocab]
+    cudaGraphExec_t g_logits = nullptr, g_greedy = nullptr;
+    uint32_t seq_len = 0;
+    uint64_t bytes = 0;
+    std::vector<void*> allocs;
+
+    ~wick_cuda_model() {
+        cudaSetDevice(device);
+        if (stream) cudaStreamSynchronize(stream);
+        if (g_logits) cudaGraphExecDestroy(g_logits);
+        if (g_greedy) cudaGraphExecDestroy(g_greedy);
+        for (void* p : allocs) cudaFree(p);
+        if (h_u32) cudaFreeHost(h_u32);
+        if (h_logits) cudaFreeHost(h_logits);
+        if (stream) cudaStreamDestroy(stream);
+    }
+};
+
+namespace {
+
+template <class T>
+int32_t dev_alloc(wick_cuda_model* m, T** out, size_t count) {
+    void* p = nullptr;
+    size_t bytes = std::max<size_t>(count * sizeof(T), 256);
+    CU_TRY(cudaMalloc(&p, bytes));
+    m->allocs.push_back(p);
+    m->bytes += bytes;
+    *out = (T*)p;
+    return WICK_CUDA_OK;
+}
+
+int32_t upload_f32(wick_cuda_model* m, const GgufImage& g, const std::string& name, size_t expect, float** out) {
+    const GgufTensor* t = g.tensor(name);
+    if (!t) return fail(WICK_CUDA_ERR_BAD_GGUF, "tensor not found: " + name);
+    uint64_t ne = 1;
+    for (uint64_t d : t->dims) ne *= d;
+    if (ne != expect) return fail(WICK_CUDA_ERR_BAD_GGUF, "tensor " + name + ": unexpected element count");
+    std::vector<float> host(ne);
+    if (t->type == 0) {
+        memcpy(host.data(), g.data() + t->offset, ne * 4);
+    } else if (t->type == 1) {
+        const __half* h = (const __half*)(g.data() + t->offset);
+        for (uint64_t i = 0; i < ne; i++) host[i] = __half2float(h[i]);
+    } else {
+        return fail(WICK_CUDA_ERR_UNSUPPORTED_DTYPE, "tensor " + name + ": expected F32 or F16");
+    }
+    W_TRY(dev_alloc(m, out, ne));
+    CU_TRY(cudaMemcpy(*out, host.data(), ne * 4, cudaMemcpyHostToDevice));
+    return WICK_CUDA_OK;
+}
+
+// Uploads GGUF block rows and re-lays them out into planes (see DevWeight).
+int32_t upload_weight_raw(int dtype, const uint8_t* raw_host, int mrows, int k, uint8_t* staging, cudaStream_t st,
+                          uint8_t* q_dev, __half* d_dev) {
+    size_t nblk = (size_t)mrows * (k / QK);
+    size_t raw_bytes = nblk * (dtype == DT_Q4_0 ? 18 : 34);
+    CU_TRY(cudaMemcpyAsync(staging, raw_host, raw_bytes, cudaMemcpyHostToDevice, st));
+    launch_repack(st, dtype, staging, q_dev, d_dev, nblk);
+    CU_TRY(cudaGetLastError());
+    CU_TRY(cudaStreamSynchronize(st));
+    return WICK_CUDA_OK;
+}
+
+int32_t upload_weight(wick_cuda_model* m, const GgufImage& g, const std::string& name, int expect_m, int expect_k,
+                      uint8_t* staging, DevWeight* out) {
+    const GgufTensor* t = g.tensor(name);
+    if (!t) return fail(WICK_CUDA_ERR_BAD_GGUF, "tensor not found: " + name);
+    if (t->type != DT_Q4_0 && t->type != DT_Q8_0)
+        return fail(WICK_CUDA_ERR_UNSUPPORTED_DTYPE,
+                    "tensor " + name + ": ggml type " + std::to_string(t->type) + " (only Q4_0 and Q8_0 are supported)");
+    // GGUF shape [inner, outer] -> rows of `inner` elements (lfm2.rs:323-329)
+    int k = t->dims.size() > 0 ? (int)t->dims[0] : 1;
+    int rows = t->dims.size() > 1 ? (int)t->dims[1] : 1;
+    if (rows != expect_m || k != expect_k || k % QK)
+        return fail(WICK_CUDA_ERR_BAD_GGUF, "tensor " + name + ": shape [" + std::to_string(k) + "," + std::to_string(rows) +
+                                                "] does not match the model config");
+    DevWeight w;
+    w.m = rows;
+    w.k = k;
+    w.dtype = (int)t->type;
+    uint8_t* q = nullptr;
+    __half* d = nullptr;
+    W_TRY(dev_alloc(m, &q, w.q_bytes()));
+    W_TRY(dev_alloc(m, &d, w.d_bytes() / 2));
+    W_TRY(upload_weight_raw(w.dtype, g.data() + t->offset, rows, k, staging, m->stream, q, d));
+    w.q = q;
+    w.d = d;
+    *out = w;
+    return WICK_CUDA_OK;
+}
+
+// cos / sin of every (position, pair) evaluated with the host libm in the reference's order
+// (cpu.rs:2145-2158): theta starts at pos as f32 and is multiplied by powf(base, -2/hd).
+void fill_rope_table(int n_pos, int hd, float base, std::vector<float>& c, std::vector<float>& s) {
+    int half = hd / 2;
+    c.resize((size_t)n_pos * half);
+    s.resize((size_t)n_pos * half);
+    float theta_scale = powf(base, -2.0f / (float)hd);
+    for (int p = 0; p < n_pos; p++) {
+        float theta = (float)p;
+        for (int i = 0; i < half; i++) {
+            c[(size_t)p * half + i] = cosf(theta);
+            s[(size_t)p * half + i] = sinf(theta);
+            theta *= theta_scale;
+        }
+    }
+}
+
+size_t naive_attn_smem(const wick_cuda_model* m) { return (size_t)(m->head_dim + m->cfg.max_seq_len) * sizeof(float); }
+
+// One decode step on the stream; token and position come from m->ctl (run_layers,
+// lfm2.rs:1020-1124, then the tied-embedding logits GEMV, lfm2.rs:2268-2288).
+void enqueue_decode(wick_cuda_model* m, bool greedy) {
+    cudaStream_t st = m->stream;
+    const int hs = m->cfg.hidden_size, is = m->cfg.intermediate_size, hd = m->head_dim;
+    launch_embed(st, m->embd, nullptr, m->ctl, m->hidden, 1);
+    const float* pending = nullptr;  // block output not yet added to the residual stream
+    for (size_t li = 0; li < m->layers.size(); li++) {
+        Layer& L = m->layers[li];
+        launch_add_rmsnorm_quant(st, m->hidden, pending, L.attn_norm, m->cfg.rms_norm_eps, 1, hs, m->q8s, m->q8q, nullptr);
+        if (!L.is_attn) {
+            GemvJob j{};
+            j.count = 1; j.w[0] = L.in_proj; j.y[0] = m->proj;
+            launch_gemv(st, j, m->q8s, m->q8q);
+            launch_shortconv(st, m->proj, L.conv_w, L.conv_state, 1, hs, m->cfg.conv_kernel_size, nullptr, m->q8s, m->q8q);
+            GemvJob o{};
+            o.count = 1; o.w[0] = L.out_proj; o.y[0] = m->block_out;
+            launch_gemv(st, o, m->q8s, m->q8q);
+        } else {
+            GemvJob j{};
+            j.count = 3;
+            j.w[0] = L.q; j.y[0] = m->qbuf;
+            j.w[1] = L.k; j.y[1] = m->kbuf;
+            j.w[2] = L.v; j.y[2] = m->vbuf;
+            launch_gemv(st, j, m->q8s, m->q8q);
+            launch_qknorm_rope_kv(st, m->qbuf, m->kbuf, m->vbuf, L.q_norm, L.k_norm, m->cfg.rms_norm_eps, m->rope_cos,
+                                  m->rope_sin, L.k_cache, L.v_cache, 1, -1, m->ctl, m->cfg.n_heads, L.n_kv, hd);
+            launch_attention_naive(st, m->qbuf, L.k_cache, L.v_cache, m->attn_out, 1, -1, m->ctl, m->cfg.n_heads, L.n_kv, hd,
+                                   m->cfg.max_seq_len);
+            launch_quant_rows(st, m->attn_out, 1, hs, m->q8s, m->q8q);
+            GemvJob o{};
+            o.count = 1; o.w[0] = L.o; o.y[0] = m->block_out;
+            launch_gemv(st, o, m->q8s, m->q8q);
+        }
+        launch_add_rmsnorm_quant(st, m->hidden, m->block_out, L.ffn_norm, m->cfg.rms_norm_eps, 1, hs, m->q8s, m->q8q, nullptr);
+        GemvJob gu{};
+        gu.count = 2;
+        gu.w[0] = L.gate; gu.y[0] = m->gate;
+        gu.w[1] = L.up; gu.y[1] = m->up;
+        launch_gemv(st, gu, m->q8s, m->q8q);
+        launch_silu_mul_quant(st, m->gate, m->up, 1, is, m->q8s, m->q8q, nullptr);
+        GemvJob dn{};
+        dn.count = 1; dn.w[0] = L.down; dn.y[0] = m->ffn_out;
+        launch_gemv(st, dn, m->q8s, m->q8q);
+        pending = m->ffn_out;
+    }
+    launch_add_rmsnorm_quant(st, m->hidden, pending, m->output_norm, m->cfg.rms_norm_eps, 1, hs, m->q8s, m->q8q, nullptr);
+    GemvJob lg{};
+    lg.count = 1; lg.w[0] = m->embd; lg.y[0] = m->logits;
+    launch_gemv(st, lg, m->q8s, m->q8q);
+    if (greedy) {
+        launch_argmax(st, m->logits, m->cfg.vocab_size, &m->ctl->argmax, m->argmax_tok);
+        launch_decode_advance(st, m->ctl, m->argmax_tok, m->ring, m->ring_len);
+    } else {
+        launch_decode_advance(st, m->ctl, &m->ctl->token, nullptr, 0);  // keeps the token, pos += 1
+    }
+}
+
+int32_t capture_graph(wick_cuda_model* m, bool greedy, cudaGraphExec_t* out) {
+    cudaGraph_t graph = nullptr;
+    CU_TRY(cudaStreamBeginCapture(m->stream, cudaStreamCaptureModeThreadLocal));
+    enqueue_decode(m, greedy);
+    cudaError_t e = cudaStreamEndCapture(m->stream, &graph);
+    if (e != cudaSuccess) return fail(WICK_CUDA_ERR_CUDA, std::string("graph capture: ") + cudaGetErrorString(e));
+    e = cudaGraphInstantiate(out, graph, 0);
+    cudaGraphDestroy(graph);
+    if (e != cudaSuccess) return fail(WICK_CUDA_ERR_CUDA, std::string("graph instantiate: ") + cudaGetErrorString(e));
+    return WICK_CUDA_OK;
+}
+
+// One internal prefill chunk of n <= max_chunk tokens already in m->tokens_dev
+// (prefill_layers_and_logits, lfm2.rs:1139-2213, aarch64 non-BLAS branch).
+void enqueue_prefill_chunk(wick_cuda_model* m, int n, int start_pos, bool flash, bool want_logits) {
+    cudaStream_t st = m->stream;
+    const int hs = m->cfg.hidden_size, is = m->cfg.intermediate_size, hd = m->head_dim;
+    const float eps = m->cfg.rms_norm_eps;
+    launch_embed(st, m->embd, m->tokens_dev, nullptr, m->hidden, n);
+    const float* pending = nullptr;
+    for (size_t li = 0; li < m->layers.size(); li++) {
+        Layer& L = m->layers[li];
+        launch_add_rmsnorm_quant(st, m->hidden, pending, L.attn_norm, eps, n, hs, m->q8s, m->q8q, nullptr);
+        if (!L.is_attn) {
+            launch_gemm(st, L.in_proj, m->q8s, m->q8q, n, m->proj);
+            launch_shortconv(st, m->proj, L.conv_w, L.conv_state, n, hs, m->cfg.conv_kernel_size, nullptr, m->q8s, m->q8q);
+            launch_gemm(st, L.out_proj, m->q8s, m->q8q, n, m->block_out);
+        } else {
+            launch_gemm(st, L.q, m->q8s, m->q8q, n, m->qbuf);
+            launch_gemm(st, L.k, m->q8s, m->q8q, n, m->kbuf);
+            launch_gemm(st, L.v, m->q8s, m->q8q, n, m->vbuf);
+            launch_qknorm_rope_kv(st, m->qbuf, m->kbuf, m->vbuf, L.q_norm, L.k_norm, eps, m->rope_cos, m->rope_sin, L.k_cache,
+                                  L.v_cache, n, start_pos, nullptr, m->cfg.n_heads, L.n_kv, hd);
+            if (flash)
+                launch_attention_flash(st, m->qbuf, L.k_cache, L.v_cache, m->attn_out, n, start_pos, m->cfg.n_heads, L.n_kv, hd);
+            else
+                launch_attention_naive(st, m->qbuf, L.k_cache, L.v_cache, m->attn_out, n, start_pos, nullptr, m->cfg.n_heads,
+                                       L.n_kv, hd, m->cfg.max_seq_len);
+            launch_quant_rows(st, m->attn_out, n, hs, m->q8s, m->q8q);
+            launch_gemm(st, L.o, m->q8s, m->q8q, n, m->block_out);
+        }
+        launch_add_rmsnorm_quant(st, m->hidden, m->block_out, L.ffn_norm, eps, n, hs, m->q8s, m->q8q, nullptr);
+        launch_gemm(st, L.gate, m->q8s, m->q8q, n, m->gate);
+        launch_gemm(st, L.up, m->q8s, m->q8q, n, m->up);
+        launch_silu_mul_quant(st, m->gate, m->up, n, is, m->q8s, m->q8q, nullptr);
+        launch_gemm(st, L.down, m->q8s, m->q8q, n, m->ffn_out);
+        pending = m->ffn_out;
+    }
+    if (want_logits) {
+        // last token only (lfm2.rs:2190-2212)
+        size_t last = (size_t)(n - 1) * hs;
+        launch_add_rmsnorm_quant(st, m->hidden + last, pending + last, m->output_norm, eps, 1, hs, m->q8s, m->q8q, nullptr);
+        GemvJob lg{};
+        lg.count = 1; lg.w[0] = m->embd; lg.y[0] = m->logits;
+        launch_gemv(st, lg, m->q8s, m->q8q);
+    }
+}
+
+int32_t reset_sequence(wick_cuda_model* m) {
+    const int hs = m->cfg.hidden_size, dc = (int)m->cfg.conv_kernel_size - 1;
+    for (Layer& L : m->layers)
+        if (!L.is_attn && dc > 0) CU_TRY(cudaMemsetAsync(L.conv_state, 0, (size_t)dc * hs * sizeof(float), m->stream));
+    DecodeCtl z{};
+    // pinned staging keeps the copy asynchronous and ordered on the stream
+    memcpy(m->h_u32, &z, sizeof(z));
+    CU_TRY(cudaMemcpyAsync(m->ctl, m->h_u32, sizeof(z), cudaMemcpyHostToDevice, m->stream));
+    CU_TRY(cudaStreamSynchronize(m->stream));
+    m->seq_len = 0;
+    return WICK_CUDA_OK;
+}
+
+int32_t build_model(wick_cuda_model* m, const GgufImage& g, uint32_t context_size) {
+    // config: Lfm2Model::from_gguf_with_id, lfm2.rs:97-185
+    std::string arch;
+    if (!g.get_str("general.architecture", &arch) || arch != "lfm2")
+        return fail(WICK_CUDA_ERR_BAD_GGUF, "unsupported architecture: " + (arch.empty() ? std::string("unknown") : arch));
+    if (context_size == 0) return fail(WICK_CUDA_ERR_BAD_ARG, "context_size must be > 0");
+    wick_cuda_config& c = m->cfg;
+    if (!g.get_u32("lfm2.block_count", &c.n_layers)) return fail(WICK_CUDA_ERR_BAD_GGUF, "missing lfm2.block_count");
+    if (!g.get_u32("lfm2.embedding_length", &c.hidden_size)) return fail(WICK_CUDA_ERR_BAD_GGUF, "missing lfm2.embedding_length");
+    if (!g.get_u32("lfm2.feed_forward_length", &c.intermediate_size))
+        return fail(WICK_CUDA_ERR_BAD_GGUF, "missing lfm2.feed_forward_length");
+    if (!g.get_u32("lfm2.attention.head_count", &c.n_heads)) return fail(WICK_CUDA_ERR_BAD_GGUF, "missing lfm2.attention.head_count");
+    if (!g.get_u32("lfm2.vocab_size", &c.vocab_size)) return fail(WICK_CUDA_ERR_BAD_GGUF, "missing lfm2.vocab_size");
+    uint32_t gguf_ctx = 128000;
+    g.get_u32("lfm2.context_length", &gguf_ctx);
+    c.max_seq_len = std::min(context_size, gguf_ctx);
+    c.rope_theta = 1000000.0f;
+    g.get_f32("lfm2.rope.freq_base", &c.rope_theta);
+    c.rms_norm_eps = 1e-5f;
+    g.get_f32("lfm2.attention.layer_norm_rms_epsilon", &c.rms_norm_eps);
+    c.conv_kernel_size = 3;
+    g.get_u32("lfm2.shortconv.l_cache", &c.conv_kernel_size);
+    std::vector<int32_t> kvh;
+    if (!g.get_i32_array("lfm2.attention.head_count_kv", &kvh)) return fail(WICK_CUDA_ERR_BAD_GGUF, "missing lfm2.attention.head_count_kv");
+    if (kvh.size() < c.n_layers)
+        return fail(WICK_CUDA_ERR_BAD_GGUF, "head_count_kv array length (" + std::to_string(kvh.size()) + ") < block_count (" +
+                                                std::to_string(c.n_layers) + ")");
+    if (!c.n_layers || !c.hidden_size || !c.n_heads || c.hidden_size % c.n_heads || !c.vocab_size || !c.intermediate_size)
+        return fail(WICK_CUDA_ERR_BAD_GGUF, "inconsistent model dimensions");
+    const int hs = c.hidden_size, is = c.intermediate_size;
+    m->head_dim = hs / c.n_heads;
+    const int hd = m->head_dim;
+    if (hs % QK || is % QK) return fail(WICK_CUDA_ERR_BAD_GGUF, "hidden and feed-forward sizes must be multiples of 32");
+    if (hd % 8 || hd > 256) return fail(WICK_CUDA_ERR_BAD_GGUF, "head_dim must be a multiple of 8 and <= 256");
+    if (c.conv_kernel_size < 1 || c.conv_kernel_size > 8) return fail(WICK_CUDA_ERR_BAD_GGUF, "unsupported shortconv.l_cache");
+    if (naive_attn_smem(m) > 200 * 1024)
+        return fail(WICK_CUDA_ERR_BAD_ARG, "context_size too large for the exact attention kernel (max ~51000 positions)");
+
+    CU_TRY(cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking));
+
+    size_t max_raw = 0;
+    m->layers.resize(c.n_layers);
+    c.n_kv_heads = 0;
+    for (uint32_t i = 0; i < c.n_layers; i++) {
+        Layer& L = m->layers[i];
+        L.is_attn = g.tensor("blk." + std::to_string(i) + ".attn_q.weight") != nullptr;  // lfm2.rs:154
+        if (L.is_attn) {
+            int nkv = kvh[i];
+            if (nkv <= 0 || c.n_heads % nkv)
+                return fail(WICK_CUDA_ERR_BAD_GGUF, "layer " + std::to_string(i) + ": n_kv_heads (" + std::to_string(nkv) +
+                                                        ") must be > 0 and divide n_heads (" + std::to_string(c.n_heads) + ")");
+            L.n_kv = nkv;
+            c.n_kv_heads = std::max<uint32_t>(c.n_kv_heads, nkv);
+        }
+    }
+    // staging buffer for the largest quantised tensor
+    max_raw = (size_t)std::max<size_t>((size_t)c.vocab_size * hs, (size_t)3 * hs * std::max(hs, is)) / QK * 34;
+    uint8_t* staging = nullptr;
+    CU_TRY(cudaMalloc((void**)&staging, max_raw));
+    struct StagingGuard {
+        uint8_t* p;
+        ~StagingGuard() { cudaFree(p); }
+    } guard{staging};
+
+    W_TRY(upload_weight(m, g, "token_embd.weight", c.vocab_size, hs, staging, &m->embd));
+    W_TRY(upload_f32(m, g, "token_embd_norm.weight", hs, &m->output_norm));  // the OUTPUT norm, lfm2.rs:188
+    const int dc = (int)c.conv_kernel_size - 1;
+    for (uint32_t i = 0; i < c.n_layers; i++) {
+        Layer& L = m->layers[i];
+        std::string p = "blk." + std::to_string(i) + ".";
+        W_TRY(upload_f32(m, g, p + "attn_norm.weight", hs, &L.attn_norm));
+        W_TRY(upload_f32(m, g, p + "ffn_norm.weight", hs, &L.ffn_norm));
+        W_TRY(upload_weight(m, g, p + "ffn_gate.weight", is, hs, staging, &L.gate));
+        W_TRY(upload_weight(m, g, p + "ffn_up.weight", is, hs, staging, &L.up));
+        W_TRY(upload_weight(m, g, p + "ffn_down.weight", hs, is, staging, &L.down));
+        if (L.is_attn) {
+            int kv_dim = L.n_kv * hd;
+            W_TRY(upload_weight(m, g, p + "attn_q.weight", hs, hs, staging, &L.q));
+            W_TRY(upload_weight(m, g, p + "attn_k.weight", kv_dim, hs, staging, &L.k));
+            W_TRY(upload_weight(m, g, p + "attn_v.weight", kv_dim, hs, staging, &L.v));
+            W_TRY(upload_weight(m, g, p + "attn_output.weight", hs, hs, staging, &L.o));
+            W_TRY(upload_f32(m, g, p + "attn_q_norm.weight", hd, &L.q_norm));
+            W_TRY(upload_f32(m, g, p + "attn_k_norm.weight", hd, &L.k_norm));
+            W_TRY(dev_alloc(m, &L.k_cache, (size_t)c.max_seq_len * kv_dim));
+            W_TRY(dev_alloc(m, &L.v_cache, (size_t)c.max_seq_len * kv_dim));
+        } else {
+            W_TRY(upload_weight(m, g, p + "shortconv.in_proj.weight", 3 * hs, hs, staging, &L.in_proj));
+            W_TRY(upload_weight(m, g, p + "shortconv.out_proj.weight", hs, hs, staging, &L.out_proj));
+            W_TRY(upload_f32(m, g, p + "shortconv.conv.weight", (size_t)hs * c.conv_kernel_size, &L.conv_w));
+            W_TRY(dev_alloc(m, &L.conv_state, (size_t)std::max(dc, 1) * hs));
+        }
+    }
+    // RoPE table
+    {
+        std::vector<float> cs, sn;
+        fill_rope_table(c.max_seq_len, hd, c.rope_theta, cs, sn);
+        W_TRY(dev_alloc(m, &m->rope_cos, cs.size()));
+        W_TRY(dev_alloc(m, &m->rope_sin, sn.size()));
+        CU_TRY(cudaMemcpy(m->rope_cos, cs.data(), cs.size() * 4, cudaMemcpyHostToDevice));
+        CU_TRY(cudaMemcpy(m->rope_sin, sn.data(), sn.size() * 4, cudaMemcpyHostToDevice));
+    }
+    // scratch
+    m->max_chunk = (int)std::min<uint32_t>(c.max_seq_len, 4096);
+    const size_t N = m->max_chunk;
+    const int kvmax = c.n_kv_heads * hd;
+    W_TRY(dev_alloc(m, &m->hidden, N * hs));
+    W_TRY(dev_alloc(m, &m->block_out, N * hs));
+    W_TRY(dev_alloc(m, &m->ffn_out, N * hs));
+    W_TRY(dev_alloc(m, &m->proj, N * 3 * hs));
+    W_TRY(dev_alloc(m, &m->qbuf, N * hs));
+    W_TRY(dev_alloc(m, &m->kbuf, N * std::max(kvmax, 1)));
+    W_TRY(dev_alloc(m, &m->vbuf, N * std::max(kvmax, 1)));
+    W_TRY(dev_alloc(m, &m->attn_out, N * hs));
+    W_TRY(dev_alloc(m, &m->gate, N * is));
+    W_TRY(dev_alloc(m, &m->up, N * is));
+    W_TRY(dev_alloc(m, &m->logits, (size_t)c.vocab_size));
+    W_TRY(dev_alloc(m, &m->q8s, N * (std::max(hs, is) / QK)));
+    W_TRY(dev_alloc(m, &m->q8q, N * std::max(hs, is)));
+    W_TRY(dev_alloc(m, &m->tokens_dev, N));
+    W_TRY(dev_alloc(m, &m->ctl, 1));
+    W_TRY(dev_alloc(m, &m->argmax_tok, 1));
+    m->ring_len = (int)c.max_seq_len;
+    W_TRY(dev_alloc(m, &m->ring, (size_t)m->ring_len));
+    CU_TRY(cudaMallocHost((void**)&m->h_u32, std::max<size_t>((size_t)std::max<int>(m->ring_len, m->max_chunk) * 4, 256)));
+    CU_TRY(cudaMallocHost((void**)&m->h_logits, (size_t)c.vocab_size * 4));
+    CU_TRY(cudaMemset(m->ctl, 0, sizeof(DecodeCtl)));
+    W_TRY(reset_sequence(m));
+    if (naive_attn_smem(m) > 48 * 1024) {
+        configure_naive_attention_smem(naive_attn_smem(m));
+    }
+    W_TRY(capture_graph(m, false, &m->g_logits));
+    W_TRY(capture_graph(m, true, &m->g_greedy));
+    CU_TRY(cudaStreamSynchronize(m->stream));
+    return WICK_CUDA_OK;
+}
+
+int32_t check_model(const wick_cuda_model* m) {
+    if (!m) return fail(WICK_CUDA_ERR_BAD_ARG, "model handle is NULL");
+    return WICK_CUDA_OK;
+}
+
+int32_t pre_step(wick_cuda_model* m, uint32_t token, uint32_t pos) {
+    W_TRY(check_model(m));
+    if (token >= m->cfg.vocab_size)
+        return fail(WICK_CUDA_ERR_BAD_ARG, "token_id " + std::to_string(token) + " out of range (vocab_size=" +
+                                               std::to_string(m->cfg.vocab_size) + ")");
+    if (pos != m->seq_len)
+        return fail(WICK_CUDA_ERR_BAD_ARG, "pos " + std::to_string(pos) + " != model seq_len " + std::to_string(m->seq_len));
+    if (m->seq_len >= m->cfg.max_seq_len)
+        return fail(WICK_CUDA_ERR_CONTEXT_FULL, "seq_len " + std::to_string(m->seq_len) + " reached max_seq_len " +
+                                                    std::to_string(m->cfg.max_seq_len));
+    CU_TRY(cudaSetDevice(m->device));
+    return WICK_CUDA_OK;
+}
+
+}  // namespace
+
+// ── C ABI ──────────────────────────────────────────────────────────────────
+extern "C" {
+
+int32_t wick_cuda_device_count(int32_t* count) {
+    if (!count) return fail(WICK_CUDA_ERR_BAD_ARG, "count is NULL");
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess) {
+        *count = 0;
+        return fail(WICK_CUDA_ERR_CUDA, std::string("cudaGetDeviceCount: ") + cudaGetErrorString(e));
+    }
+    *count = n;
+    return WICK_CUDA_OK;
+}
+
+const char* wick_cuda_last_error(void) { return g_last_error.c_str(); }
+
+int32_t wick_cuda_model_create(const uint8_t* gguf_host, size_t gguf_len, uint32_t context_size, int32_t device,
+                               wick_cuda_model** out) {
+    if (!gguf_host || !out) return fail(WICK_CUDA_ERR_BAD_ARG, "NULL argument");
+    *out = nullptr;
+    std::unique_ptr<GgufImage> img;
+    try {
+        img.reset(new GgufImage(gguf_host, gguf_len));
+    } catch (const std::exception& e) {
+        return fail(WICK_CUDA_ERR_BAD_GGUF, e.what());
+    }
+    int ndev = 0;
+    CU_TRY(cudaGetDeviceCount(&ndev));
+    if (device < 0 || device >= ndev) return fail(WICK_CUDA_ERR_BAD_ARG, "no such CUDA device: " + std::to_string(device));
+    CU_TRY(cudaSetDevice(device));
+    std::unique_ptr<wick_cuda_model> m(new wick_cuda_model());
+    m->device = device;
+    int32_t r = build_model(m.get(), *img, context_size);
+    if (r != WICK_CUDA_OK) return r;
+    *out = m.release();
+    return WICK_CUDA_OK;
+}
+
+int32_t wick_cuda_model_create_from_file(const char* path, uint32_t context_size, int32_t device, wick_cuda_model** out) {
+    if (!path || !out) return fail(WICK_CUDA_ERR_BAD_ARG, "NULL argument");
+    std::ifstream f(path, std::ios::binary | std::ios::ate);
+    if (!f) return fail(WICK_CUDA_ERR_BAD_GGUF, std::string("cannot open ") + path);
+    std::streamsize len = f.tellg();
+    f.seekg(0);
+    std::vector<uint8_t> buf((size_t)len);
+    if (len > 0 && !f.read((char*)buf.data(), len)) return fail(WICK_CUDA_ERR_BAD_GGUF, std::string("cannot read ") + path);
+    return wick_cuda_model_create(buf.data(), buf.size(), context_size, device, out);
+}
+
+void wick_cuda_model_destroy(wick_cuda_model* m) { delete m; }
+
+int32_t wick_cuda_model_config(const wick_cuda_model* m, wick_cuda_config* out) {
+    W_TRY(check_model(m));
+    if (!out) return fail(WICK_CUDA_ERR_BAD_ARG, "out is NULL");
+    *out = m->cfg;
+    return WICK_CUDA_OK;
+}
+
+int32_t wick_cuda_model_kv_heads_per_layer(const wick_cuda_model* m, uint32_t* out, uint32_t n) {
+    W_TRY(check_model(m));
+    if (!out || n != m->cfg.n_layers) return fail(WICK_CUDA_ERR_BAD_ARG, "out is NULL or n != n_layers");
+    for (uint32_t i = 0; i < n; i++) out[i] = m->layers[i].is_attn ? m->layers[i].n_kv : 0;
+    return WICK_CUDA_OK;
+}
+
+int32_t wick_cuda_gpu_memory_bytes(const wick_cuda_model* m, uint64_t* out) {
+    W_TRY(check_model(m));
+    if (!out) return fail(WICK_CUDA_ERR_BAD_ARG, "out is NULL");
+    *out = m->bytes;
+    return WICK_CUDA_OK;
+}
+
+int32_t wick_cuda_forward(wick_cuda_model* m, uint32_t token, uint32_t pos, float* logits_host) {
+    W_TRY(pre_step(m, token, pos));
+    if (!logits_host) return fail(WICK_CUDA_ERR_BAD_ARG, "logits_host is NULL");
+    m->h_u32[0] = token;
+    CU_TRY(cudaMemcpyAsync(&m->ctl->token, m->h_u32, 4, cudaMemcpyHostToDevice, m->stream));
+    CU_TRY(cudaGraphLaunch(m->g_logits, m->stream));
+    CU_TRY(cudaMemcpyAsync(m->h_logits, m->logits, (size_t)m->cfg.vocab_size * 4, cudaMemcpyDeviceToHost, m->stream));
+    CU_TRY(cudaStreamSynchronize(m->stream));
+    memcpy(logits_host, m->h_logits, (size_t)m->cfg.vocab_size * 4);
+    m->seq_len += 1;
+    return WICK_CUDA_OK;
+}
+
+int32_t wick_cuda_forward_greedy(wick_cuda_model* m, uint32_t token, uint32_t pos, uint32_t* next_token) {
+    W_TRY(pre_step(m, token, pos));
+    if (!next_token) return fail(WICK_CUDA_ERR_BAD_ARG, "next_token is NULL");
+    m->h_u32[0] = token;
+    CU_TRY(cudaMemcpyAsync(&m->ctl->token, m->h_u32, 4, cudaMemcpyHostToDevice, m->stream));
+    CU_TRY(cudaGraphLaunch(m->g_greedy, m->stream));
+    CU_TRY(cudaMemcpyAsync(m->h_u32 + 1, m->argmax_tok, 4, cudaMemcpyDeviceToHost, m->stream));
+    CU_TRY(cudaStreamSynchronize(m->stream));
+    *next_token = m->h_u32[1];
+    m->seq_len += 1;
+    return WICK_CUDA_OK;
+}
+
+int32_t wick_cuda_generate_greedy(wick_cuda_model* m, uint32_t first_token, uint32_t n_steps, uint32_t* out_tokens_host) {
+    W_TRY(check_model(m));
+    if (n_steps == 0) return WICK_CUDA_OK;
+    W_TRY(pre_step(m, first_token, m->seq_len));
+    if (!out_tokens_host) return fail(WICK_CUDA_ERR_BAD_ARG, "out_tokens_host is NULL");
+    if ((uint64_t)m->seq_len + n_steps > m->cfg.max_seq_len)
+        return fail(WICK_CUDA_ERR_CONTEXT_FULL, "seq_len + n_steps exceeds max_seq_len " + std::to_string(m->cfg.max_seq_len));
+    // token and ring cursor for this run
+    uint32_t init[3] = {first_token, m->seq_len, 0};
+    memcpy(m->h_u32, init, sizeof(init));
+    CU_TRY(cudaMemcpyAsync(m->ctl, m->h_u32, sizeof(init), cudaMemcpyHostToDevice, m->stream));
+    for (uint32_t i = 0; i < n_steps; i++) CU_TRY(cudaGraphLaunch(m->g_greedy, m->stream));
+    CU_TRY(cudaMemcpyAsync(m->h_u32, m->ring, (size_t)n_steps * 4, cudaMemcpyDeviceToHost, m->stream));
+    CU_TRY(cudaStreamSynchronize(m->stream));
+    memcpy(out_tokens_host, m->h_u32, (size_t)n_steps * 4);
+    m->seq_len += n_steps;
+    return WICK_CUDA_OK;
+}
+
+int32_t wick_cuda_forward_prefill(wick_cuda_model* m, const uint32_t* tokens_host, uint32_t n, uint32_t start_pos,
+                                  float* logits_host) {
+    W_TRY(check_model(m));
+    if (!tokens_host || !logits_host) return fail(WICK_CUDA_ERR_BAD_ARG, "NULL argument");
+    if (n == 0) return fail(WICK_CUDA_ERR_BAD_ARG, "forward_prefill requires at least one token");
+    for (uint32_t i = 0; i < n; i++)
+        if (tokens_host[i] >= m->cfg.vocab_size)
+            return fail(WICK_CUDA_ERR_BAD_ARG, "token_id " + std::to_string(tokens_host[i]) + " out of range for vocab size " +
+                                                   std::to_string(m->cfg.vocab_size));
+    if (start_pos != 0 && start_pos != m->seq_len)
+        return fail(WICK_CUDA_ERR_BAD_ARG, "start_pos " + std::to_string(start_pos) + " != model seq_len " + std::to_string(m->seq_len));
+    if ((uint64_t)start_pos + n > m->cfg.max_seq_len)
+        return fail(WICK_CUDA_ERR_CONTEXT_FULL, "start_pos + n = " + std::to_string((uint64_t)start_pos + n) +
+                                                    " exceeds max_seq_len " + std::to_string(m->cfg.max_seq_len));
+    CU_TRY(cudaSetDevice(m->device));
+    if (start_pos == 0) W_TRY(reset_sequence(m));  // new sequence, metal_lfm2.rs:2361-2397
+    const bool flash = n >= 256;  // FLASH_ATTN_THRESHOLD, lfm2.rs:1646-1647
+    for (uint32_t c0 = 0; c0 < n; c0 += m->max_chunk) {
+        uint32_t cn = std::min<uint32_t>(m->max_chunk, n - c0);
+        memcpy(m->h_u32, tokens_host + c0, (size_t)cn * 4);
+        CU_TRY(cudaMemcpyAsync(m->tokens_dev, m->h_u32, (size_t)cn * 4, cudaMemcpyHostToDevice, m->stream));
+        enqueue_prefill_chunk(m, (int)cn, (int)(start_pos + c0), flash, c0 + cn == n);
+        CU_TRY(cudaGetLastError());
+        CU_TRY(cudaStreamSynchronize(m->stream));  // h_u32 is reused by the next chunk
+    }
+    uint32_t newpos[2] = {0, start_pos + n};
+    memcpy(m->h_u32, newpos, 8);
+    CU_TRY(cudaMemcpyAsync(&m->ctl->pos, m->h_u32 + 1, 4, cudaMemcpyHostToDevice, m->stream));
+    CU_TRY(cudaMemcpyAsync(m->h_logits, m->logits, (size_t)m->cfg.vocab_size * 4, cudaMemcpyDeviceToHost, m->stream));
+    CU_TRY(cudaStreamSynchronize(m->stream));
+    memcpy(logits_host, m->h_logits, (size_t)m->cfg.vocab_size * 4);
+    m->seq_len = start_pos + n;
+    return WICK_CUDA_OK;
+}
+
+int32_t wick_cuda_reset(wick_cuda_model* m) {
+    W_TRY(check_model(m));
+    CU_TRY(cudaSetDevice(m->device));
+    return reset_sequence(m);
+}
+
+int32_t wick_cuda_seq_len(const wick_cuda_model* m, uint32_t* out) {
+    W_TRY(check_model(m));
+    if (!out) return fail(WICK_CUDA_ERR_BAD_ARG, "out is NULL");
+    *out = m->seq_len;
+    return WICK_CUDA_OK;
+}
+
+// snapshot image: u32 magic, u32 seq_len, then per layer either K rows + V rows (seq_len x
+// kv_dim f32 each) or the conv buffer (d_conv x hidden f32)
+static const uint32_t SNAP_MAGIC = 0x534B4357u;  // "WCKS"
+
+int32_t wick_cuda_snapshot_size(const wick_cuda_model* m, uint64_t* bytes) {
+    W_TRY(check_model(m));
+    if (!bytes) return fail(WICK_CUDA_ERR_BAD_ARG, "bytes is NULL");
+    uint64_t b = 8;
+    const int dc = (int)m->cfg.conv_kernel_size - 1;
+    for (const Layer& L : m->layers)
+        b += L.is_attn ? (uint64_t)2 * m->seq_len * L.n_kv * m->head_dim * 4 : (uint64_t)dc * m->cfg.hidden_size * 4;
+    *bytes = b;
+    return WICK_CUDA_OK;
+}
+
+int32_t wick_cuda_snapshot(wick_cuda_model* m, uint8_t* out_host, uint64_t capacity) {
+    uint64_t need = 0;
+    W_TRY(wick_cuda_snapshot_size(m, &need));
+    if (!out_host || capacity < need) return fail(WICK_CUDA_ERR_BAD_ARG, "snapshot buffer too small");
+    CU_TRY(cudaSetDevice(m->device));
+    CU_TRY(cudaStreamSynchronize(m->stream));
+    uint32_t head[2] = {SNAP_MAGIC, m->seq_len};
+    memcpy(out_host, head, 8);
+    uint8_t* p = out_host + 8;
+    const int dc = (int)m->cfg.conv_kernel_size - 1;
+    for (const Layer& L : m->layers) {
+        if (L.is_attn) {
+            size_t b = (size_t)m->seq_len * L.n_kv * m->head_dim * 4;
+            if (b) {
+                CU_TRY(cudaMemcpy(p, L.k_cache, b, cudaMemcpyDeviceToHost));
+                CU_TRY(cudaMemcpy(p + b, L.v_cache, b, cudaMemcpyDeviceToHost));
+            }
+            p += 2 * b;
+        } else {
+            size_t b = (size_t)dc * m->cfg.hidden_size * 4;
+            if (b) CU_TRY(cudaMemcpy(p, L.conv_state, b, cudaMemcpyDeviceToHost));
+            p += b;
+        }
+    }
+    return WICK_CUDA_OK;
+}
+
+int32_t wick_cuda_restore(wick_cuda_model* m, const uint8_t* snap_host, uint64_t len) {
+    W_TRY(check_model(m));
+    if (!snap_host || len < 8) return fail(WICK_CUDA_ERR_BAD_ARG, "snapshot too short");
+    uint32_t head[2];
+    memcpy(head, snap_host, 8);
+    if (head[0] != SNAP_MAGIC) return fail(WICK_CUDA_ERR_BAD_ARG, "not a wick_cuda snapshot");
+    if (head[1] > m->cfg.max_seq_len) return fail(WICK_CUDA_ERR_CONTEXT_FULL, "snapshot longer than max_seq_len");
+    uint32_t saved = m->seq_len;
+    m->seq_len = head[1];
+    uint64_t need = 0;
+    wick_cuda_snapshot_size(m, &need);
+    if (need != len) {
+        m->seq_len = saved;
+        return fail(WICK_CUDA_ERR_BAD_ARG, "snapshot size does not match this model");
+    }
+    CU_TRY(cudaSetDevice(m->device));
+    CU_TRY(cudaStreamSynchronize(m->stream));
+    const uint8_t* p = snap_host + 8;
+    const int dc = (int)m->cfg.conv_kernel_size - 1;
+    for (const Layer& L : m->layers) {
+        if (L.is_attn) {
+            size_t b = (size_t)m->seq_len * L.n_kv * m->head_dim * 4;
+            if (b) {
+                CU_TRY(cudaMemcpy(L.k_cache, p, b, cudaMemcpyHostToDevice));
+                CU_TRY(cudaMemcpy(L.v_cache, p + b, b, cudaMemcpyHostToDevice));
+            }
+            p += 2 * b;
+        } else {
+            size_t b = (size_t)dc * m->cfg.hidden_size * 4;
+            if (b) CU_TRY(cudaMemcpy(L.conv_state, p, b, cudaMemcpyHostToDevice));
+            p += b;
+        }
+    }
+    CU_TRY(cudaMemcpy(&m->ctl->pos, &m->seq_len, 4, cudaMemcpyHostToDevice));
+    return WICK_CUDA_OK;
+}
+
+int32_t wick_cuda_read_kv(wick_cuda_model* m, uint32_t layer, float* k_host, float* v_host) {
+    W_TRY(check_model(m));
+    if (layer >= m->layers.size() || !m->layers[layer].is_attn) return fail(WICK_CUDA_ERR_BAD_ARG, "not an attention layer");
+    CU_TRY(cudaSetDevice(m->device));
+    CU_TRY(cudaStreamSynchronize(m->stream));
+    const Layer& L = m->layers[layer];
+    size_t b = (size_t)m->seq_len * L.n_kv * m->head_dim * 4;
+    if (b && k_host) CU_TRY(cudaMemcpy(k_host, L.k_cache, b, cudaMemcpyDeviceToHost));
+    if (b && v_host) CU_TRY(cudaMemcpy(v_host, L.v_cache, b, cudaMemcpyDeviceToHost));
+    return WICK_CUDA_OK;
+}
+
+int32_t wick_cuda_read_conv_state(wick_cuda_model* m, uint32_t layer, float* out_host) {
+    W_TRY(check_model(m));
+    if (layer >= m->layers.size() || m->layers[layer].is_attn || !out_host) return fail(WICK_CUDA_ERR_BAD_ARG, "not a conv layer");
+    CU_TRY(cudaSetDevice(m->device));
+    CU_TRY(cudaStreamSynchronize(m->stream));
+    size_t b = (size_t)((int)m->cfg.conv_kernel_size - 1) * m->cfg.hidden_size * 4;
+    if (b) CU_TRY(cudaMemcpy(out_host, m->layers[layer].conv_state, b, cudaMemcpyDeviceToHost));
+    return WICK_CUDA_OK;
+}
+
+// ── operators ──────────────────────────────────────────────────────────────
+
+int32_t wick_cuda_weight_create(int32_t dtype, const uint8_t* raw_host, uint32_t mrows, uint32_t k, wick_cuda_weight** out) {
+    if (!raw_host || !out) return fail(WICK_CUDA_ERR_BAD_ARG, "NULL argument");
+    *out = nullptr;
+    if (dtype != DT_Q4_0 && dtype != DT_Q8_0) return fail(WICK_CUDA_ERR_UNSUPPORTED_DTYPE, "only Q4_0 (2) and Q8_0 (8) weights are supported");
+    if (k == 0 || k % QK || mrows == 0) return fail(WICK_CUDA_ERR_BAD_ARG, "k must be a positive multiple of 32 and m > 0");
+    std::unique_ptr<wick_cuda_weight> w(new wick_cuda_weight());
+    CU_TRY(cudaGetDevice(&w->device));
+    w->w.m = (int)mrows;
+    w->w.k = (int)k;
+    w->w.dtype = dtype;
+    size_t nblk = (size_t)mrows * (k / QK);
+    uint8_t *staging = nullptr, *q = nullptr;
+    __half* d = nullptr;
+    CU_TRY(cudaMalloc((void**)&staging, nblk * 34));
+    cudaError_t e1 = cudaMalloc((void**)&q, std::max<size_t>(w->w.q_bytes(), 256));
+    cudaError_t e2 = cudaMalloc((void**)&d, std::max<size_t>(w->w.d_bytes(), 256));
+    int32_t r = WICK_CUDA_OK;
+    if (e1 != cudaSuccess || e2 != cudaSuccess) r = fail(WICK_CUDA_ERR_OOM, "cudaMalloc failed for weight planes");
+    if (r == WICK_CUDA_OK) r = upload_weight_raw(dtype, raw_host, (int)mrows, (int)k, staging, nullptr, q, d);
+    cudaFree(staging);
+    if (r != WICK_CUDA_OK) {
+        cudaFree(q);
+        cudaFree(d);
+        return r;
+    }
+    w->w.q = q;
+    w->w.d = d;
+    *out = w.release();
+    return WICK_CUDA_OK;
+}
+
+void wick_cuda_weight_destroy(wick_cuda_weight* w) {
+    if (!w) return;
+    cudaFree((void*)w->w.q);
+    cudaFree((void*)w->w.d);
+    delete w;
+}
+
+#define OP_END()                  \
+    CU_TRY(cudaGetLastError());   \
+    return WICK_CUDA_OK
+
+int32_t wick_cuda_quantize_q8_0(const float* x_dev, uint32_t n, uint32_t k, float* scales_dev, int8_t* quants_dev, void* stream) {
+    if (!x_dev || !scales_dev || !quants_dev) return fail(WICK_CUDA_ERR_BAD_ARG, "NULL argument");
+    if (k % QK) return fail(WICK_CUDA_ERR_BAD_ARG, "quantize_q8_0: k must be divisible by 32");
+    launch_quant_rows((cudaStream_t)stream, x_dev, (int)n, (int)k, scales_dev, quants_dev);
+    OP_END();
+}
+
+int32_t wick_cuda_gemv_q8(const wick_cuda_weight* w, const float* xs_dev, const int8_t* xq_dev, float* y_dev, void* stream) {
+    if (!w || !xs_dev || !xq_dev || !y_dev) return fail(WICK_CUDA_ERR_BAD_ARG, "NULL argument");
+    GemvJob j{};
+    j.count = 1;
+    j.w[0] = w->w;
+    j.y[0] = y_dev;
+    launch_gemv((cudaStream_t)stream, j, xs_dev, xq_dev);
+    OP_END();
+}
+
+int32_t wick_cuda_gemm_q8(const wick_cuda_weight* w, const float* bs_dev, const int8_t* bq_dev, uint32_t n, float* out_dev,
+                          void* stream) {
+    if (!w || !bs_dev || !bq_dev || !out_dev) return fail(WICK_CUDA_ERR_BAD_ARG, "NULL argument");
+    launch_gemm((cudaStream_t)stream, w->w, bs_dev, bq_dev, (int)n, out_dev);
+    OP_END();
+}
+
+int32_t wick_cuda_block_sums(const wick_cuda_weight* w, const int8_t* xq_dev, int32_t* s_dev, void* stream) {
+    if (!w || !xq_dev || !s_dev) return fail(WICK_CUDA_ERR_BAD_ARG, "NULL argument");
+    launch_block_sums((cudaStream_t)stream, w->w, xq_dev, s_dev);
+    OP_END();
+}
+
+int32_t wick_cuda_rmsnorm(float* x_dev, const float* weight_dev, uint32_t n, uint32_t dim, float eps, void* stream) {
+    if (!x_dev || !weight_dev) return fail(WICK_CUDA_ERR_BAD_ARG, "NULL argument");
+    if (n && dim) launch_rmsnorm((cudaStream_t)stream, x_dev, weight_dev, (int)n, (int)dim, eps);
+    OP_END();
+}
+
+int32_t wick_cuda_silu_mul(float* gate_dev, const float* up_dev, uint64_t count, void* stream) {
+    if (!gate_dev || !up_dev) return fail(WICK_CUDA_ERR_BAD_ARG, "NULL argument");
+    launch_silu_mul((cudaStream_t)stream, gate_dev, up_dev, count);
+    OP_END();
+}
+
+int32_t wick_cuda_expf(const float* x_dev, float* y_dev, uint64_t count, void* stream) {
+    if (!x_dev || !y_dev) return fail(WICK_CUDA_ERR_BAD_ARG, "NULL argument");
+    launch_expf((cudaStream_t)stream, x_dev, y_dev, count);
+    OP_END();
+}
+
+int32_t wick_cuda_rope(float* q_dev, float* k_dev, uint32_t pos, uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim,
+                       float freq_base, void* stream) {
+    if (!q_dev || !k_dev) return fail(WICK_CUDA_ERR_BAD_ARG, "NULL argument");
+    if (head_dim % 2 || head_dim > 512) return fail(WICK_CUDA_ERR_BAD_ARG, "head_dim must be even and <= 512");
+    const int half = head_dim / 2;
+    std::vector<float> tab(2 * half);
+    float theta_scale = powf(freq_base, -2.0f / (float)head_dim);
+    float theta = (float)pos;
+    for (int i = 0; i < half; i++) {
+        tab[i] = cosf(theta);
+        tab[half + i] = sinf(theta);
+        theta *= theta_scale;
+    }
+    float* dtab = nullptr;
+    cudaStream_t st = (cudaStream_t)stream;
+    CU_TRY(cudaMallocAsync((void**)&dtab, tab.size() * 4, st));
+    CU_TRY(cudaMemcpyAsync(dtab, tab.data(), tab.size() * 4, cudaMemcpyHostToDevice, st));
+    launch_rope(st, q_dev, k_dev, dtab, dtab + half, (int)n_heads, (int)n_kv_heads, (int)head_dim);
+    CU_TRY(cudaStreamSynchronize(st));  // `tab` is pageable host memory
+    CU_TRY(cudaFreeAsync(dtab, st));
+    OP_END();
+}
+
+int32_t wick_cuda_attention_decode(const float* q_dev, const float* k_cache_dev, const float* v_cache_dev, float* out_dev,
+                                   uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim, uint32_t seq, void* stream) {
+    return wick_cuda_attention_prefill(q_dev, k_cache_dev, v_cache_dev, out_dev, 1, seq ? seq - 1 : 0, n_heads, n_kv_heads,
+                                       head_dim, 0, stream);
+}
+
+int32_t wick_cuda_attention_prefill(const float* q_dev, const float* k_cache_dev, const float* v_cache_dev, float* out_dev,
+                                    uint32_t n, uint32_t start_pos, uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim,
+                                    int32_t flash, void* stream) {
+    if (!q_dev || !k_cache_dev || !v_cache_dev || !out_dev) return fail(WICK_CUDA_ERR_BAD_ARG, "NULL argument");
+    if (!n_kv_heads || n_heads % n_kv_heads || head_dim % 8 || head_dim > 256 || n == 0)
+        return fail(WICK_CUDA_ERR_BAD_ARG, "bad attention shape");
+    if (flash) {
+        if (head_dim != 64 && head_dim != 32) return fail(WICK_CUDA_ERR_BAD_ARG, "tiled attention supports head_dim 32 or 64");
+        launch_attention_flash((cudaStream_t)stream, q_dev, k_cache_dev, v_cache_dev, out_dev, (int)n, (int)start_pos, (int)n_heads,
+                               (int)n_kv_heads, (int)head_dim);
+    } else {
+        size_t smem = (size_t)(head_dim + start_pos + n) * 4;
+        if (smem > 200 * 1024) return fail(WICK_CUDA_ERR_BAD_ARG, "sequence too long for the per-token attention kernel");
+        if (smem > 48 * 1024) {
+                configure_naive_attention_smem(smem);
+        }
+        launch_attention_naive((cudaStream_t)stream, q_dev, k_cache_dev, v_cache_dev, out_dev, (int)n, (int)start_pos, nullptr,
+                               (int)n_heads, (int)n_kv_heads, (int)head_dim, (int)(start_pos + n));
+    }
+    OP_END();
+}
+
+int32_t wick_cuda_shortconv(const float* proj_dev, const float* conv_w_dev, float* state_dev, float* out_dev, uint32_t n,
+                            uint32_t hidden, uint32_t kernel_size, void* stream) {
+    if (!proj_dev || !conv_w_dev || !state_dev || !out_dev) return fail(WICK_CUDA_ERR_BAD_ARG, "NULL argument");
+    if (hidden % QK || kernel_size < 1 || kernel_size > 8) return fail(WICK_CUDA_ERR_BAD_ARG, "bad short-conv shape");
+    launch_shortconv((cudaStream_t)stream, proj_dev, conv_w_dev, state_dev, (int)n, (int)hidden, (int)kernel_size, out_dev, nullptr,
+                     nullptr);
+    OP_END();
+}
+
+int32_t wick_cuda_argmax(const float* logits_dev, uint32_t count, uint32_t* out_dev, void* stream) {
+    if (!logits_dev || !out_dev || !count) return fail(WICK_CUDA_ERR_BAD_ARG, "NULL argument or empty input");
+    cudaStream_t st = (cudaStream_t)stream;
+    unsigned long long* scratch = nullptr;
+    CU_TRY(cudaMallocAsync((void**)&scratch, 8, st));
+    CU_TRY(cudaMemsetAsync(scratch, 0, 8, st));
+    launch_argmax(st, logits_dev, (int)count, scratch, out_dev);
+    CU_TRY(cudaFreeAsync(scratch, st));
+    OP_END();
+}
+
+}  // extern "C"

@@ -72,6 +72,12 @@ class Lfm2Spec:
         params += self.vocab * hs
         return params // QK * bb
 
+    def decode_bytes_per_token(self, qtype: str) -> int:
+        """Algorithmic HBM bytes of one decode step: every quantised weight once (the tied
+        vocabulary head included) plus the one embedding row that is looked up."""
+        bb = {"q4_0": 18, "q8_0": 34}[qtype]
+        return self.quant_bytes(qtype) + self.hidden // QK * bb
+
 
 _LFM2_ATTN = (2, 5, 8, 10, 12, 14)
 
@@ -80,7 +86,7 @@ SPECS: Dict[str, Lfm2Spec] = {
     "lfm2-350m": Lfm2Spec("lfm2-350m", 1024, 16, _LFM2_ATTN, 16, 8, 4608, 65536, 8192),
     # 1.6B-class (LFM2.5-1.6B shapes)
     "lfm2.5-1.6b": Lfm2Spec("lfm2.5-1.6b", 2048, 16, _LFM2_ATTN, 32, 8, 6912, 65536, 8192),
-    # small shapes for parity tests the CPU oracle finishes in seconds
+    # small shapes for parity tests that a CPU reference finishes in seconds
     "tiny": Lfm2Spec("tiny", 256, 4, (1, 3), 4, 2, 512, 512, 1024),
     "tiny-wide": Lfm2Spec("tiny-wide", 512, 5, (2, 4), 8, 2, 1152, 1024, 2048),
 }
