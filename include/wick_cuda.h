@@ -124,6 +124,13 @@ int32_t wick_cuda_snapshot_size(const wick_cuda_model* m, uint64_t* bytes);
 int32_t wick_cuda_snapshot(wick_cuda_model* m, uint8_t* out_host, uint64_t capacity);
 int32_t wick_cuda_restore(wick_cuda_model* m, const uint8_t* snap_host, uint64_t len);
 
+/* Profiling hooks in the spirit of wick's GPU timers (WICK_PROFILE=gpu, metal_lfm2.rs:3922-3984):
+ * device time, from CUDA events on the model's stream, of the GPU work of the last forward /
+ * forward_greedy / forward_prefill / generate_greedy call (host<->device copies included), and the
+ * number of kernels this model has launched since it was created (graph replays count their nodes). */
+int32_t wick_cuda_last_elapsed_ms(wick_cuda_model* m, float* ms);
+int32_t wick_cuda_kernel_launches(const wick_cuda_model* m, uint64_t* count);
+
 /* Debug / parity taps: f32 K and V rows [0, seq_len) x kv_dim of an attention layer
  * (LayerState::Attention, kv_cache.rs:62-70) or the [d_conv][hidden] rolling buffer of a conv
  * layer (LayerState::Conv, kv_cache.rs:72-74). */

@@ -14,19 +14,38 @@ constexpr int QK = 32;         // elements per quantised block
 constexpr int DT_Q4_0 = 2;     // ggml type ids (wick/src/gguf.rs:38, :42)
 constexpr int DT_Q8_0 = 8;
 
-// A quantised matrix in the library's device layout: the 16 (Q4_0) or 32 (Q8_0)
-// quant bytes of every block in one plane, row-major [m][k/32], the f16 scales in
-// a second plane [m][k/32].  Same bytes as the GGUF blocks (wick/src/quant.rs:13-34),
-// but 16-byte aligned so they can be fetched with 128-bit loads / bulk copies.
+// A quantised matrix in the library's device layout.  Same bytes as the GGUF blocks
+// (wick/src/quant.rs:13-34: f16 scale + 16 nibble bytes, or + 32 int8), re-ordered once at
+// load time so that the eight accumulation chains of four consecutive rows sit next to each
+// other: rows are taken in groups of four and, inside a group, the quant words are stored
+// block-major.  With (r = row in group, l = 32-bit word of the lane, p = block parity):
+//   Q4_0 quant plane : word  b*16 + r*4 + l                    (16 bytes per row per block)
+//   Q8_0 quant plane : word  (b/2)*64 + half*32 + p*16 + r*4 + l   (half 0 = elements 0..15)
+//   scale plane      : f16   b*4 + r
+// A warp whose lanes are (p, r, l) therefore reads 128 contiguous bytes per step, from
+// global or shared memory alike (no bank conflicts), and any run of whole groups is one
+// contiguous, 16-byte aligned byte range that a single bulk copy can fetch.
+// m is padded to a multiple of 4 with zero rows; for Q8_0 an odd block count is padded to even.
 struct DevWeight {
     const uint8_t* q = nullptr;
     const __half* d = nullptr;
     int m = 0, k = 0, dtype = 0;
     __host__ __device__ int nb() const { return k / QK; }
-    __host__ __device__ int qrow_bytes() const { return dtype == DT_Q4_0 ? k / 2 : k; }
-    size_t q_bytes() const { return (size_t)m * qrow_bytes(); }
-    size_t d_bytes() const { return (size_t)m * nb() * 2; }
+    __host__ __device__ int groups() const { return (m + 3) / 4; }
+    // bytes of one 4-row group in each plane
+    __host__ __device__ size_t q_group_bytes() const {
+        return dtype == DT_Q4_0 ? (size_t)nb() * 64 : (size_t)((nb() + 1) / 2) * 256;
+    }
+    __host__ __device__ size_t d_group_bytes() const { return (size_t)nb() * 8; }
+    size_t q_bytes() const { return (size_t)groups() * q_group_bytes(); }
+    size_t d_bytes() const { return (size_t)groups() * d_group_bytes(); }
 };
+
+// Word offsets inside a group (see DevWeight).
+__host__ __device__ __forceinline__ int q4_word(int b, int r, int l) { return b * 16 + r * 4 + l; }
+__host__ __device__ __forceinline__ int q8_word(int b, int half, int r, int l) {
+    return (b >> 1) * 64 + half * 32 + (b & 1) * 16 + r * 4 + l;
+}
 
 __device__ __forceinline__ int dp4a_ss(int a, int b, int c) { return __dp4a(a, b, c); }
 

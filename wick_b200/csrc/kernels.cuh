@@ -5,6 +5,10 @@
 
 namespace wick {
 
+// Number of kernels launched by the launch_* wrappers on this host thread (also counts launches
+// recorded into a stream capture).
+extern thread_local unsigned long long g_kernel_launches;
+
 // Device-resident control block of the decode step: lets one captured CUDA graph
 // serve every position (kernels read the token and position from here).
 struct DecodeCtl {
@@ -16,7 +20,7 @@ struct DecodeCtl {
 };
 
 // Re-layout of GGUF block rows into the quant / scale planes of DevWeight.
-void launch_repack(cudaStream_t st, int dtype, const uint8_t* raw, uint8_t* q, __half* d, size_t n_blocks);
+void launch_repack(cudaStream_t st, const DevWeight& w, const uint8_t* raw, uint8_t* q, __half* d);
 
 // Embedding rows: out[j][:] = dequantised row tokens[j] (quant.rs:78-105, :154-177).
 // tokens may be a device array, or NULL to read the single token from ctl.

@@ -121,6 +121,7 @@ void launch_attention_naive(cudaStream_t st, const float* q, const float* k_cach
                             int max_seq) {
     dim3 grid(n_heads, n);
     size_t smem = (size_t)(head_dim + max_seq) * sizeof(float);
+    g_kernel_launches++;
     k_attention_naive<<<grid, NAIVE_THREADS, smem, st>>>(q, k_cache, v_cache, out, start_pos, ctl, n_heads, n_kv_heads,
                                                         head_dim);
 }
@@ -234,6 +235,7 @@ void launch_attention_flash(cudaStream_t st, const float* q, const float* k_cach
     const int group = n_heads / n_kv_heads;
     const int qb = FLASH_THREADS / group;
     dim3 grid(n_kv_heads, (n + qb - 1) / qb);
+    g_kernel_launches++;
     if (head_dim == 64)
         k_attention_flash<64><<<grid, FLASH_THREADS, 0, st>>>(q, k_cache, v_cache, out, n, start_pos, n_heads, n_kv_heads);
     else if (head_dim == 32)

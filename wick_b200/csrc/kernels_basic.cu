@@ -3,24 +3,38 @@
 
 namespace wick {
 
+thread_local unsigned long long g_kernel_launches = 0;
+
 // ── weight re-layout ───────────────────────────────────────────────────────
 // GGUF block = f16 d followed by 16 (Q4_0) or 32 (Q8_0) quant bytes, 18 / 34 bytes,
-// only 2-byte aligned (wick/src/quant.rs:13-34).  One thread moves one block.
-__global__ void k_repack(int dtype, const uint8_t* __restrict__ raw, uint8_t* __restrict__ q, __half* __restrict__ d,
-                         size_t n_blocks) {
-    size_t b = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (b >= n_blocks) return;
-    const int qb = dtype == DT_Q4_0 ? 16 : 32;
-    const uint16_t* src = reinterpret_cast<const uint16_t*>(raw + b * (size_t)(qb + 2));
-    reinterpret_cast<uint16_t*>(d)[b] = src[0];
-    uint16_t* dst = reinterpret_cast<uint16_t*>(q + b * (size_t)qb);
-    for (int i = 0; i < qb / 2; i++) dst[i] = src[1 + i];
+// only 2-byte aligned (wick/src/quant.rs:13-34).  One thread moves one block of one row into
+// the grouped layout described at DevWeight.  The planes are zero-filled first (padding rows).
+__global__ void k_repack(DevWeight w, const uint8_t* __restrict__ raw, uint8_t* __restrict__ q, __half* __restrict__ d) {
+    const int nb = w.k / QK;
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)w.m * nb) return;
+    const int row = (int)(idx / nb), b = (int)(idx % nb);
+    const int g = row >> 2, r = row & 3;
+    const int qb = w.dtype == DT_Q4_0 ? 16 : 32;
+    const uint16_t* src = reinterpret_cast<const uint16_t*>(raw + idx * (size_t)(qb + 2));
+    reinterpret_cast<uint16_t*>(d)[(size_t)g * nb * 4 + b * 4 + r] = src[0];
+    uint16_t* qg = reinterpret_cast<uint16_t*>(q + (size_t)g * w.q_group_bytes());
+    if (w.dtype == DT_Q4_0) {
+        for (int i = 0; i < 8; i++) qg[q4_word(b, r, 0) * 2 + i] = src[1 + i];
+    } else {
+        for (int i = 0; i < 8; i++) qg[q8_word(b, 0, r, 0) * 2 + i] = src[1 + i];
+        for (int i = 0; i < 8; i++) qg[q8_word(b, 1, r, 0) * 2 + i] = src[9 + i];
+    }
 }
 
-void launch_repack(cudaStream_t st, int dtype, const uint8_t* raw, uint8_t* q, __half* d, size_t n_blocks) {
+void launch_repack(cudaStream_t st, const DevWeight& w, const uint8_t* raw, uint8_t* q, __half* d) {
+    size_t n_blocks = (size_t)w.m * (w.k / QK);
     if (!n_blocks) return;
+    cudaMemsetAsync(q, 0, w.q_bytes(), st);
+    cudaMemsetAsync(d, 0, w.d_bytes(), st);
     unsigned grid = (unsigned)((n_blocks + 255) / 256);
-    k_repack<<<grid, 256, 0, st>>>(dtype, raw, q, d, n_blocks);
+    g_kernel_launches++;
+    k_repack<<<grid, 256, 0, st>>>(w, raw, q, d);
 }
 
 // ── embedding ──────────────────────────────────────────────────────────────
@@ -30,22 +44,25 @@ __global__ void k_embed(DevWeight w, const uint32_t* __restrict__ tokens, const 
     uint32_t tok = tokens ? tokens[j] : ctl->token;
     if (tok >= (uint32_t)w.m) tok = 0;  // host validates ids; never index outside the table
     const int k = w.k, nb = k / QK;
-    const __half* dr = w.d + (size_t)tok * nb;
+    const int g = tok >> 2, r = tok & 3;
+    const __half* dg = w.d + (size_t)g * nb * 4;
+    const uint8_t* qg = w.q + (size_t)g * w.q_group_bytes();
     for (int e = threadIdx.x; e < k; e += blockDim.x) {
         int b = e >> 5, i = e & 31;
-        float d = __half2float(dr[b]);
+        float d = __half2float(dg[b * 4 + r]);
         int v;
         if (w.dtype == DT_Q4_0) {
-            uint8_t byte = w.q[(size_t)tok * (k / 2) + b * 16 + (i & 15)];
+            uint8_t byte = qg[q4_word(b, r, 0) * 4 + (i & 15)];
             v = (int)(i < 16 ? (byte & 0x0F) : (byte >> 4)) - 8;
         } else {
-            v = (int)((const int8_t*)w.q)[(size_t)tok * k + e];
+            v = (int)((const int8_t*)qg)[q8_word(b, i >> 4, r, 0) * 4 + (i & 15)];
         }
         out[(size_t)j * k + e] = __fmul_rn((float)v, d);
     }
 }
 
 void launch_embed(cudaStream_t st, const DevWeight& w, const uint32_t* tokens, const DecodeCtl* ctl, float* out, int n) {
+    g_kernel_launches++;
     k_embed<<<n, 256, 0, st>>>(w, tokens, ctl, out);
 }
 
@@ -87,6 +104,7 @@ __global__ void __launch_bounds__(256) k_add_rmsnorm_quant(float* __restrict__ h
 
 void launch_add_rmsnorm_quant(cudaStream_t st, float* hidden, const float* add, const float* weight, float eps, int n,
                               int dim, float* q8s, int8_t* q8q, float* normed_out) {
+    g_kernel_launches++;
     k_add_rmsnorm_quant<<<n, 256, dim * sizeof(float), st>>>(hidden, add, weight, eps, dim, q8s, q8q, normed_out);
 }
 
@@ -100,6 +118,7 @@ __global__ void __launch_bounds__(256) k_rmsnorm_generic(float* __restrict__ x, 
 }
 
 void launch_rmsnorm(cudaStream_t st, float* x, const float* weight, int n, int dim, float eps) {
+    g_kernel_launches++;
     k_rmsnorm_generic<<<n, 256, 0, st>>>(x, weight, dim, eps);
 }
 
@@ -119,6 +138,7 @@ void launch_quant_rows(cudaStream_t st, const float* x, int n, int k, float* q8s
     size_t total = (size_t)n * (k / QK);
     if (!total) return;
     unsigned grid = (unsigned)((total * 32 + 255) / 256);
+    g_kernel_launches++;
     k_quant_rows<<<grid, 256, 0, st>>>(x, total, q8s, q8q);
 }
 
@@ -142,6 +162,7 @@ void launch_silu_mul_quant(cudaStream_t st, const float* gate, const float* up, 
     size_t total = (size_t)n * (dim / QK);
     if (!total) return;
     unsigned grid = (unsigned)((total * 32 + 255) / 256);
+    g_kernel_launches++;
     k_silu_mul_quant<<<grid, 256, 0, st>>>(gate, up, total, q8s, q8q, act_out);
 }
 
@@ -151,6 +172,7 @@ __global__ void k_silu_mul(float* __restrict__ gate, const float* __restrict__ u
 }
 void launch_silu_mul(cudaStream_t st, float* gate, const float* up, size_t count) {
     if (!count) return;
+    g_kernel_launches++;
     k_silu_mul<<<(unsigned)((count + 255) / 256), 256, 0, st>>>(gate, up, count);
 }
 __global__ void k_expf(const float* __restrict__ x, float* __restrict__ y, size_t count) {
@@ -159,6 +181,7 @@ __global__ void k_expf(const float* __restrict__ x, float* __restrict__ y, size_
 }
 void launch_expf(cudaStream_t st, const float* x, float* y, size_t count) {
     if (!count) return;
+    g_kernel_launches++;
     k_expf<<<(unsigned)((count + 255) / 256), 256, 0, st>>>(x, y, count);
 }
 
@@ -227,8 +250,9 @@ void launch_shortconv(cudaStream_t st, const float* proj, const float* conv_w, f
                       float* out, float* q8s, int8_t* q8q) {
     size_t warps = (size_t)n * (hs / QK);
     if (!warps) return;
+    g_kernel_launches++;
     k_shortconv<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, st>>>(proj, conv_w, state, n, hs, ks, out, q8s, q8q);
-    if (ks > 1) k_shortconv_state<<<(hs + 255) / 256, 256, 0, st>>>(proj, state, n, hs, ks);
+    if (ks > 1) g_kernel_launches++, k_shortconv_state<<<(hs + 255) / 256, 256, 0, st>>>(proj, state, n, hs, ks);
 }
 
 // ── per-head QK RMSNorm + RoPE + KV append ─────────────────────────────────
@@ -280,6 +304,7 @@ void launch_qknorm_rope_kv(cudaStream_t st, float* q, const float* k, const floa
                            float* v_cache, int n, int start_pos, const DecodeCtl* ctl, int n_heads, int n_kv_heads,
                            int head_dim) {
     dim3 grid(n, n_heads + n_kv_heads);
+    g_kernel_launches++;
     k_qknorm_rope_kv<<<grid, 32, 0, st>>>(q, k, v, q_norm, k_norm, eps, rope_cos, rope_sin, k_cache, v_cache, start_pos,
                                           ctl, n_heads, n_kv_heads, head_dim);
 }
@@ -296,6 +321,7 @@ __global__ void k_rope(float* __restrict__ q, float* __restrict__ k, const float
 }
 void launch_rope(cudaStream_t st, float* q, float* k, const float* cos_row, const float* sin_row, int n_heads,
                  int n_kv_heads, int head_dim) {
+    g_kernel_launches++;
     k_rope<<<n_heads + n_kv_heads, 32, 0, st>>>(q, k, cos_row, sin_row, n_heads, head_dim);
 }
 
@@ -321,7 +347,9 @@ void launch_argmax(cudaStream_t st, const float* logits, int count, unsigned lon
     int grid = (count + 1023) / 1024;
     if (grid > 148) grid = 148;
     if (grid < 1) grid = 1;
+    g_kernel_launches++;
     k_argmax_partial<<<grid, 256, 0, st>>>(logits, count, scratch);
+    g_kernel_launches++;
     k_argmax_finish<<<1, 1, 0, st>>>(scratch, out);
 }
 
@@ -334,6 +362,7 @@ __global__ void k_decode_advance(DecodeCtl* __restrict__ ctl, const uint32_t* __
     ctl->step += 1;
 }
 void launch_decode_advance(cudaStream_t st, DecodeCtl* ctl, const uint32_t* argmax_tok, uint32_t* ring, int ring_len) {
+    g_kernel_launches++;
     k_decode_advance<<<1, 1, 0, st>>>(ctl, argmax_tok, ring, ring_len);
 }
 

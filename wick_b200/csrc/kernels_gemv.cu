@@ -24,39 +24,45 @@ __device__ __forceinline__ int lane_sum_q8(int w_lo, int w_hi, int x_lo, int x_h
     return __dp4a(w_hi, x_hi, __dp4a(w_lo, x_lo, 0));
 }
 
-// vaddvq_f32(sumv0) + vaddvq_f32(sumv1) across the 8 threads of a row (lane bits: l = 0..1,
-// parity = bit 2).  IEEE addition is commutative, so every thread ends with the same value.
+// Lane layout of a warp that owns one 4-row group: lane = p*16 + r*4 + l (parity, row in
+// group, word) -- the word order of the grouped weight layout (DevWeight).
+// vaddvq_f32(sumv0) + vaddvq_f32(sumv1) across the 8 chains of a row: lane^1, lane^2 give
+// (l0+l1)+(l2+l3), lane^16 adds the other parity.  IEEE addition is commutative, so every
+// thread of the row ends with the same value.
 __device__ __forceinline__ float reduce_row8(float a) {
     a = __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, 1));
     a = __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, 2));
-    a = __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, 4));
+    a = __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, 16));
     return a;
 }
 
-// ── GEMV: 256 threads = 32 rows x 8 chains; x staged in shared memory ───────
-constexpr int GEMV_ROWS = 32;
+// ── GEMV: 8 warps = 8 row groups per CTA; x staged in shared memory ─────────
+constexpr int GEMV_GROUPS = 8;
 
+// One chain (p, r, l) of group `g` over the blocks of its parity.
 template <int DT>
-__device__ __forceinline__ float gemv_chain(const DevWeight& w, int row, int p, int l, const int* __restrict__ xq32,
+__device__ __forceinline__ float gemv_chain(const DevWeight& w, int g, int lane, const int* __restrict__ xq32,
                                             const float* __restrict__ xs) {
     const int nb = w.k / QK;
-    const __half* dr = w.d + (size_t)row * nb;
+    const int p = lane >> 4, r = (lane >> 2) & 3, l = lane & 3;
+    const __half* dg = w.d + (size_t)g * nb * 4 + r;
+    const uint32_t* qg = reinterpret_cast<const uint32_t*>(w.q + (size_t)g * w.q_group_bytes());
     float acc = 0.0f;
     if (DT == DT_Q4_0) {
-        const uint32_t* qr = reinterpret_cast<const uint32_t*>(w.q + (size_t)row * (w.k / 2));
+        const uint32_t* qp = qg + (lane & 15);
 #pragma unroll 4
         for (int b = p; b < nb; b += 2) {
-            uint32_t ww = __ldg(qr + b * 4 + l);
-            float d = __fmul_rn(__half2float(__ldg(dr + b)), xs[b]);
+            uint32_t ww = __ldg(qp + b * 16);
+            float d = __fmul_rn(__half2float(__ldg(dg + b * 4)), xs[b]);
             int s = lane_sum_q4(ww, xq32[b * 8 + l], xq32[b * 8 + 4 + l]);
             acc = __fadd_rn(acc, __fmul_rn((float)s, d));
         }
     } else {
-        const int* qr = reinterpret_cast<const int*>(w.q + (size_t)row * w.k);
+        const uint32_t* qp = qg + lane;  // p*16 + r*4 + l inside a block pair's half
 #pragma unroll 4
         for (int b = p; b < nb; b += 2) {
-            int w_lo = __ldg(qr + b * 8 + l), w_hi = __ldg(qr + b * 8 + 4 + l);
-            float d = __fmul_rn(__half2float(__ldg(dr + b)), xs[b]);
+            int w_lo = (int)__ldg(qp + (b >> 1) * 64), w_hi = (int)__ldg(qp + (b >> 1) * 64 + 32);
+            float d = __fmul_rn(__half2float(__ldg(dg + b * 4)), xs[b]);
             int s = lane_sum_q8(w_lo, w_hi, xq32[b * 8 + l], xq32[b * 8 + 4 + l]);
             acc = __fadd_rn(acc, __fmul_rn((float)s, d));
         }
@@ -75,31 +81,29 @@ __global__ void __launch_bounds__(256) k_gemv(GemvJob job, const float* __restri
     for (int i = threadIdx.x; i < nb; i += blockDim.x) xs[i] = xs_g[i];
     __syncthreads();
 
-    int row = blockIdx.x * GEMV_ROWS + (threadIdx.x >> 3);
-    const int p = (threadIdx.x >> 2) & 1, l = threadIdx.x & 3;
+    const int lane = threadIdx.x & 31;
+    int g = blockIdx.x * GEMV_GROUPS + (threadIdx.x >> 5);
     int mi = 0;
-    while (mi < job.count && row >= job.w[mi].m) {
-        row -= job.w[mi].m;
+    while (mi < job.count && g >= (job.w[mi].m + 3) / 4) {
+        g -= (job.w[mi].m + 3) / 4;
         mi++;
     }
-    // rows of one 8-thread group always fall in the same matrix: shuffles stay convergent
-    const bool valid = mi < job.count;
-    float acc = 0.0f;
-    if (valid) {
-        const DevWeight& w = job.w[mi];
-        acc = w.dtype == DT_Q4_0 ? gemv_chain<DT_Q4_0>(w, row, p, l, xq32, xs) : gemv_chain<DT_Q8_0>(w, row, p, l, xq32, xs);
-    }
+    if (mi >= job.count) return;  // whole warp leaves together
+    const DevWeight& w = job.w[mi];
+    float acc = w.dtype == DT_Q4_0 ? gemv_chain<DT_Q4_0>(w, g, lane, xq32, xs) : gemv_chain<DT_Q8_0>(w, g, lane, xq32, xs);
     acc = reduce_row8(acc);
-    if (valid && (threadIdx.x & 7) == 0) job.y[mi][row] = acc;
+    const int row = g * 4 + ((lane >> 2) & 3);
+    if ((lane & 19) == 0 && row < w.m) job.y[mi][row] = acc;
 }
 
 void launch_gemv(cudaStream_t st, const GemvJob& job, const float* xs, const int8_t* xq) {
-    int rows = 0;
-    for (int i = 0; i < job.count; i++) rows += job.w[i].m;
-    if (!rows) return;
+    int groups = 0;
+    for (int i = 0; i < job.count; i++) groups += (job.w[i].m + 3) / 4;
+    if (!groups) return;
     const int k = job.w[0].k;
     size_t smem = (size_t)k + (size_t)(k / QK) * 4;
-    k_gemv<<<(rows + GEMV_ROWS - 1) / GEMV_ROWS, 256, smem, st>>>(job, xs, xq);
+    g_kernel_launches++;
+    k_gemv<<<(groups + GEMV_GROUPS - 1) / GEMV_GROUPS, 256, smem, st>>>(job, xs, xq);
 }
 
 // ── block sums (parity tap) ────────────────────────────────────────────────
@@ -108,26 +112,27 @@ __global__ void k_block_sums(DevWeight w, const int8_t* __restrict__ xq, int32_t
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (size_t)w.m * nb) return;
     int row = (int)(idx / nb), b = (int)(idx % nb);
+    const int g = row >> 2, r = row & 3;
     const int* x32 = reinterpret_cast<const int*>(xq) + b * 8;
+    const uint32_t* qg = reinterpret_cast<const uint32_t*>(w.q + (size_t)g * w.q_group_bytes());
     int s = 0;
     if (w.dtype == DT_Q4_0) {
-        const uint32_t* qr = reinterpret_cast<const uint32_t*>(w.q + (size_t)row * (w.k / 2)) + b * 4;
-        for (int l = 0; l < 4; l++) s += lane_sum_q4(qr[l], x32[l], x32[4 + l]);
+        for (int l = 0; l < 4; l++) s += lane_sum_q4(qg[q4_word(b, r, l)], x32[l], x32[4 + l]);
     } else {
-        const int* qr = reinterpret_cast<const int*>(w.q + (size_t)row * w.k) + b * 8;
-        for (int l = 0; l < 4; l++) s += lane_sum_q8(qr[l], qr[4 + l], x32[l], x32[4 + l]);
+        for (int l = 0; l < 4; l++) s += lane_sum_q8((int)qg[q8_word(b, 0, r, l)], (int)qg[q8_word(b, 1, r, l)], x32[l], x32[4 + l]);
     }
     S[idx] = s;
 }
 void launch_block_sums(cudaStream_t st, const DevWeight& w, const int8_t* xq, int32_t* S) {
     size_t total = (size_t)w.m * (w.k / QK);
     if (!total) return;
+    g_kernel_launches++;
     k_block_sums<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(w, xq, S);
 }
 
 // ── GEMM over n quantised tokens ───────────────────────────────────────────
-// Same chains, TJ tokens per CTA sharing each weight word.  256 threads = 32 rows x
-// 8 chains; every thread keeps TJ accumulators.  Activation words are staged transposed,
+// Same chains, TJ tokens per CTA sharing each weight word.  256 threads = 8 warps = 8 row
+// groups (32 rows) x 8 chains; every thread keeps TJ accumulators.  Activation words are staged transposed,
 // xt[(b*8 + word)][token], so one 128-bit shared load feeds four tokens.  K is walked in
 // chunks of KC blocks so the staging buffer stays small; chains continue across chunks.
 constexpr int GEMM_ROWS = 32;
@@ -142,13 +147,14 @@ __global__ void __launch_bounds__(256) k_gemm(DevWeight w, const float* __restri
     __shared__ __align__(16) float st[KC * TJP];
     const int k = w.k, nb = k / QK, m = w.m;
     const int j0 = blockIdx.y * TJ;
-    const int rloc = threadIdx.x >> 3, p = (threadIdx.x >> 2) & 1, l = threadIdx.x & 3;
-    const int row = blockIdx.x * GEMM_ROWS + rloc;
+    const int lane = threadIdx.x & 31;
+    const int p = lane >> 4, r = (lane >> 2) & 3, l = lane & 3;
+    int g = blockIdx.x * (GEMM_ROWS / 4) + (threadIdx.x >> 5);
+    const int row = g * 4 + r;
     const bool rvalid = row < m;
-    const int rr = rvalid ? row : 0;
-    const __half* dr = w.d + (size_t)rr * nb;
-    const uint32_t* q4 = reinterpret_cast<const uint32_t*>(w.q + (size_t)rr * (k / 2));
-    const int* q8 = reinterpret_cast<const int*>(w.q + (size_t)rr * (DT == DT_Q8_0 ? k : 0));
+    if (g >= w.groups()) g = 0;  // keep the warp in the barriers below; results are not stored
+    const __half* dr = w.d + (size_t)g * nb * 4 + r;
+    const uint32_t* qg = reinterpret_cast<const uint32_t*>(w.q + (size_t)g * w.q_group_bytes());
 
     float acc[TJ];
 #pragma unroll
@@ -174,11 +180,11 @@ __global__ void __launch_bounds__(256) k_gemm(DevWeight w, const float* __restri
         // chain parity is that of the global block index
         for (int bi = (p - (b0 & 1)) & 1; bi < nbc; bi += 2) {
             const int b = b0 + bi;
-            const float dw = __half2float(__ldg(dr + b));
+            const float dw = __half2float(__ldg(dr + b * 4));
             uint32_t ww = 0;
             int w_lo = 0, w_hi = 0;
-            if (DT == DT_Q4_0) ww = __ldg(q4 + b * 4 + l);
-            else { w_lo = __ldg(q8 + b * 8 + l); w_hi = __ldg(q8 + b * 8 + 4 + l); }
+            if (DT == DT_Q4_0) ww = __ldg(qg + q4_word(b, r, l));
+            else { w_lo = (int)__ldg(qg + q8_word(b, 0, r, l)); w_hi = (int)__ldg(qg + q8_word(b, 1, r, l)); }
             const int4* xlo = reinterpret_cast<const int4*>(xt + (bi * 8 + l) * TJP);
             const int4* xhi = reinterpret_cast<const int4*>(xt + (bi * 8 + 4 + l) * TJP);
             const float4* sx = reinterpret_cast<const float4*>(st + bi * TJP);
@@ -201,20 +207,20 @@ __global__ void __launch_bounds__(256) k_gemm(DevWeight w, const float* __restri
             }
         }
     }
-    const int sub = threadIdx.x & 7;
+    const int sub = (lane & 3) | ((lane >> 2) & 4);  // 0..7 over the row's eight chains
 #pragma unroll
     for (int t = 0; t < TJ; t++) {
-        float r = reduce_row8(acc[t]);
+        float v = reduce_row8(acc[t]);
         int j = j0 + t;
-        if ((t & 7) == sub && rvalid && j < n) out[(size_t)j * m + row] = r;
+        if ((t & 7) == sub && rvalid && j < n) out[(size_t)j * m + row] = v;
     }
 }
 
 void launch_gemm(cudaStream_t st, const DevWeight& w, const float* bs, const int8_t* bq, int n, float* out) {
     if (!n || !w.m) return;
     dim3 grid((w.m + GEMM_ROWS - 1) / GEMM_ROWS, (n + TJ - 1) / TJ);
-    if (w.dtype == DT_Q4_0) k_gemm<DT_Q4_0><<<grid, 256, 0, st>>>(w, bs, bq, n, out);
-    else k_gemm<DT_Q8_0><<<grid, 256, 0, st>>>(w, bs, bq, n, out);
+    if (w.dtype == DT_Q4_0) g_kernel_launches++, k_gemm<DT_Q4_0><<<grid, 256, 0, st>>>(w, bs, bq, n, out);
+    else g_kernel_launches++, k_gemm<DT_Q8_0><<<grid, 256, 0, st>>>(w, bs, bq, n, out);
 }
 
 }  // namespace wick

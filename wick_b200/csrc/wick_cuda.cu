@@ -80,6 +80,9 @@ struct wick_cuda_model {
     uint32_t* h_u32 = nullptr;   // [ring_len] tokens in / out
     float* h_logits = nullptr;   // [vocab]
     cudaGraphExec_t g_logits = nullptr, g_greedy = nullptr;
+    uint64_t nodes_logits = 0, nodes_greedy = 0;  // kernels per graph replay
+    uint64_t launches = 0;                        // kernels launched so far
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;     // bracket the GPU work of the last call
     uint32_t seq_len = 0;
     uint64_t bytes = 0;
     std::vector<void*> allocs;
@@ -89,6 +92,8 @@ struct wick_cuda_model {
         if (stream) cudaStreamSynchronize(stream);
         if (g_logits) cudaGraphExecDestroy(g_logits);
         if (g_greedy) cudaGraphExecDestroy(g_greedy);
+        if (ev0) cudaEventDestroy(ev0);
+        if (ev1) cudaEventDestroy(ev1);
         for (void* p : allocs) cudaFree(p);
         if (h_u32) cudaFreeHost(h_u32);
         if (h_logits) cudaFreeHost(h_logits);
@@ -130,12 +135,12 @@ int32_t upload_f32(wick_cuda_model* m, const GgufImage& g, const std::string& na
 }
 
 // Uploads GGUF block rows and re-lays them out into planes (see DevWeight).
-int32_t upload_weight_raw(int dtype, const uint8_t* raw_host, int mrows, int k, uint8_t* staging, cudaStream_t st,
-                          uint8_t* q_dev, __half* d_dev) {
-    size_t nblk = (size_t)mrows * (k / QK);
-    size_t raw_bytes = nblk * (dtype == DT_Q4_0 ? 18 : 34);
+int32_t upload_weight_raw(const DevWeight& w, const uint8_t* raw_host, uint8_t* staging, cudaStream_t st, uint8_t* q_dev,
+                          __half* d_dev) {
+    size_t nblk = (size_t)w.m * (w.k / QK);
+    size_t raw_bytes = nblk * (w.dtype == DT_Q4_0 ? 18 : 34);
     CU_TRY(cudaMemcpyAsync(staging, raw_host, raw_bytes, cudaMemcpyHostToDevice, st));
-    launch_repack(st, dtype, staging, q_dev, d_dev, nblk);
+    launch_repack(st, w, staging, q_dev, d_dev);
     CU_TRY(cudaGetLastError());
     CU_TRY(cudaStreamSynchronize(st));
     return WICK_CUDA_OK;
@@ -162,7 +167,7 @@ int32_t upload_weight(wick_cuda_model* m, const GgufImage& g, const std::string&
     __half* d = nullptr;
     W_TRY(dev_alloc(m, &q, w.q_bytes()));
     W_TRY(dev_alloc(m, &d, w.d_bytes() / 2));
-    W_TRY(upload_weight_raw(w.dtype, g.data() + t->offset, rows, k, staging, m->stream, q, d));
+    W_TRY(upload_weight_raw(w, g.data() + t->offset, staging, m->stream, q, d));
     w.q = q;
     w.d = d;
     *out = w;
@@ -246,10 +251,12 @@ void enqueue_decode(wick_cuda_model* m, bool greedy) {
     }
 }
 
-int32_t capture_graph(wick_cuda_model* m, bool greedy, cudaGraphExec_t* out) {
+int32_t capture_graph(wick_cuda_model* m, bool greedy, cudaGraphExec_t* out, uint64_t* nodes) {
     cudaGraph_t graph = nullptr;
     CU_TRY(cudaStreamBeginCapture(m->stream, cudaStreamCaptureModeThreadLocal));
+    const unsigned long long before = g_kernel_launches;
     enqueue_decode(m, greedy);
+    *nodes = g_kernel_launches - before;
     cudaError_t e = cudaStreamEndCapture(m->stream, &graph);
     if (e != cudaSuccess) return fail(WICK_CUDA_ERR_CUDA, std::string("graph capture: ") + cudaGetErrorString(e));
     e = cudaGraphInstantiate(out, graph, 0);
@@ -447,8 +454,10 @@ int32_t build_model(wick_cuda_model* m, const GgufImage& g, uint32_t context_siz
     if (naive_attn_smem(m) > 48 * 1024) {
         configure_naive_attention_smem(naive_attn_smem(m));
     }
-    W_TRY(capture_graph(m, false, &m->g_logits));
-    W_TRY(capture_graph(m, true, &m->g_greedy));
+    CU_TRY(cudaEventCreate(&m->ev0));
+    CU_TRY(cudaEventCreate(&m->ev1));
+    W_TRY(capture_graph(m, false, &m->g_logits, &m->nodes_logits));
+    W_TRY(capture_graph(m, true, &m->g_greedy, &m->nodes_greedy));
     CU_TRY(cudaStreamSynchronize(m->stream));
     return WICK_CUDA_OK;
 }
@@ -551,9 +560,12 @@ int32_t wick_cuda_forward(wick_cuda_model* m, uint32_t token, uint32_t pos, floa
     W_TRY(pre_step(m, token, pos));
     if (!logits_host) return fail(WICK_CUDA_ERR_BAD_ARG, "logits_host is NULL");
     m->h_u32[0] = token;
+    CU_TRY(cudaEventRecord(m->ev0, m->stream));
     CU_TRY(cudaMemcpyAsync(&m->ctl->token, m->h_u32, 4, cudaMemcpyHostToDevice, m->stream));
     CU_TRY(cudaGraphLaunch(m->g_logits, m->stream));
+    m->launches += m->nodes_logits;
     CU_TRY(cudaMemcpyAsync(m->h_logits, m->logits, (size_t)m->cfg.vocab_size * 4, cudaMemcpyDeviceToHost, m->stream));
+    CU_TRY(cudaEventRecord(m->ev1, m->stream));
     CU_TRY(cudaStreamSynchronize(m->stream));
     memcpy(logits_host, m->h_logits, (size_t)m->cfg.vocab_size * 4);
     m->seq_len += 1;
@@ -564,9 +576,12 @@ int32_t wick_cuda_forward_greedy(wick_cuda_model* m, uint32_t token, uint32_t po
     W_TRY(pre_step(m, token, pos));
     if (!next_token) return fail(WICK_CUDA_ERR_BAD_ARG, "next_token is NULL");
     m->h_u32[0] = token;
+    CU_TRY(cudaEventRecord(m->ev0, m->stream));
     CU_TRY(cudaMemcpyAsync(&m->ctl->token, m->h_u32, 4, cudaMemcpyHostToDevice, m->stream));
     CU_TRY(cudaGraphLaunch(m->g_greedy, m->stream));
+    m->launches += m->nodes_greedy;
     CU_TRY(cudaMemcpyAsync(m->h_u32 + 1, m->argmax_tok, 4, cudaMemcpyDeviceToHost, m->stream));
+    CU_TRY(cudaEventRecord(m->ev1, m->stream));
     CU_TRY(cudaStreamSynchronize(m->stream));
     *next_token = m->h_u32[1];
     m->seq_len += 1;
@@ -583,9 +598,12 @@ int32_t wick_cuda_generate_greedy(wick_cuda_model* m, uint32_t first_token, uint
     // token and ring cursor for this run
     uint32_t init[3] = {first_token, m->seq_len, 0};
     memcpy(m->h_u32, init, sizeof(init));
+    CU_TRY(cudaEventRecord(m->ev0, m->stream));
     CU_TRY(cudaMemcpyAsync(m->ctl, m->h_u32, sizeof(init), cudaMemcpyHostToDevice, m->stream));
     for (uint32_t i = 0; i < n_steps; i++) CU_TRY(cudaGraphLaunch(m->g_greedy, m->stream));
+    m->launches += m->nodes_greedy * n_steps;
     CU_TRY(cudaMemcpyAsync(m->h_u32, m->ring, (size_t)n_steps * 4, cudaMemcpyDeviceToHost, m->stream));
+    CU_TRY(cudaEventRecord(m->ev1, m->stream));
     CU_TRY(cudaStreamSynchronize(m->stream));
     memcpy(out_tokens_host, m->h_u32, (size_t)n_steps * 4);
     m->seq_len += n_steps;
@@ -609,11 +627,14 @@ int32_t wick_cuda_forward_prefill(wick_cuda_model* m, const uint32_t* tokens_hos
     CU_TRY(cudaSetDevice(m->device));
     if (start_pos == 0) W_TRY(reset_sequence(m));  // new sequence, metal_lfm2.rs:2361-2397
     const bool flash = n >= 256;  // FLASH_ATTN_THRESHOLD, lfm2.rs:1646-1647
+    CU_TRY(cudaEventRecord(m->ev0, m->stream));
     for (uint32_t c0 = 0; c0 < n; c0 += m->max_chunk) {
         uint32_t cn = std::min<uint32_t>(m->max_chunk, n - c0);
         memcpy(m->h_u32, tokens_host + c0, (size_t)cn * 4);
         CU_TRY(cudaMemcpyAsync(m->tokens_dev, m->h_u32, (size_t)cn * 4, cudaMemcpyHostToDevice, m->stream));
+        const unsigned long long before = g_kernel_launches;
         enqueue_prefill_chunk(m, (int)cn, (int)(start_pos + c0), flash, c0 + cn == n);
+        m->launches += g_kernel_launches - before;
         CU_TRY(cudaGetLastError());
         CU_TRY(cudaStreamSynchronize(m->stream));  // h_u32 is reused by the next chunk
     }
@@ -621,6 +642,7 @@ int32_t wick_cuda_forward_prefill(wick_cuda_model* m, const uint32_t* tokens_hos
     memcpy(m->h_u32, newpos, 8);
     CU_TRY(cudaMemcpyAsync(&m->ctl->pos, m->h_u32 + 1, 4, cudaMemcpyHostToDevice, m->stream));
     CU_TRY(cudaMemcpyAsync(m->h_logits, m->logits, (size_t)m->cfg.vocab_size * 4, cudaMemcpyDeviceToHost, m->stream));
+    CU_TRY(cudaEventRecord(m->ev1, m->stream));
     CU_TRY(cudaStreamSynchronize(m->stream));
     memcpy(logits_host, m->h_logits, (size_t)m->cfg.vocab_size * 4);
     m->seq_len = start_pos + n;
@@ -719,6 +741,22 @@ int32_t wick_cuda_restore(wick_cuda_model* m, const uint8_t* snap_host, uint64_t
     return WICK_CUDA_OK;
 }
 
+int32_t wick_cuda_last_elapsed_ms(wick_cuda_model* m, float* ms) {
+    W_TRY(check_model(m));
+    if (!ms) return fail(WICK_CUDA_ERR_BAD_ARG, "ms is NULL");
+    CU_TRY(cudaSetDevice(m->device));
+    CU_TRY(cudaEventSynchronize(m->ev1));
+    CU_TRY(cudaEventElapsedTime(ms, m->ev0, m->ev1));
+    return WICK_CUDA_OK;
+}
+
+int32_t wick_cuda_kernel_launches(const wick_cuda_model* m, uint64_t* count) {
+    W_TRY(check_model(m));
+    if (!count) return fail(WICK_CUDA_ERR_BAD_ARG, "count is NULL");
+    *count = m->launches;
+    return WICK_CUDA_OK;
+}
+
 int32_t wick_cuda_read_kv(wick_cuda_model* m, uint32_t layer, float* k_host, float* v_host) {
     W_TRY(check_model(m));
     if (layer >= m->layers.size() || !m->layers[layer].is_attn) return fail(WICK_CUDA_ERR_BAD_ARG, "not an attention layer");
@@ -761,7 +799,7 @@ int32_t wick_cuda_weight_create(int32_t dtype, const uint8_t* raw_host, uint32_t
     cudaError_t e2 = cudaMalloc((void**)&d, std::max<size_t>(w->w.d_bytes(), 256));
     int32_t r = WICK_CUDA_OK;
     if (e1 != cudaSuccess || e2 != cudaSuccess) r = fail(WICK_CUDA_ERR_OOM, "cudaMalloc failed for weight planes");
-    if (r == WICK_CUDA_OK) r = upload_weight_raw(dtype, raw_host, (int)mrows, (int)k, staging, nullptr, q, d);
+    if (r == WICK_CUDA_OK) r = upload_weight_raw(w->w, raw_host, staging, nullptr, q, d);
     cudaFree(staging);
     if (r != WICK_CUDA_OK) {
         cudaFree(q);

@@ -201,6 +201,18 @@ class CudaLfm2Model:
         check(self._lib.wick_cuda_seq_len(self._h, C.byref(v)))
         return v.value
 
+    def last_elapsed_ms(self) -> float:
+        """Device time of the GPU work of the last forward* / generate call (CUDA events on the
+        model's stream), cf. wick's GpuTimer (metal_lfm2.rs:3922-3984)."""
+        v = C.c_float(0)
+        check(self._lib.wick_cuda_last_elapsed_ms(self._h, C.byref(v)))
+        return v.value
+
+    def kernel_launches(self) -> int:
+        v = C.c_uint64(0)
+        check(self._lib.wick_cuda_kernel_launches(self._h, C.byref(v)))
+        return v.value
+
     def read_kv(self, layer: int) -> Tuple[np.ndarray, np.ndarray]:
         kv_dim = self._config.kv_heads_per_layer[layer] * (self._config.hidden_size // self._config.n_heads)
         rows = self.seq_len
