@@ -131,6 +131,15 @@ int32_t wick_cuda_restore(wick_cuda_model* m, const uint8_t* snap_host, uint64_t
 int32_t wick_cuda_last_elapsed_ms(wick_cuda_model* m, float* ms);
 int32_t wick_cuda_kernel_launches(const wick_cuda_model* m, uint64_t* count);
 
+/* Test hook for the bounded waits of the persistent decode kernel: shifts the barrier sequence
+ * number the NEXT decode call waits for by `delta` arrivals, so that its grid-wide waits expire
+ * (about a second) and the call returns WICK_CUDA_ERR_TIMEOUT with the device context intact.
+ * Returns WICK_CUDA_ERR_BAD_ARG when the model decodes through captured graphs instead. */
+int32_t wick_cuda_debug_skew_barrier(wick_cuda_model* m, int64_t delta);
+/* 1 if decode steps run in the persistent kernel, 0 if through the captured per-kernel graph
+ * (models whose row length is not a multiple of 64, or WICK_CUDA_DECODE=graph in the environment). */
+int32_t wick_cuda_decode_path(const wick_cuda_model* m, int32_t* persistent);
+
 /* Debug / parity taps: f32 K and V rows [0, seq_len) x kv_dim of an attention layer
  * (LayerState::Attention, kv_cache.rs:62-70) or the [d_conv][hidden] rolling buffer of a conv
  * layer (LayerState::Conv, kv_cache.rs:72-74). */

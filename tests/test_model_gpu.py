@@ -221,3 +221,53 @@ def test_350m_prefill_equals_sequential_decode(wick, orc, model_dir, qtype):
     want = om.generate_greedy(first, 8)
     got = m.generate_greedy(first, 8, st)
     assert list(want) == list(got)
+
+
+def test_persistent_and_graph_decode_agree(wick, orc, model_dir, monkeypatch):
+    """The persistent decode kernel and the captured per-kernel graph are two schedules of the same
+    arithmetic: identical logits, KV rows and greedy tokens (and both equal the oracle)."""
+    from wick_b200 import gguf_synth as gs
+    path = _model_path(model_dir, "tiny-wide", "q4_0", norm_jitter=0.2, weight_std=0.05)
+    a = wick.CudaLfm2Model(path, 256)
+    monkeypatch.setenv("WICK_CUDA_DECODE", "graph")
+    b = wick.CudaLfm2Model(path, 256)
+    monkeypatch.delenv("WICK_CUDA_DECODE")
+    assert a.decode_path() == "persistent" and b.decode_path() == "graph"
+    om = orc.OracleModel(path, 256)
+    sa, sb = wick.InferenceState(), wick.InferenceState()
+    toks = gs.random_prompt(20, a.config().vocab_size, seed=4)
+    for i, t in enumerate(toks):
+        la, lb, lo = a.forward([int(t)], i, sa), b.forward([int(t)], i, sb), om.forward(int(t))
+        assert_logits_equal(la, lo, f"persistent step {i}")
+        assert_logits_equal(lb, lo, f"graph step {i}")
+    ga, gb = a.generate_greedy(7, 40, sa), b.generate_greedy(7, 40, sb)
+    assert list(ga) == list(gb) == list(om.generate_greedy(7, 40))
+    for li, kvh in enumerate(a.config().kv_heads_per_layer):
+        if kvh:
+            assert all(np.array_equal(x, y) for x, y in zip(a.read_kv(li), b.read_kv(li)))
+        else:
+            assert np.array_equal(a.read_conv_state(li), b.read_conv_state(li))
+
+
+def test_bounded_waits_report_timeout(wick, model_dir):
+    """Failure detection without a GPU fault: a grid-wide wait whose condition never comes true runs
+    out after a bounded number of polls, the call reports TIMEOUT, and the context stays usable."""
+    import ctypes as C
+    from wick_b200 import gguf_synth as gs
+    from wick_b200._lib import WickCudaError, check
+    path = _model_path(model_dir, "tiny", "q4_0")
+    m = wick.CudaLfm2Model(path, 64)
+    if m.decode_path() != "persistent":
+        pytest.skip("graph decode has no device-side waits")
+    st = wick.InferenceState()
+    toks = gs.random_prompt(8, m.config().vocab_size)
+    want = m.forward_prefill(toks, 0, st)
+    t1 = m.forward_greedy([3], 8, st)
+    check(m._lib.wick_cuda_debug_skew_barrier(m._h, C.c_int64(5)))      # wait for arrivals nobody makes
+    with pytest.raises(WickCudaError) as e:
+        m.generate_greedy(3, 2, st)
+    assert e.value.code == -6
+    # the same handle works again after a reset
+    st = wick.InferenceState()
+    assert np.array_equal(m.forward_prefill(toks, 0, st), want)
+    assert m.forward_greedy([3], 8, st) == t1

@@ -56,6 +56,8 @@ SIGNATURES = {
     "wick_cuda_restore": [_vp, _vp, _u64],
     "wick_cuda_last_elapsed_ms": [_vp, C.POINTER(_f)],
     "wick_cuda_kernel_launches": [_vp, C.POINTER(_u64)],
+    "wick_cuda_debug_skew_barrier": [_vp, C.c_int64],
+    "wick_cuda_decode_path": [_vp, C.POINTER(_i32)],
     "wick_cuda_read_kv": [_vp, _u32, _vp, _vp],
     "wick_cuda_read_conv_state": [_vp, _u32, _vp],
     "wick_cuda_weight_create": [_i32, _vp, _u32, _u32, C.POINTER(_vp)],

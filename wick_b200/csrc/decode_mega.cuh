@@ -1,0 +1,78 @@
+// Parameter blocks of the persistent decode kernel (decode_mega.cu).
+#pragma once
+#include "kernels.cuh"
+
+namespace wick {
+
+constexpr int MEGA_CONSUMER_WARPS = 16;
+constexpr int MEGA_THREADS = 32 * (MEGA_CONSUMER_WARPS + 1);  // warp 0 issues the bulk copies
+
+enum MegaPhaseKind : int {
+    MPH_NORM = 0,   // input = RMSNorm(hidden) (first phase of a token: hidden = embedding row)
+    MPH_CONV = 1,   // input = c * shortconv(b * x) from proj
+    MPH_ATTN = 2,   // no matmul: QK-norm, RoPE, KV append, single-query attention per head
+    MPH_QUANT = 3,  // input = attn_out
+    MPH_SILU = 4,   // input = silu(gate) * up
+};
+
+enum MegaEpilogue : int {
+    MEP_STORE = 0,   // y[row] = v
+    MEP_ADD = 1,     // y[row] = y[row] + v          (residual add, cpu::add_inplace)
+    MEP_LOGITS = 2,  // store (optional) + running argmax
+};
+
+struct MegaMat {
+    DevWeight w;
+    float* y;
+    int epi;
+};
+
+struct MegaPhase {
+    int kind;
+    int n_mat;
+    int k;              // input length
+    int layer;          // conv / attention layer this phase belongs to (or -1)
+    int embed;          // MPH_NORM: 1 = first phase of a token
+    int conv_commit;    // MPH_NORM: layer whose conv state is advanced in this prologue, or -1
+    const float* norm_w;
+    MegaMat mat[3];
+};
+
+struct MegaLayer {
+    const float* conv_w;
+    float* conv_state;
+    const float* q_norm;
+    const float* k_norm;
+    float* k_cache;
+    float* v_cache;
+    int n_kv;
+};
+
+struct MegaParams {
+    const MegaPhase* phases;
+    const MegaLayer* layers;
+    int n_phases;
+    int n_tokens;
+    int greedy;      // 1: feed the argmax back; 0: single step, logits only
+    int hs, is, n_heads, head_dim, vocab, conv_ks, max_seq;
+    float eps;
+    DevWeight embd;
+    float *hidden, *proj, *qbuf, *kbuf, *vbuf, *attn_out, *gate, *up, *logits;
+    const float *rope_cos, *rope_sin;
+    DecodeCtl* ctl;
+    uint32_t* ring;
+    int ring_len;
+    unsigned long long* bar_counter;   // monotonically increasing arrival counter
+    unsigned long long bar_base;       // barriers completed before this launch
+    unsigned long long* argmax_acc;    // [2], alternating by token
+    int slot_bytes, n_slots;           // bulk-copy ring geometry
+    int kmax;                          // max input length over phases (shared-memory sizing)
+};
+
+size_t mega_smem_bytes(const MegaParams& P);
+// Launches the persistent kernel (cooperative: one CTA per SM, all co-resident).
+cudaError_t launch_decode_mega(cudaStream_t st, const MegaParams& P, int n_ctas);
+// Largest grid that is guaranteed co-resident for this configuration on the current device.
+int mega_max_ctas(const MegaParams& P);
+
+}  // namespace wick

@@ -14,6 +14,7 @@
 
 #include "../../include/wick_cuda.h"
 #include "gguf.hpp"
+#include "decode_mega.cuh"
 #include "kernels.cuh"
 
 using namespace wick;
@@ -83,6 +84,16 @@ struct wick_cuda_model {
     uint64_t nodes_logits = 0, nodes_greedy = 0;  // kernels per graph replay
     uint64_t launches = 0;                        // kernels launched so far
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;     // bracket the GPU work of the last call
+    // persistent decode kernel (decode_mega.cu); falls back to the captured graphs when the
+    // model does not meet its layout requirements or WICK_CUDA_DECODE=graph is set
+    bool mega_ok = false;
+    int mega_ctas = 0;
+    MegaParams mega{};
+    MegaPhase* d_phases = nullptr;
+    MegaLayer* d_mlayers = nullptr;
+    unsigned long long* d_sync = nullptr;  // [0] barrier counter, [1..2] argmax accumulators
+    unsigned long long bar_base = 0;
+    DecodeCtl* h_ctl = nullptr;            // pinned copy of the control block
     uint32_t seq_len = 0;
     uint64_t bytes = 0;
     std::vector<void*> allocs;
@@ -97,6 +108,7 @@ struct wick_cuda_model {
         for (void* p : allocs) cudaFree(p);
         if (h_u32) cudaFreeHost(h_u32);
         if (h_logits) cudaFreeHost(h_logits);
+        if (h_ctl) cudaFreeHost(h_ctl);
         if (stream) cudaStreamDestroy(stream);
     }
 };
@@ -189,6 +201,135 @@ void fill_rope_table(int n_pos, int hd, float base, std::vector<float>& c, std::
             theta *= theta_scale;
         }
     }
+}
+
+// Phase list of one decode step for the persistent kernel (see decode_mega.cu).
+int32_t build_mega(wick_cuda_model* m) {
+    const char* env = getenv("WICK_CUDA_DECODE");
+    if (env && std::string(env) == "graph") return WICK_CUDA_OK;
+    int coop = 0;
+    CU_TRY(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, m->device));
+    if (!coop) return WICK_CUDA_OK;
+    const wick_cuda_config& c = m->cfg;
+    const int hs = c.hidden_size, is = c.intermediate_size;
+    std::vector<MegaPhase> ph;
+    std::vector<MegaLayer> ml(c.n_layers);
+    size_t max_group = 0;
+    bool ok = true;
+    auto mat = [&](const DevWeight& w, float* y, int epi) {
+        MegaMat mm{};
+        mm.w = w;
+        mm.y = y;
+        mm.epi = epi;
+        if (w.k % 64) ok = false;  // an even block count keeps every bulk copy 16-byte sized
+        max_group = std::max(max_group, w.q_group_bytes() + w.d_group_bytes());
+        return mm;
+    };
+    int pending_commit = -1;
+    for (uint32_t i = 0; i < c.n_layers; i++) {
+        Layer& L = m->layers[i];
+        MegaLayer& M = ml[i];
+        M.conv_w = L.conv_w; M.conv_state = L.conv_state; M.q_norm = L.q_norm; M.k_norm = L.k_norm;
+        M.k_cache = L.k_cache; M.v_cache = L.v_cache; M.n_kv = L.n_kv;
+        MegaPhase a{};
+        a.kind = MPH_NORM; a.k = hs; a.layer = (int)i; a.embed = i == 0; a.conv_commit = -1; a.norm_w = L.attn_norm;
+        if (!L.is_attn) {
+            a.n_mat = 1; a.mat[0] = mat(L.in_proj, m->proj, MEP_STORE);
+            ph.push_back(a);
+            MegaPhase b{};
+            b.kind = MPH_CONV; b.k = hs; b.layer = (int)i; b.conv_commit = -1; b.n_mat = 1;
+            b.mat[0] = mat(L.out_proj, m->hidden, MEP_ADD);
+            ph.push_back(b);
+            pending_commit = (int)i;
+        } else {
+            a.n_mat = 3;
+            a.mat[0] = mat(L.q, m->qbuf, MEP_STORE);
+            a.mat[1] = mat(L.k, m->kbuf, MEP_STORE);
+            a.mat[2] = mat(L.v, m->vbuf, MEP_STORE);
+            ph.push_back(a);
+            MegaPhase at{};
+            at.kind = MPH_ATTN; at.layer = (int)i; at.conv_commit = -1; at.k = hs;
+            ph.push_back(at);
+            MegaPhase o{};
+            o.kind = MPH_QUANT; o.k = hs; o.layer = (int)i; o.conv_commit = -1; o.n_mat = 1;
+            o.mat[0] = mat(L.o, m->hidden, MEP_ADD);
+            ph.push_back(o);
+        }
+        MegaPhase f{};
+        f.kind = MPH_NORM; f.k = hs; f.layer = (int)i; f.conv_commit = pending_commit; f.norm_w = L.ffn_norm; f.n_mat = 2;
+        pending_commit = -1;
+        f.mat[0] = mat(L.gate, m->gate, MEP_STORE);
+        f.mat[1] = mat(L.up, m->up, MEP_STORE);
+        ph.push_back(f);
+        MegaPhase d{};
+        d.kind = MPH_SILU; d.k = is; d.layer = (int)i; d.conv_commit = -1; d.n_mat = 1;
+        d.mat[0] = mat(L.down, m->hidden, MEP_ADD);
+        ph.push_back(d);
+    }
+    MegaPhase v{};
+    v.kind = MPH_NORM; v.k = hs; v.layer = -1; v.conv_commit = -1; v.norm_w = m->output_norm; v.n_mat = 1;
+    v.mat[0] = mat(m->embd, m->logits, MEP_LOGITS);
+    ph.push_back(v);
+    if (!ok || (c.conv_kernel_size < 2) || m->head_dim > 256) return WICK_CUDA_OK;
+
+    MegaParams& P = m->mega;
+    P.n_phases = (int)ph.size();
+    P.hs = hs; P.is = is; P.n_heads = c.n_heads; P.head_dim = m->head_dim; P.vocab = c.vocab_size;
+    P.conv_ks = c.conv_kernel_size; P.max_seq = c.max_seq_len; P.eps = c.rms_norm_eps;
+    P.embd = m->embd;
+    P.hidden = m->hidden; P.proj = m->proj; P.qbuf = m->qbuf; P.kbuf = m->kbuf; P.vbuf = m->vbuf;
+    P.attn_out = m->attn_out; P.gate = m->gate; P.up = m->up; P.logits = m->logits;
+    P.rope_cos = m->rope_cos; P.rope_sin = m->rope_sin;
+    P.ctl = m->ctl; P.ring = m->ring; P.ring_len = m->ring_len;
+    P.kmax = std::max(hs, is);
+    P.slot_bytes = (int)std::max<size_t>(16384, (max_group + 1023) / 1024 * 1024);
+    P.n_slots = 0;
+    int max_smem = 0;
+    CU_TRY(cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, m->device));
+    size_t fixed = mega_smem_bytes(P);
+    if (fixed + 4 * (size_t)P.slot_bytes + 64 * 4 > (size_t)max_smem) return WICK_CUDA_OK;
+    P.n_slots = (int)(((size_t)max_smem - fixed - 64 * 4) / ((size_t)P.slot_bytes + 16));
+    if (P.n_slots > 32) P.n_slots = 32;
+    W_TRY(dev_alloc(m, &m->d_phases, ph.size()));
+    W_TRY(dev_alloc(m, &m->d_mlayers, ml.size()));
+    W_TRY(dev_alloc(m, &m->d_sync, 4));
+    CU_TRY(cudaMemcpy(m->d_phases, ph.data(), ph.size() * sizeof(MegaPhase), cudaMemcpyHostToDevice));
+    CU_TRY(cudaMemcpy(m->d_mlayers, ml.data(), ml.size() * sizeof(MegaLayer), cudaMemcpyHostToDevice));
+    CU_TRY(cudaMemset(m->d_sync, 0, 32));
+    P.phases = m->d_phases;
+    P.layers = m->d_mlayers;
+    P.bar_counter = m->d_sync;
+    P.argmax_acc = m->d_sync + 1;
+    m->mega_ctas = mega_max_ctas(P);
+    m->mega_ok = m->mega_ctas > 0;
+    return WICK_CUDA_OK;
+}
+
+// Runs n decode steps with the persistent kernel; ctl holds token / pos / step on entry.
+int32_t run_mega(wick_cuda_model* m, int n_tokens, bool greedy) {
+    MegaParams P = m->mega;
+    P.n_tokens = n_tokens;
+    P.greedy = greedy ? 1 : 0;
+    P.bar_base = m->bar_base;
+    CU_TRY(launch_decode_mega(m->stream, P, m->mega_ctas));
+    m->launches += 1;
+    m->bar_base += (unsigned long long)n_tokens * P.n_phases;
+    CU_TRY(cudaMemcpyAsync(m->h_ctl, m->ctl, sizeof(DecodeCtl), cudaMemcpyDeviceToHost, m->stream));
+    return WICK_CUDA_OK;
+}
+
+int32_t check_mega_status(wick_cuda_model* m) {
+    if (m->h_ctl->error) {
+        uint32_t e = m->h_ctl->error;
+        // the barrier counter is no longer in step with bar_base: resynchronise and clear
+        cudaMemsetAsync(m->d_sync, 0, 32, m->stream);
+        cudaMemsetAsync(&m->ctl->error, 0, 4, m->stream);
+        cudaStreamSynchronize(m->stream);
+        m->bar_base = 0;
+        return fail(WICK_CUDA_ERR_TIMEOUT, "decode kernel gave up waiting (flags " + std::to_string(e) +
+                                               "); the sequence state is undefined, reset before reuse");
+    }
+    return WICK_CUDA_OK;
 }
 
 size_t naive_attn_smem(const wick_cuda_model* m) { return (size_t)(m->head_dim + m->cfg.max_seq_len) * sizeof(float); }
@@ -449,6 +590,8 @@ int32_t build_model(wick_cuda_model* m, const GgufImage& g, uint32_t context_siz
     W_TRY(dev_alloc(m, &m->ring, (size_t)m->ring_len));
     CU_TRY(cudaMallocHost((void**)&m->h_u32, std::max<size_t>((size_t)std::max<int>(m->ring_len, m->max_chunk) * 4, 256)));
     CU_TRY(cudaMallocHost((void**)&m->h_logits, (size_t)c.vocab_size * 4));
+    CU_TRY(cudaMallocHost((void**)&m->h_ctl, sizeof(DecodeCtl)));
+    memset(m->h_ctl, 0, sizeof(DecodeCtl));
     CU_TRY(cudaMemset(m->ctl, 0, sizeof(DecodeCtl)));
     W_TRY(reset_sequence(m));
     if (naive_attn_smem(m) > 48 * 1024) {
@@ -456,6 +599,7 @@ int32_t build_model(wick_cuda_model* m, const GgufImage& g, uint32_t context_siz
     }
     CU_TRY(cudaEventCreate(&m->ev0));
     CU_TRY(cudaEventCreate(&m->ev1));
+    W_TRY(build_mega(m));
     W_TRY(capture_graph(m, false, &m->g_logits, &m->nodes_logits));
     W_TRY(capture_graph(m, true, &m->g_greedy, &m->nodes_greedy));
     CU_TRY(cudaStreamSynchronize(m->stream));
@@ -562,11 +706,16 @@ int32_t wick_cuda_forward(wick_cuda_model* m, uint32_t token, uint32_t pos, floa
     m->h_u32[0] = token;
     CU_TRY(cudaEventRecord(m->ev0, m->stream));
     CU_TRY(cudaMemcpyAsync(&m->ctl->token, m->h_u32, 4, cudaMemcpyHostToDevice, m->stream));
-    CU_TRY(cudaGraphLaunch(m->g_logits, m->stream));
-    m->launches += m->nodes_logits;
+    if (m->mega_ok) {
+        W_TRY(run_mega(m, 1, false));
+    } else {
+        CU_TRY(cudaGraphLaunch(m->g_logits, m->stream));
+        m->launches += m->nodes_logits;
+    }
     CU_TRY(cudaMemcpyAsync(m->h_logits, m->logits, (size_t)m->cfg.vocab_size * 4, cudaMemcpyDeviceToHost, m->stream));
     CU_TRY(cudaEventRecord(m->ev1, m->stream));
     CU_TRY(cudaStreamSynchronize(m->stream));
+    if (m->mega_ok) W_TRY(check_mega_status(m));
     memcpy(logits_host, m->h_logits, (size_t)m->cfg.vocab_size * 4);
     m->seq_len += 1;
     return WICK_CUDA_OK;
@@ -578,11 +727,19 @@ int32_t wick_cuda_forward_greedy(wick_cuda_model* m, uint32_t token, uint32_t po
     m->h_u32[0] = token;
     CU_TRY(cudaEventRecord(m->ev0, m->stream));
     CU_TRY(cudaMemcpyAsync(&m->ctl->token, m->h_u32, 4, cudaMemcpyHostToDevice, m->stream));
-    CU_TRY(cudaGraphLaunch(m->g_greedy, m->stream));
-    m->launches += m->nodes_greedy;
-    CU_TRY(cudaMemcpyAsync(m->h_u32 + 1, m->argmax_tok, 4, cudaMemcpyDeviceToHost, m->stream));
+    if (m->mega_ok) {
+        W_TRY(run_mega(m, 1, true));  // copies the control block (with the chosen token) back
+    } else {
+        CU_TRY(cudaGraphLaunch(m->g_greedy, m->stream));
+        m->launches += m->nodes_greedy;
+        CU_TRY(cudaMemcpyAsync(m->h_u32 + 1, m->argmax_tok, 4, cudaMemcpyDeviceToHost, m->stream));
+    }
     CU_TRY(cudaEventRecord(m->ev1, m->stream));
     CU_TRY(cudaStreamSynchronize(m->stream));
+    if (m->mega_ok) {
+        W_TRY(check_mega_status(m));
+        m->h_u32[1] = m->h_ctl->token;
+    }
     *next_token = m->h_u32[1];
     m->seq_len += 1;
     return WICK_CUDA_OK;
@@ -600,11 +757,16 @@ int32_t wick_cuda_generate_greedy(wick_cuda_model* m, uint32_t first_token, uint
     memcpy(m->h_u32, init, sizeof(init));
     CU_TRY(cudaEventRecord(m->ev0, m->stream));
     CU_TRY(cudaMemcpyAsync(m->ctl, m->h_u32, sizeof(init), cudaMemcpyHostToDevice, m->stream));
-    for (uint32_t i = 0; i < n_steps; i++) CU_TRY(cudaGraphLaunch(m->g_greedy, m->stream));
-    m->launches += m->nodes_greedy * n_steps;
+    if (m->mega_ok) {
+        W_TRY(run_mega(m, (int)n_steps, true));
+    } else {
+        for (uint32_t i = 0; i < n_steps; i++) CU_TRY(cudaGraphLaunch(m->g_greedy, m->stream));
+        m->launches += m->nodes_greedy * n_steps;
+    }
     CU_TRY(cudaMemcpyAsync(m->h_u32, m->ring, (size_t)n_steps * 4, cudaMemcpyDeviceToHost, m->stream));
     CU_TRY(cudaEventRecord(m->ev1, m->stream));
     CU_TRY(cudaStreamSynchronize(m->stream));
+    if (m->mega_ok) W_TRY(check_mega_status(m));
     memcpy(out_tokens_host, m->h_u32, (size_t)n_steps * 4);
     m->seq_len += n_steps;
     return WICK_CUDA_OK;
@@ -754,6 +916,20 @@ int32_t wick_cuda_kernel_launches(const wick_cuda_model* m, uint64_t* count) {
     W_TRY(check_model(m));
     if (!count) return fail(WICK_CUDA_ERR_BAD_ARG, "count is NULL");
     *count = m->launches;
+    return WICK_CUDA_OK;
+}
+
+int32_t wick_cuda_debug_skew_barrier(wick_cuda_model* m, int64_t delta) {
+    W_TRY(check_model(m));
+    if (!m->mega_ok) return fail(WICK_CUDA_ERR_BAD_ARG, "this model decodes through captured graphs");
+    m->bar_base = (unsigned long long)((long long)m->bar_base + delta);
+    return WICK_CUDA_OK;
+}
+
+int32_t wick_cuda_decode_path(const wick_cuda_model* m, int32_t* persistent) {
+    W_TRY(check_model(m));
+    if (!persistent) return fail(WICK_CUDA_ERR_BAD_ARG, "persistent is NULL");
+    *persistent = m->mega_ok ? 1 : 0;
     return WICK_CUDA_OK;
 }
 

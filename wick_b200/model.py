@@ -213,6 +213,12 @@ class CudaLfm2Model:
         check(self._lib.wick_cuda_kernel_launches(self._h, C.byref(v)))
         return v.value
 
+    def decode_path(self) -> str:
+        """'persistent' (one kernel runs whole decode steps) or 'graph' (captured per-kernel graph)."""
+        v = C.c_int32(0)
+        check(self._lib.wick_cuda_decode_path(self._h, C.byref(v)))
+        return "persistent" if v.value else "graph"
+
     def read_kv(self, layer: int) -> Tuple[np.ndarray, np.ndarray]:
         kv_dim = self._config.kv_heads_per_layer[layer] * (self._config.hidden_size // self._config.n_heads)
         rows = self.seq_len
