@@ -131,6 +131,14 @@ int32_t wick_cuda_restore(wick_cuda_model* m, const uint8_t* snap_host, uint64_t
 int32_t wick_cuda_last_elapsed_ms(wick_cuda_model* m, float* ms);
 int32_t wick_cuda_kernel_launches(const wick_cuda_model* m, uint64_t* count);
 
+/* Per-phase timeline of the most recent decode step run by the persistent kernel, in the spirit of
+ * wick's per-category timers (WICK_PROFILE=timing, metal_lfm2.rs:3986-4035): for each phase four
+ * device timestamps in ns (dependency barrier passed, input prologue done, mat-vec done, arrived at
+ * the next barrier) taken by one CTA, and the phase kind (0 norm, 1 short-conv, 2 attention,
+ * 3 attention-output quantise, 4 SwiGLU).  *n_phases is always set; the arrays are filled when
+ * capacity >= *n_phases (ns_out holds 4 values per phase). */
+int32_t wick_cuda_decode_profile(wick_cuda_model* m, uint64_t* ns_out, int32_t* kinds_out, uint32_t capacity,
+                                 uint32_t* n_phases);
 /* Test hook for the bounded waits of the persistent decode kernel: shifts the barrier sequence
  * number the NEXT decode call waits for by `delta` arrivals, so that its grid-wide waits expire
  * (about a second) and the call returns WICK_CUDA_ERR_TIMEOUT with the device context intact.

@@ -56,6 +56,7 @@ SIGNATURES = {
     "wick_cuda_restore": [_vp, _vp, _u64],
     "wick_cuda_last_elapsed_ms": [_vp, C.POINTER(_f)],
     "wick_cuda_kernel_launches": [_vp, C.POINTER(_u64)],
+    "wick_cuda_decode_profile": [_vp, _vp, _vp, _u32, C.POINTER(_u32)],
     "wick_cuda_debug_skew_barrier": [_vp, C.c_int64],
     "wick_cuda_decode_path": [_vp, C.POINTER(_i32)],
     "wick_cuda_read_kv": [_vp, _u32, _vp, _vp],

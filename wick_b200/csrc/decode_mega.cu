@@ -65,6 +65,11 @@ __device__ __forceinline__ unsigned long long ld_acquire_u64(const unsigned long
     asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
     return v;
 }
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(NCT) : "memory"); }
 
 struct Smem {
@@ -116,7 +121,10 @@ __device__ __forceinline__ Smem carve(uint8_t* base, const MegaParams& P) {
 }
 
 // Work split of one phase for one CTA: a contiguous run [lo, hi) of the phase's row groups
-// (all matrices of the phase concatenated), cut into stages of at most `rg` groups.
+// (all matrices of the phase concatenated), cut into stages of at most `rg` groups (one ring
+// slot each).  EVERY consumer warp waits for EVERY stage in order and releases it, so a warp
+// can never wait two uses of a slot ahead (mbarrier parity would alias); inside a stage the
+// groups are dealt to the warps round-robin by their running index in the phase.
 struct Plan {
     int lo, hi, rg;
 };
@@ -131,9 +139,8 @@ __device__ __forceinline__ Plan plan_phase(const MegaPhase& ph, int cta, int nct
     p.lo = (int)((long long)cta * gt / ncta);
     p.hi = (int)((long long)(cta + 1) * gt / ncta);
     int cap = slot_bytes / gb;
-    int rg = (p.hi - p.lo + NC - 1) / NC;
-    rg = rg < 1 ? 1 : rg;
-    p.rg = rg > cap ? cap : rg;
+    cap = cap < 1 ? 1 : cap;
+    p.rg = cap > 4 ? 4 : cap;
     return p;
 }
 
@@ -482,6 +489,8 @@ __device__ void consumer(const MegaParams& P, const Smem& S, int cta, int ncta) 
         for (int pi = 0; pi < P.n_phases; pi++) {
             const MegaPhase& ph = P.phases[pi];
             if (t > 0 || pi > 0) grid_wait(c, (P.bar_base + (unsigned long long)t * P.n_phases + pi) * (unsigned long long)ncta);
+            const bool prof = P.prof && cta == 0 && c.ct == 0 && t == P.n_tokens - 1;
+            if (prof) P.prof[pi * 4 + 0] = globaltimer_ns();
             if (pi == 0 && t > 0) {
                 // argmax of the previous step is this step's input (Session::generate, session.rs:1251)
                 token = (uint32_t)(__ldcg(&P.argmax_acc[(t - 1) & 1]) & 0xffffffffull);
@@ -495,6 +504,7 @@ __device__ void consumer(const MegaParams& P, const Smem& S, int cta, int ncta) 
                 case MPH_QUANT: prologue_quant(c, ph); break;
                 default: phase_attention(c, ph, pos); break;
             }
+            if (prof) P.prof[pi * 4 + 1] = globaltimer_ns();
             if (ph.kind != MPH_ATTN) {
                 Plan pl = plan_phase(ph, cta, ncta, P.slot_bytes);
                 int off = 0, ls = 0;
@@ -504,8 +514,7 @@ __device__ void consumer(const MegaParams& P, const Smem& S, int cta, int ncta) 
                     const int gm = w.groups(), nb = w.k / QK;
                     int a = (pl.lo > off ? pl.lo : off) - off, b = (pl.hi < off + gm ? pl.hi : off + gm) - off;
                     const uint32_t qgb = (uint32_t)w.q_group_bytes();
-                    for (int g0 = a; g0 < b; g0 += pl.rg, cnt++, ls++) {
-                        if (ls % NC != c.cw) continue;
+                    for (int g0 = a; g0 < b; g0 += pl.rg, cnt++) {
                         int ng = pl.rg < b - g0 ? pl.rg : b - g0;
                         int slot = (int)(cnt % P.n_slots);
                         uint32_t u = (uint32_t)(cnt / P.n_slots);
@@ -520,7 +529,8 @@ __device__ void consumer(const MegaParams& P, const Smem& S, int cta, int ncta) 
                         }
                         const uint8_t* base = S.ring + (size_t)slot * P.slot_bytes;
                         const __half* dbase = reinterpret_cast<const __half*>(base + (size_t)ng * qgb);
-                        for (int gi = 0; gi < ng; gi++) {
+                        for (int gi = 0; gi < ng; gi++, ls++) {
+                            if (ls % NC != c.cw) continue;
                             const uint32_t* qs = reinterpret_cast<const uint32_t*>(base + (size_t)gi * qgb);
                             const __half* ds = dbase + (size_t)gi * nb * 4;
                             float acc = w.dtype == DT_Q4_0 ? group_chain<DT_Q4_0>(qs, ds, nb, c.lane, xq32, S.xs16)
@@ -560,7 +570,9 @@ __device__ void consumer(const MegaParams& P, const Smem& S, int cta, int ncta) 
                     atomicMax(&P.argmax_acc[t & 1], b);
                 }
             }
+            if (prof) P.prof[pi * 4 + 2] = globaltimer_ns();
             grid_arrive(c);
+            if (prof) P.prof[pi * 4 + 3] = globaltimer_ns();
         }
     }
     // last step's result and the control block
@@ -587,7 +599,7 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) k_decode_mega(const MegaParam
     if (threadIdx.x == 0) {
         for (int i = 0; i < P.n_slots; i++) {
             mbar_init(&S.full[i], 1);
-            mbar_init(&S.empty[i], 1);
+            mbar_init(&S.empty[i], NC);  // every consumer warp releases every stage
         }
         *S.abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -645,6 +657,9 @@ int mega_max_ctas(const MegaParams& P) {
 
 cudaError_t launch_decode_mega(cudaStream_t st, const MegaParams& P, int n_ctas) {
     size_t smem = mega_smem_bytes(P);
+    // the attribute is per function, not per model: models of different size share the kernel
+    cudaError_t e = cudaFuncSetAttribute(k_decode_mega, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
     void* args[] = {(void*)&P};
     g_kernel_launches++;
     return cudaLaunchCooperativeKernel((const void*)k_decode_mega, dim3(n_ctas), dim3(MEGA_THREADS), args, smem, st);

@@ -67,6 +67,9 @@ struct MegaParams {
     unsigned long long* argmax_acc;    // [2], alternating by token
     int slot_bytes, n_slots;           // bulk-copy ring geometry
     int kmax;                          // max input length over phases (shared-memory sizing)
+    // optional per-phase timestamps (globaltimer ns) of CTA 0 for the last step of a launch:
+    // [phase][0] barrier passed, [1] prologue done, [2] mat-vec done, [3] arrived
+    unsigned long long* prof;
 };
 
 size_t mega_smem_bytes(const MegaParams& P);

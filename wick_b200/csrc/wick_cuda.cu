@@ -92,6 +92,7 @@ struct wick_cuda_model {
     MegaPhase* d_phases = nullptr;
     MegaLayer* d_mlayers = nullptr;
     unsigned long long* d_sync = nullptr;  // [0] barrier counter, [1..2] argmax accumulators
+    unsigned long long* d_prof = nullptr;  // [n_phases][4] timestamps of the last step
     unsigned long long bar_base = 0;
     DecodeCtl* h_ctl = nullptr;            // pinned copy of the control block
     uint32_t seq_len = 0;
@@ -293,6 +294,9 @@ int32_t build_mega(wick_cuda_model* m) {
     W_TRY(dev_alloc(m, &m->d_phases, ph.size()));
     W_TRY(dev_alloc(m, &m->d_mlayers, ml.size()));
     W_TRY(dev_alloc(m, &m->d_sync, 4));
+    W_TRY(dev_alloc(m, &m->d_prof, ph.size() * 4));
+    CU_TRY(cudaMemset(m->d_prof, 0, ph.size() * 32));
+    P.prof = m->d_prof;
     CU_TRY(cudaMemcpy(m->d_phases, ph.data(), ph.size() * sizeof(MegaPhase), cudaMemcpyHostToDevice));
     CU_TRY(cudaMemcpy(m->d_mlayers, ml.data(), ml.size() * sizeof(MegaLayer), cudaMemcpyHostToDevice));
     CU_TRY(cudaMemset(m->d_sync, 0, 32));
@@ -916,6 +920,21 @@ int32_t wick_cuda_kernel_launches(const wick_cuda_model* m, uint64_t* count) {
     W_TRY(check_model(m));
     if (!count) return fail(WICK_CUDA_ERR_BAD_ARG, "count is NULL");
     *count = m->launches;
+    return WICK_CUDA_OK;
+}
+
+int32_t wick_cuda_decode_profile(wick_cuda_model* m, uint64_t* ns_out, int32_t* kinds_out, uint32_t capacity, uint32_t* n_phases) {
+    W_TRY(check_model(m));
+    if (!m->mega_ok) return fail(WICK_CUDA_ERR_BAD_ARG, "this model decodes through captured graphs");
+    if (!n_phases) return fail(WICK_CUDA_ERR_BAD_ARG, "n_phases is NULL");
+    *n_phases = (uint32_t)m->mega.n_phases;
+    if (!ns_out || !kinds_out || capacity < (uint32_t)m->mega.n_phases) return WICK_CUDA_OK;
+    CU_TRY(cudaSetDevice(m->device));
+    CU_TRY(cudaStreamSynchronize(m->stream));
+    CU_TRY(cudaMemcpy(ns_out, m->d_prof, (size_t)m->mega.n_phases * 32, cudaMemcpyDeviceToHost));
+    std::vector<MegaPhase> ph(m->mega.n_phases);
+    CU_TRY(cudaMemcpy(ph.data(), m->d_phases, ph.size() * sizeof(MegaPhase), cudaMemcpyDeviceToHost));
+    for (size_t i = 0; i < ph.size(); i++) kinds_out[i] = ph[i].kind;
     return WICK_CUDA_OK;
 }
 

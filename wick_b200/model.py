@@ -219,6 +219,15 @@ class CudaLfm2Model:
         check(self._lib.wick_cuda_decode_path(self._h, C.byref(v)))
         return "persistent" if v.value else "graph"
 
+    def decode_profile(self):
+        """Timeline of the last decode step of the persistent kernel: (kinds [n], ns [n, 4])."""
+        n = C.c_uint32(0)
+        check(self._lib.wick_cuda_decode_profile(self._h, None, None, 0, C.byref(n)))
+        ns = np.zeros((n.value, 4), np.uint64)
+        kinds = np.zeros(n.value, np.int32)
+        check(self._lib.wick_cuda_decode_profile(self._h, ns.ctypes.data, kinds.ctypes.data, n.value, C.byref(n)))
+        return kinds, ns
+
     def read_kv(self, layer: int) -> Tuple[np.ndarray, np.ndarray]:
         kv_dim = self._config.kv_heads_per_layer[layer] * (self._config.hidden_size // self._config.n_heads)
         rows = self.seq_len
