@@ -9,7 +9,7 @@
 //     (cp.async.bulk + mbarrier) into a ring of shared-memory slots.  The weights do not
 //     depend on activations, so this producer runs AHEAD across phase boundaries: while the
 //     grid waits for a dependency, HBM keeps streaming into the ring;
-//   * 16 consumer warps take ring slots; a warp owns 4-row groups and its lanes are the
+//   * 15 consumer warps take ring slots; a warp owns 4-row groups and its lanes are the
 //     eight f32 accumulation chains of each row (see kernels_gemv.cu), reading weights and the
 //     quantised input from shared memory without bank conflicts (grouped layout, DevWeight);
 //   * the small operators between mat-vecs (RMSNorm + Q8_0 quantise, short-conv gating,
@@ -55,9 +55,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 // 1-D bulk copy global -> shared, completion counted in bytes on `bar`.  Both addresses and
 // the size are multiples of 16.
-__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)),
-                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
+// The weights are read once per step and are far larger than L2: they are fetched with an
+// evict-first policy so that they do not push the activations, KV rows and norm weights out.
+__device__ __forceinline__ uint64_t l2_evict_first_policy() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar, uint64_t pol) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(
+                     smem_u32(dst)),
+                 "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(pol)
                  : "memory");
 }
 __device__ __forceinline__ unsigned long long ld_acquire_u64(const unsigned long long* p) {
@@ -72,9 +80,13 @@ __device__ __forceinline__ unsigned long long globaltimer_ns() {
 }
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(NCT) : "memory"); }
 
+// floats of the attention staging area: normalised scores of up to max_seq keys plus at least
+// 64 gathered V rows of 16 columns
+__host__ __device__ __forceinline__ int xf_floats(const MegaParams& P) { return P.max_seq + 4 + 64 * 16; }
+
 struct Smem {
     uint8_t* ring;
-    float* xf;     // f32 staging of a phase input (also attention scores)
+    float* xf;     // attention phase: normalised scores, then gathered V rows
     int8_t* xq;    // quantised phase input
     float* xs;     // its block scales
     float* xs16;   // scales / 16 (Q4_0 lane sums are kept multiplied by 16)
@@ -85,6 +97,8 @@ struct Smem {
     uint64_t* full;
     uint64_t* empty;
     volatile int* abort;
+    MegaPhase* ph;      // the phase list, copied from global memory when the kernel starts
+    MegaLayer* layers;
 };
 
 __device__ __forceinline__ Smem carve(uint8_t* base, const MegaParams& P) {
@@ -92,7 +106,7 @@ __device__ __forceinline__ Smem carve(uint8_t* base, const MegaParams& P) {
     size_t o = 0;
     s.ring = base;
     o += (size_t)P.n_slots * P.slot_bytes;
-    int nf = P.kmax > P.max_seq ? P.kmax : P.max_seq;
+    int nf = xf_floats(P);
     s.xf = (float*)(base + o);
     o += (size_t)nf * 4;
     s.xs = (float*)(base + o);
@@ -117,8 +131,16 @@ __device__ __forceinline__ Smem carve(uint8_t* base, const MegaParams& P) {
     s.head = (float*)(base + o);
     o += 4 * 256 * 4;
     s.abort = (volatile int*)(base + o);
+    o += 16;
+    s.ph = (MegaPhase*)(base + o);
+    o += (size_t)P.n_phases * sizeof(MegaPhase);
+    s.layers = (MegaLayer*)(base + o);
     return s;
 }
+
+// floor(i * n / d) in 32-bit arithmetic (64-bit integer division is emulated and costs hundreds of
+// cycles); every product here stays far below 2^32 (n < 2^21 elements or groups, i <= #SMs).
+__device__ __forceinline__ int share(int i, int n, int d) { return (int)((unsigned)i * (unsigned)n / (unsigned)d); }
 
 // Work split of one phase for one CTA: a contiguous run [lo, hi) of the phase's row groups
 // (all matrices of the phase concatenated), cut into stages of at most `rg` groups (one ring
@@ -127,6 +149,7 @@ __device__ __forceinline__ Smem carve(uint8_t* base, const MegaParams& P) {
 // groups are dealt to the warps round-robin by their running index in the phase.
 struct Plan {
     int lo, hi, rg;
+    bool pair;
 };
 __device__ __forceinline__ Plan plan_phase(const MegaPhase& ph, int cta, int ncta, int slot_bytes) {
     int gt = 0, gb = 1;
@@ -136,11 +159,12 @@ __device__ __forceinline__ Plan plan_phase(const MegaPhase& ph, int cta, int nct
         gb = b > gb ? b : gb;
     }
     Plan p;
-    p.lo = (int)((long long)cta * gt / ncta);
-    p.hi = (int)((long long)(cta + 1) * gt / ncta);
+    p.lo = share(cta, gt, ncta);
+    p.hi = share(cta + 1, gt, ncta);
     int cap = slot_bytes / gb;
     cap = cap < 1 ? 1 : cap;
-    p.rg = cap > 4 ? 4 : cap;
+    p.pair = cap >= 2 && (p.hi - p.lo) > NC;
+    p.rg = p.pair ? (cap >= 4 ? 4 : 2) : (cap > 2 ? 2 : cap);
     return p;
 }
 
@@ -148,9 +172,12 @@ __device__ __forceinline__ Plan plan_phase(const MegaPhase& ph, int cta, int nct
 // Returns the number of stages issued (the caller drains the last n_slots of them on abort).
 __device__ unsigned long long producer(const MegaParams& P, const Smem& S, int cta, int ncta) {
     unsigned long long cnt = 0;
+    const uint64_t pol = l2_evict_first_policy();
+    int slot = 0;      // cnt % n_slots and the parity of cnt / n_slots, kept incrementally
+    uint32_t par = 0;  // (a 64-bit division per stage would cost more than issuing the copy)
     for (int t = 0; t < P.n_tokens; t++) {
         for (int pi = 0; pi < P.n_phases; pi++) {
-            const MegaPhase& ph = P.phases[pi];
+            const MegaPhase& ph = S.ph[pi];
             if (ph.kind == MPH_ATTN) continue;
             Plan pl = plan_phase(ph, cta, ncta, P.slot_bytes);
             int off = 0;
@@ -159,12 +186,10 @@ __device__ unsigned long long producer(const MegaParams& P, const Smem& S, int c
                 const int gm = w.groups();
                 int a = (pl.lo > off ? pl.lo : off) - off, b = (pl.hi < off + gm ? pl.hi : off + gm) - off;
                 const uint32_t qgb = (uint32_t)w.q_group_bytes(), dgb = (uint32_t)w.d_group_bytes();
-                for (int g0 = a; g0 < b; g0 += pl.rg, cnt++) {
+                for (int g0 = a; g0 < b; g0 += pl.rg, cnt++, slot = slot + 1 == P.n_slots ? 0 : slot + 1, par ^= (slot == 0)) {
                     int ng = pl.rg < b - g0 ? pl.rg : b - g0;
-                    int slot = (int)(cnt % P.n_slots);
-                    uint32_t u = (uint32_t)(cnt / P.n_slots);
                     unsigned spins = 0;
-                    while (!mbar_try_wait(&S.empty[slot], (u & 1) ^ 1)) {
+                    while (!mbar_try_wait(&S.empty[slot], par ^ 1)) {
                         if (*S.abort) return cnt;
                         if (++spins > SPIN_LIMIT) {
                             atomicOr(&P.ctl->error, 2u);
@@ -175,8 +200,8 @@ __device__ unsigned long long producer(const MegaParams& P, const Smem& S, int c
                     }
                     uint8_t* dst = S.ring + (size_t)slot * P.slot_bytes;
                     mbar_expect_tx(&S.full[slot], ng * (qgb + dgb));
-                    bulk_g2s(dst, w.q + (size_t)g0 * qgb, ng * qgb, &S.full[slot]);
-                    bulk_g2s(dst + (size_t)ng * qgb, (const uint8_t*)w.d + (size_t)g0 * dgb, ng * dgb, &S.full[slot]);
+                    bulk_g2s(dst, w.q + (size_t)g0 * qgb, ng * qgb, &S.full[slot], pol);
+                    bulk_g2s(dst + (size_t)ng * qgb, (const uint8_t*)w.d + (size_t)g0 * dgb, ng * dgb, &S.full[slot], pol);
                 }
                 off += gm;
             }
@@ -190,7 +215,12 @@ struct Ctx {
     const MegaParams& P;
     const Smem& S;
     int cta, ncta, ct, cw, lane;
+    unsigned long long* stamp;  // fine-grained timeline of one selected phase (debug), or NULL
 };
+#define STAMP(c, i)                                             \
+    do {                                                        \
+        if ((c).stamp) (c).stamp[i] = globaltimer_ns();          \
+    } while (0)
 
 // Waits are "fail open": once a wait has expired (here or in any CTA, seen through ctl->error)
 // the abort flag is set and every later wait returns at once, so all threads still walk the same
@@ -212,25 +242,42 @@ __device__ void grid_wait(Ctx& c, unsigned long long target) {
 
 __device__ void grid_arrive(Ctx& c) {
     consumer_sync();
-    if (c.ct == 0) {
-        __threadfence();
-        atomicAdd(c.P.bar_counter, 1ull);
-    }
+    if (c.ct == 0)  // release: orders the CTA's writes (made visible to this thread by the barrier) before the count
+        asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(c.P.bar_counter), "l"(1ull) : "memory");
 }
 
-// Quantise xf[0..k) to Q8_0 in shared memory (simd.rs:255-323), one block per warp step.
-__device__ void quantize_input(Ctx& c, int k) {
-    const int nb = k / QK;
-    for (int b = c.cw; b < nb; b += NC) {
-        float sc;
-        int8_t q = quantize_lane(c.S.xf[b * QK + c.lane], &sc);
-        c.S.xq[b * QK + c.lane] = q;
-        if (c.lane == 0) {
-            c.S.xs[b] = sc;
-            c.S.xs16[b] = __fmul_rn(sc, 0.0625f);
+// Phase inputs are produced block-wise: consumer warp cw owns the 32-element blocks
+// cw, cw + NC, ... and lane `lane` element `lane` of each, so a value is computed, quantised
+// (simd.rs:255-323) and stored by the same thread with no staging pass.
+constexpr int MAXJ = 16;  // blocks per warp: inputs up to NC * MAXJ * 32 = 7680 elements
+constexpr int FASTJ = 5;  // inputs of up to NC * FASTJ * 32 = 2400 elements take the short path
+
+// Quantises blocks cw + j*NC (j < J, those below nb) whose element `lane` is v[j].  The J
+// reductions are independent and interleaved by hand so their shuffle latencies overlap.
+template <int J>
+__device__ __forceinline__ void quantize_blocks(Ctx& c, const float (&v)[J], int j0, int nb) {
+    float a[J];
+#pragma unroll
+    for (int j = 0; j < J; j++) a[j] = fabsf(v[j]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+        for (int j = 0; j < J; j++) a[j] = fmaxf(a[j], __shfl_xor_sync(0xffffffffu, a[j], o));
+    }
+#pragma unroll
+    for (int j = 0; j < J; j++) {
+        const int b = c.cw + (j0 + j) * NC;
+        if (b < nb) {
+            const float d = __fdiv_rn(a[j], 127.0f);
+            const float id = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+            c.S.xq[b * QK + c.lane] = (int8_t)__float2int_rn(__fmul_rn(v[j], id));
+            if (c.lane == 0) {
+                const float sc = __half2float(__float2half_rn(d));
+                c.S.xs[b] = sc;
+                c.S.xs16[b] = __fmul_rn(sc, 0.0625f);
+            }
         }
     }
-    consumer_sync();
 }
 
 __device__ __forceinline__ float embed_elem(const DevWeight& w, uint32_t tok, int e) {
@@ -252,74 +299,151 @@ __device__ __forceinline__ float conv_bx(const float* proj, int hs, int ch) {
     return __fmul_rn(__ldcg(proj + ch), __ldcg(proj + 2 * hs + ch));
 }
 
-__device__ void prologue_norm(Ctx& c, const MegaPhase& ph, uint32_t token) {
+// Norm weights of the thread's elements; static data, fetched BEFORE the dependency wait.
+__device__ __forceinline__ void load_norm_w(const Ctx& c, const MegaPhase& ph, float (&w)[MAXJ]) {
+    const int nb = ph.k / QK;
+#pragma unroll
+    for (int j = 0; j < MAXJ; j++) {
+        const int b = c.cw + j * NC;
+        w[j] = b < nb ? __ldg(ph.norm_w + b * QK + c.lane) : 0.0f;
+    }
+}
+
+__device__ void prologue_norm(Ctx& c, const MegaPhase& ph, uint32_t token, const float (&w)[MAXJ]) {
     const MegaParams& P = c.P;
-    const int k = ph.k;
+    const int k = ph.k, nb = k / QK;
     if (ph.conv_commit >= 0) {
         // advance the conv rolling buffer of the layer whose gating ran one phase ago; every CTA
         // finished reading the old buffer before the barrier that was just passed
-        const MegaLayer& L = P.layers[ph.conv_commit];
+        const MegaLayer& L = c.S.layers[ph.conv_commit];
         const int dc = P.conv_ks - 1, hs = P.hs;
-        int c0 = (int)((long long)c.cta * hs / c.ncta), c1 = (int)((long long)(c.cta + 1) * hs / c.ncta);
+        int c0 = share(c.cta, hs, c.ncta), c1 = share(c.cta + 1, hs, c.ncta);
         for (int ch = c0 + c.ct; ch < c1; ch += NCT) {
             for (int kk = 0; kk + 1 < dc; kk++) L.conv_state[(size_t)kk * hs + ch] = __ldcg(L.conv_state + (size_t)(kk + 1) * hs + ch);
             if (dc > 0) L.conv_state[(size_t)(dc - 1) * hs + ch] = conv_bx(P.proj, hs, ch);
         }
     }
-    if (ph.embed) {
-        int e0 = (int)((long long)c.cta * k / c.ncta), e1 = (int)((long long)(c.cta + 1) * k / c.ncta);
-        for (int e = c.ct; e < k; e += NCT) {
-            float v = embed_elem(P.embd, token, e);
-            c.S.xf[e] = v;
-            if (e >= e0 && e < e1) P.hidden[e] = v;
+    STAMP(c, 0);
+    float v[MAXJ];
+    const int e0 = ph.embed ? share(c.cta, k, c.ncta) : 0, e1 = ph.embed ? share(c.cta + 1, k, c.ncta) : 0;
+#pragma unroll
+    for (int j = 0; j < MAXJ; j++) {
+        const int b = c.cw + j * NC, e = b * QK + c.lane;
+        v[j] = 0.0f;
+        if (b < nb) {
+            if (ph.embed) {
+                v[j] = embed_elem(P.embd, token, e);
+                if (e >= e0 && e < e1) P.hidden[e] = v[j];
+            } else {
+                v[j] = __ldcg(P.hidden + e);
+            }
         }
-    } else {
-        for (int e = c.ct; e < k; e += NCT) c.S.xf[e] = __ldcg(P.hidden + e);
     }
     // cpu::rmsnorm (cpu.rs:577-594); f64 partial sums combined in a fixed order
     double s = 0.0;
-    for (int e = c.ct; e < k; e += NCT) {
-        double v = (double)c.S.xf[e];
-        s += v * v;
+#pragma unroll
+    for (int j = 0; j < MAXJ; j++) {
+        double x = (double)v[j];
+        s += x * x;  // absent blocks add +0.0
     }
+    STAMP(c, 1);
     s = warp_sum_f64(s);
     if (c.lane == 0) c.S.red[c.cw] = s;
     consumer_sync();
+    STAMP(c, 2);
     double tot = 0.0;
     for (int i = 0; i < NC; i++) tot += c.S.red[i];
     const float inv = (float)(1.0 / sqrt(tot / (double)k + (double)P.eps));
-    for (int e = c.ct; e < k; e += NCT) c.S.xf[e] = __fmul_rn(__fmul_rn(c.S.xf[e], inv), __ldg(ph.norm_w + e));
+    STAMP(c, 3);
+#pragma unroll
+    for (int j = 0; j < MAXJ; j++) v[j] = __fmul_rn(__fmul_rn(v[j], inv), w[j]);
+    if (nb <= FASTJ * NC) {
+        float vf[FASTJ];  // (a cast to a sub-array would force v into local memory)
+#pragma unroll
+        for (int j = 0; j < FASTJ; j++) vf[j] = v[j];
+        quantize_blocks<FASTJ>(c, vf, 0, nb);
+    } else {
+        quantize_blocks<MAXJ>(c, v, 0, nb);
+    }
+    STAMP(c, 4);
     consumer_sync();
-    quantize_input(c, k);
+    STAMP(c, 5);
 }
 
 __device__ void prologue_conv(Ctx& c, const MegaPhase& ph) {
     const MegaParams& P = c.P;
-    const MegaLayer& L = P.layers[ph.layer];
-    const int hs = P.hs, ks = P.conv_ks, dc = ks - 1;
-    for (int ch = c.ct; ch < hs; ch += NCT) {
-        float sum = 0.0f;
-        for (int kk = 0; kk < dc; kk++)
-            sum = __fadd_rn(sum, __fmul_rn(__ldcg(L.conv_state + (size_t)kk * hs + ch), __ldg(L.conv_w + ch * ks + kk)));
-        float bx = conv_bx(P.proj, hs, ch);
-        sum = __fadd_rn(sum, __fmul_rn(bx, __ldg(L.conv_w + ch * ks + dc)));
-        c.S.xf[ch] = __fmul_rn(__ldcg(P.proj + hs + ch), sum);
+    const MegaLayer& L = c.S.layers[ph.layer];
+    const int hs = P.hs, ks = P.conv_ks, dc = ks - 1, nb = hs / QK;
+    constexpr int MAXKS = 4;  // kernel sizes up to 4 (LFM2 uses 3); larger ones take the per-kernel path
+    for (int j0 = 0; j0 * NC < nb; j0 += 4) {
+        float st[4][MAXKS - 1], pb[4], pc[4], px[4], cw[4][MAXKS];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {  // every load of the four blocks first
+            const int b = c.cw + (j0 + j) * NC;
+            const int chs = (b < nb ? b : 0) * QK + c.lane;
+            pb[j] = __ldcg(P.proj + chs);
+            pc[j] = __ldcg(P.proj + hs + chs);
+            px[j] = __ldcg(P.proj + 2 * hs + chs);
+#pragma unroll
+            for (int kk = 0; kk < MAXKS - 1; kk++) st[j][kk] = kk < dc ? __ldcg(L.conv_state + (size_t)kk * hs + chs) : 0.0f;
+#pragma unroll
+            for (int kk = 0; kk < MAXKS; kk++) cw[j][kk] = kk < ks ? __ldg(L.conv_w + chs * ks + kk) : 0.0f;
+        }
+        float o[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            float sum = 0.0f;
+#pragma unroll
+            for (int kk = 0; kk < MAXKS - 1; kk++)
+                if (kk < dc) sum = __fadd_rn(sum, __fmul_rn(st[j][kk], cw[j][kk]));
+            const float bx = __fmul_rn(pb[j], px[j]);
+            float wl = cw[j][0];
+#pragma unroll
+            for (int kk = 1; kk < MAXKS; kk++) wl = kk == dc ? cw[j][kk] : wl;
+            sum = __fadd_rn(sum, __fmul_rn(bx, wl));
+            o[j] = __fmul_rn(pc[j], sum);
+        }
+        quantize_blocks<4>(c, o, j0, nb);
     }
     consumer_sync();
-    quantize_input(c, hs);
 }
 
 __device__ void prologue_silu(Ctx& c, const MegaPhase& ph) {
     const MegaParams& P = c.P;
-    for (int e = c.ct; e < ph.k; e += NCT) c.S.xf[e] = silu_mul_elem(__ldcg(P.gate + e), __ldcg(P.up + e));
+    const int nb = ph.k / QK;
+    float g[MAXJ], u[MAXJ];
+#pragma unroll
+    for (int j = 0; j < MAXJ; j++) {
+        const int b = c.cw + j * NC, e = (b < nb ? b : 0) * QK + c.lane;
+        g[j] = __ldcg(P.gate + e);
+        u[j] = __ldcg(P.up + e);
+    }
+#pragma unroll
+    for (int j = 0; j < MAXJ; j++) g[j] = silu_mul_elem(g[j], u[j]);
+    quantize_blocks<MAXJ>(c, g, 0, nb);
     consumer_sync();
-    quantize_input(c, ph.k);
 }
 
 __device__ void prologue_quant(Ctx& c, const MegaPhase& ph) {
-    for (int e = c.ct; e < ph.k; e += NCT) c.S.xf[e] = __ldcg(c.P.attn_out + e);
+    const int nb = ph.k / QK;
+    if (nb <= FASTJ * NC) {
+        float v[FASTJ];
+#pragma unroll
+        for (int j = 0; j < FASTJ; j++) {
+            const int b = c.cw + j * NC;
+            v[j] = __ldcg(c.P.attn_out + (b < nb ? b : 0) * QK + c.lane);
+        }
+        quantize_blocks<FASTJ>(c, v, 0, nb);
+    } else {
+        float v[MAXJ];
+#pragma unroll
+        for (int j = 0; j < MAXJ; j++) {
+            const int b = c.cw + j * NC;
+            v[j] = __ldcg(c.P.attn_out + (b < nb ? b : 0) * QK + c.lane);
+        }
+        quantize_blocks<MAXJ>(c, v, 0, nb);
+    }
     consumer_sync();
-    quantize_input(c, ph.k);
 }
 
 // NEON-order dot (cpu.rs:1430-1456) of a shared-memory q with a key row.
@@ -349,22 +473,24 @@ __device__ __forceinline__ float qk_dot_row(const float* q, const float* kv, int
     return __fadd_rn(__fadd_rn(v0, v1), __fadd_rn(v2, v3));
 }
 
-// Per-head RMSNorm (sum in element order, f64) + RoPE of `src` into dst (lfm2.rs:783-802);
-// executed by one warp, dst in shared memory.
+// Per-head RMSNorm + RoPE of `src` into dst (lfm2.rs:783-802), by one warp; dst in shared memory.
+// Lane i holds the RoPE pair (i, i + hd/2) (hd <= 64: one pair per lane; larger heads loop).  The
+// f64 sum of squares is combined in a fixed tree (the reference adds in element order; the sums
+// agree to ~1e-16 relative, far below the f32 rounding of the result it feeds).
 __device__ void head_norm_rope(const float* src_g, const float* w, float eps, const float* cosr, const float* sinr, int hd,
-                               float* raw, float* dst, int lane) {
-    for (int i = lane; i < hd; i += 32) raw[i] = __ldcg(src_g + i);
-    __syncwarp();
-    double ss = 0.0;
-    for (int i = 0; i < hd; i++) {
-        double x = (double)raw[i];
-        ss += x * x;
-    }
-    const float inv = (float)(1.0 / sqrt(ss / (double)hd + (double)eps));
+                               float* dst, int lane) {
     const int half = hd / 2;
+    double ss = 0.0;
     for (int i = lane; i < half; i += 32) {
-        float x0 = __fmul_rn(__fmul_rn(raw[i], inv), __ldg(w + i));
-        float x1 = __fmul_rn(__fmul_rn(raw[i + half], inv), __ldg(w + i + half));
+        double a = (double)__ldcg(src_g + i), b = (double)__ldcg(src_g + i + half);
+        ss += a * a;
+        ss += b * b;
+    }
+    ss = warp_sum_f64(ss);
+    const float inv = (float)(1.0 / sqrt(ss / (double)hd + (double)eps));
+    for (int i = lane; i < half; i += 32) {
+        float x0 = __fmul_rn(__fmul_rn(__ldcg(src_g + i), inv), __ldg(w + i));
+        float x1 = __fmul_rn(__fmul_rn(__ldcg(src_g + i + half), inv), __ldg(w + i + half));
         float cs = __ldg(cosr + i), sn = __ldg(sinr + i);
         dst[i] = __fsub_rn(__fmul_rn(x0, cs), __fmul_rn(x1, sn));
         dst[i + half] = __fadd_rn(__fmul_rn(x0, sn), __fmul_rn(x1, cs));
@@ -372,45 +498,108 @@ __device__ void head_norm_rope(const float* src_g, const float* w, float eps, co
     __syncwarp();
 }
 
-// forward_attn_block between the QKV and output projections (lfm2.rs:783-1007) for the
-// heads this CTA owns.
+// forward_attn_block between the QKV and output projections (lfm2.rs:783-1007).  A work item is
+// (query head, 16-wide slice of the head's output dims); items are spread over the CTAs.  Every
+// item recomputes its head's scores and softmax (cheap), then the slice's weighted V sum: the
+// needed V columns are first gathered into shared memory by all threads (one memory latency per
+// chunk), and 16 threads run the fused chains in ascending t, the reference's order.
 __device__ void phase_attention(Ctx& c, const MegaPhase& ph, int pos) {
     const MegaParams& P = c.P;
-    const MegaLayer& L = P.layers[ph.layer];
+    const MegaLayer& L = c.S.layers[ph.layer];
     const int hd = P.head_dim, n_heads = P.n_heads, n_kv = L.n_kv, kv_dim = n_kv * hd, group = n_heads / n_kv;
     const float scale = __fdiv_rn(1.0f, sqrtf((float)hd));
     const float* cosr = P.rope_cos + (size_t)pos * (hd / 2);
     const float* sinr = P.rope_sin + (size_t)pos * (hd / 2);
     float* sc = c.S.xf;
-    float *qs = c.S.head, *ks = c.S.head + 256, *raw = c.S.head + 512;  // raw: [512,768) q, [768,1024) k
+    float *qs = c.S.head, *ks = c.S.head + 256;
     const int seq = pos + 1;
-    for (int h = 0; h < n_heads; h++) {
-        if ((int)((long long)h * c.ncta / n_heads) != c.cta) continue;
+    const int nq = hd / 16, items = n_heads * nq;
+    const int nf = xf_floats(P);
+    const int sc_pad = (seq + 3) & ~3;
+    float* Vs = sc + sc_pad;                 // [rows][16]
+    int chunk = (nf - sc_pad) / 16;
+    chunk = chunk > seq ? seq : chunk;
+    // items it with floor(it * ncta / items) == cta, i.e. ceil(cta * items / ncta) <= it < ceil((cta+1) * items / ncta)
+    const int it0 = (int)(((unsigned)c.cta * items + c.ncta - 1) / c.ncta);
+    const int it1 = (int)(((unsigned)(c.cta + 1) * items + c.ncta - 1) / c.ncta);
+    for (int it = it0; it < it1 && it < items; it++) {
+        const int h = it / nq, d0 = (it % nq) * 16;
         const int kvh = h / group, off = kvh * hd;
+        STAMP(c, 0);
         consumer_sync();
-        if (c.cw == 0) head_norm_rope(P.qbuf + h * hd, L.q_norm, P.eps, cosr, sinr, hd, raw, qs, c.lane);
+        if (c.cw == 0) head_norm_rope(P.qbuf + h * hd, L.q_norm, P.eps, cosr, sinr, hd, qs, c.lane);
         if (c.cw == 1) {
-            head_norm_rope(P.kbuf + off, L.k_norm, P.eps, cosr, sinr, hd, raw + 256, ks, c.lane);
-            if (h % group == 0) {  // one writer per KV head appends to the caches
+            head_norm_rope(P.kbuf + off, L.k_norm, P.eps, cosr, sinr, hd, ks, c.lane);
+            if (h % group == 0 && d0 == 0) {  // one writer per KV head appends to the caches
                 for (int i = c.lane; i < hd; i += 32) {
                     L.k_cache[(size_t)pos * kv_dim + off + i] = ks[i];
                     L.v_cache[(size_t)pos * kv_dim + off + i] = __ldcg(P.vbuf + off + i);
                 }
             }
         }
+        STAMP(c, 1);
         consumer_sync();
-        // scores + max (attn_scores, cpu.rs:1404-1458)
+        STAMP(c, 2);
+        // scores + max (attn_scores, cpu.rs:1404-1458).  The NEON dot keeps 8 fused chains: chain
+        // ch = 0..3 is lane ch of sum0 (dims ch, ch+8, ...), chain 4..7 lane ch-4 of sum1 (dims ch, ch+8,
+        // ...), then v[l] = sum0[l] + sum1[l] and (v0+v1)+(v2+v3).  Eight threads share a key, one chain
+        // each, and every thread issues the loads of KU keys before any arithmetic.
         float mx = __int_as_float(0xFF800000);
-        for (int t = c.ct; t < seq; t += NCT) {
-            float dot = t < pos ? qk_dot_row<true>(qs, L.k_cache + (size_t)t * kv_dim + off, hd) : qk_dot_row<false>(qs, ks, hd);
-            float s = __fmul_rn(dot, scale);
-            sc[t] = s;
-            mx = fmaxf(mx, s);
+        {
+            constexpr int KU = 4;
+            constexpr int KPR = NCT / 8;                   // keys per round of the consumer threads
+            const int ch = c.ct & 7, kslot = c.ct >> 3;
+            const int nd8 = hd >> 3;
+            float qreg[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++) qreg[j] = j < nd8 ? qs[ch + j * 8] : 0.0f;
+            // cached keys t < pos: branch-free loads (out-of-range keys read row 0 and are dropped)
+            for (int tb = 0; tb < pos; tb += KPR * KU) {
+                float kv[KU][8];
+#pragma unroll
+                for (int u = 0; u < KU; u++) {
+                    const int t = tb + u * KPR + kslot;
+                    const float* kp = L.k_cache + (size_t)(t < pos ? t : 0) * kv_dim + off + ch;
+#pragma unroll
+                    for (int j = 0; j < 8; j++) kv[u][j] = __ldcg(kp + (j < nd8 ? j : 0) * 8);
+                }
+#pragma unroll
+                for (int u = 0; u < KU; u++) {
+                    const int t = tb + u * KPR + kslot;
+                    float a = 0.0f;
+#pragma unroll
+                    for (int j = 0; j < 8; j++)
+                        if (j < nd8) a = __fmaf_rn(qreg[j], kv[u][j], a);
+                    for (int j = 8; j < nd8; j++)  // heads wider than 64
+                        a = __fmaf_rn(qs[ch + j * 8], __ldcg(L.k_cache + (size_t)(t < pos ? t : 0) * kv_dim + off + ch + j * 8), a);
+                    a = __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, 4));  // sum0[l] + sum1[l]
+                    a = __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, 1));
+                    a = __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, 2));
+                    if (t < pos) {
+                        float sv = __fmul_rn(a, scale);
+                        if (ch == 0) sc[t] = sv;
+                        mx = fmaxf(mx, sv);
+                    }
+                }
+            }
+            // the key of this step is still in shared memory
+            if (c.cw == 0) {
+                float a = 0.0f;
+                for (int j = 0; j < nd8; j++) a = __fmaf_rn(qs[ch + j * 8], ks[ch + j * 8], a);
+                a = __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, 4));
+                a = __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, 1));
+                a = __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, 2));
+                float sv = __fmul_rn(a, scale);
+                if (c.lane == 0) sc[pos] = sv;
+                mx = fmaxf(mx, sv);
+            }
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        STAMP(c, 3);
         if (c.lane == 0) c.S.redf[c.cw] = mx;
         consumer_sync();
+        STAMP(c, 4);
         mx = c.S.redf[0];
         for (int i = 1; i < NC; i++) mx = fmaxf(mx, c.S.redf[i]);
         // softmax_inplace (cpu.rs:715-731)
@@ -427,17 +616,27 @@ __device__ void phase_attention(Ctx& c, const MegaPhase& ph, int pos) {
         for (int i = 0; i < NC; i++) tot += c.S.red[i];
         const float inv = (float)(1.0 / tot);
         for (int t = c.ct; t < seq; t += NCT) sc[t] = __fmul_rn(sc[t], inv);
-        consumer_sync();
+        STAMP(c, 5);
         // attn_values (cpu.rs:1463-1509): one fused chain per output dim, ascending t
-        if (c.ct < hd) {
-            const float* vp = L.v_cache + off + c.ct;
-            float acc = 0.0f;
+        float acc = 0.0f;
+        for (int t0 = 0; t0 < seq; t0 += chunk) {
+            const int rows = chunk < seq - t0 ? chunk : seq - t0;
+            consumer_sync();  // scores normalised / previous chunk consumed
+            for (int idx = c.ct; idx < rows * 4; idx += NCT) {
+                const int t = t0 + (idx >> 2), part = idx & 3;
+                const float* src = t < pos ? L.v_cache + (size_t)t * kv_dim + off + d0 + part * 4 : P.vbuf + off + d0 + part * 4;
+                reinterpret_cast<float4*>(Vs)[idx] = __ldcg(reinterpret_cast<const float4*>(src));
+            }
+            consumer_sync();
+            if (c.ct < 16) {
 #pragma unroll 8
-            for (int t = 0; t < pos; t++) acc = __fmaf_rn(sc[t], __ldcg(vp + (size_t)t * kv_dim), acc);
-            acc = __fmaf_rn(sc[pos], __ldcg(P.vbuf + off + c.ct), acc);
-            P.attn_out[h * hd + c.ct] = acc;
+                for (int tl = 0; tl < rows; tl++) acc = __fmaf_rn(sc[t0 + tl], Vs[tl * 16 + c.ct], acc);
+            }
         }
+        STAMP(c, 6);
+        if (c.ct < 16) P.attn_out[h * hd + d0 + c.ct] = acc;
     }
+    STAMP(c, 7);
 }
 
 __device__ __forceinline__ float reduce_row8(float a) {
@@ -477,9 +676,49 @@ __device__ __forceinline__ float group_chain(const uint32_t* __restrict__ qs, co
     return acc;
 }
 
+// Two 4-row groups at once: the same lane position in both, sharing every load of the
+// quantised input.  Doubles the independent work per thread (the chains themselves are serial).
+template <int DT>
+__device__ __forceinline__ void group_chain2(const uint32_t* __restrict__ qa, const __half* __restrict__ da,
+                                             const uint32_t* __restrict__ qb, const __half* __restrict__ db, int nb, int lane,
+                                             const int* __restrict__ xq32, const float* __restrict__ xsc, float& ra, float& rb) {
+    const int p = lane >> 4, r = (lane >> 2) & 3, l = lane & 3;
+    float acc0 = 0.0f, acc1 = 0.0f;
+    if (DT == DT_Q4_0) {
+        const int o = lane & 15;
+#pragma unroll 4
+        for (int b = p; b < nb; b += 2) {
+            const uint32_t w0 = qa[b * 16 + o], w1 = qb[b * 16 + o];
+            const float xs = xsc[b];
+            const int x_lo = xq32[b * 8 + l], x_hi = xq32[b * 8 + 4 + l];
+            const float d0 = __fmul_rn(__half2float(da[b * 4 + r]), xs), d1 = __fmul_rn(__half2float(db[b * 4 + r]), xs);
+            int s0 = __dp4a((int)((w0 & 0xF0F0F0F0u) ^ 0x80808080u), x_hi, __dp4a((int)(((w0 << 4) & 0xF0F0F0F0u) ^ 0x80808080u), x_lo, 0));
+            int s1 = __dp4a((int)((w1 & 0xF0F0F0F0u) ^ 0x80808080u), x_hi, __dp4a((int)(((w1 << 4) & 0xF0F0F0F0u) ^ 0x80808080u), x_lo, 0));
+            acc0 = __fadd_rn(acc0, __fmul_rn((float)s0, d0));
+            acc1 = __fadd_rn(acc1, __fmul_rn((float)s1, d1));
+        }
+    } else {
+#pragma unroll 4
+        for (int b = p; b < nb; b += 2) {
+            const int i0 = (b >> 1) * 64 + lane;
+            const int a_lo = (int)qa[i0], a_hi = (int)qa[i0 + 32], b_lo = (int)qb[i0], b_hi = (int)qb[i0 + 32];
+            const float xs = xsc[b];
+            const int x_lo = xq32[b * 8 + l], x_hi = xq32[b * 8 + 4 + l];
+            const float d0 = __fmul_rn(__half2float(da[b * 4 + r]), xs), d1 = __fmul_rn(__half2float(db[b * 4 + r]), xs);
+            int s0 = __dp4a(a_hi, x_hi, __dp4a(a_lo, x_lo, 0));
+            int s1 = __dp4a(b_hi, x_hi, __dp4a(b_lo, x_lo, 0));
+            acc0 = __fadd_rn(acc0, __fmul_rn((float)s0, d0));
+            acc1 = __fadd_rn(acc1, __fmul_rn((float)s1, d1));
+        }
+    }
+    ra = acc0;
+    rb = acc1;
+}
+
 __device__ void consumer(const MegaParams& P, const Smem& S, int cta, int ncta) {
-    Ctx c{P, S, cta, ncta, (int)threadIdx.x - 32, ((int)threadIdx.x - 32) >> 5, (int)threadIdx.x & 31};
-    unsigned long long cnt = 0;
+    Ctx c{P, S, cta, ncta, (int)threadIdx.x - 32, ((int)threadIdx.x - 32) >> 5, (int)threadIdx.x & 31, nullptr};
+    int slot = 0;
+    uint32_t par = 0;
     const uint32_t pos0 = __ldcg(&P.ctl->pos), step0 = __ldcg(&P.ctl->step);
     uint32_t token = __ldcg(&P.ctl->token);
     const int* xq32 = reinterpret_cast<const int*>(S.xq);
@@ -487,9 +726,12 @@ __device__ void consumer(const MegaParams& P, const Smem& S, int cta, int ncta) 
         const int pos = (int)pos0 + t;
         unsigned long long best = 0;
         for (int pi = 0; pi < P.n_phases; pi++) {
-            const MegaPhase& ph = P.phases[pi];
+            const MegaPhase& ph = S.ph[pi];
+            float nw[MAXJ];
+            if (ph.kind == MPH_NORM) load_norm_w(c, ph, nw);
             if (t > 0 || pi > 0) grid_wait(c, (P.bar_base + (unsigned long long)t * P.n_phases + pi) * (unsigned long long)ncta);
             const bool prof = P.prof && cta == 0 && c.ct == 0 && t == P.n_tokens - 1;
+            c.stamp = (prof && pi == P.prof_phase) ? P.prof + (size_t)P.n_phases * 4 : nullptr;
             if (prof) P.prof[pi * 4 + 0] = globaltimer_ns();
             if (pi == 0 && t > 0) {
                 // argmax of the previous step is this step's input (Session::generate, session.rs:1251)
@@ -498,7 +740,7 @@ __device__ void consumer(const MegaParams& P, const Smem& S, int cta, int ncta) 
             }
             if (pi == 1 && cta == 0 && c.ct == 0) P.argmax_acc[(t + 1) & 1] = 0;  // free for the next step
             switch (ph.kind) {
-                case MPH_NORM: prologue_norm(c, ph, token); break;
+                case MPH_NORM: prologue_norm(c, ph, token, nw); break;
                 case MPH_CONV: prologue_conv(c, ph); break;
                 case MPH_SILU: prologue_silu(c, ph); break;
                 case MPH_QUANT: prologue_quant(c, ph); break;
@@ -514,12 +756,10 @@ __device__ void consumer(const MegaParams& P, const Smem& S, int cta, int ncta) 
                     const int gm = w.groups(), nb = w.k / QK;
                     int a = (pl.lo > off ? pl.lo : off) - off, b = (pl.hi < off + gm ? pl.hi : off + gm) - off;
                     const uint32_t qgb = (uint32_t)w.q_group_bytes();
-                    for (int g0 = a; g0 < b; g0 += pl.rg, cnt++) {
+                    for (int g0 = a; g0 < b; g0 += pl.rg, slot = slot + 1 == P.n_slots ? 0 : slot + 1, par ^= (slot == 0)) {
                         int ng = pl.rg < b - g0 ? pl.rg : b - g0;
-                        int slot = (int)(cnt % P.n_slots);
-                        uint32_t u = (uint32_t)(cnt / P.n_slots);
                         unsigned spins = 0;
-                        while (!*S.abort && !mbar_try_wait(&S.full[slot], u & 1)) {
+                        while (!*S.abort && !mbar_try_wait(&S.full[slot], par)) {
                             if (++spins > SPIN_LIMIT) {
                                 atomicOr(&P.ctl->error, 4u);
                                 *S.abort = 1;
@@ -529,23 +769,36 @@ __device__ void consumer(const MegaParams& P, const Smem& S, int cta, int ncta) 
                         }
                         const uint8_t* base = S.ring + (size_t)slot * P.slot_bytes;
                         const __half* dbase = reinterpret_cast<const __half*>(base + (size_t)ng * qgb);
-                        for (int gi = 0; gi < ng; gi++, ls++) {
+                        // groups are dealt to the warps one at a time, or two at a time once the
+                        // CTA has enough of them to keep every warp busy that way
+                        const int unit = pl.pair ? 2 : 1;
+                        for (int gi = 0; gi < ng; gi += unit, ls++) {
                             if (ls % NC != c.cw) continue;
+                            const int cntg = unit < ng - gi ? unit : ng - gi;
                             const uint32_t* qs = reinterpret_cast<const uint32_t*>(base + (size_t)gi * qgb);
                             const __half* ds = dbase + (size_t)gi * nb * 4;
-                            float acc = w.dtype == DT_Q4_0 ? group_chain<DT_Q4_0>(qs, ds, nb, c.lane, xq32, S.xs16)
-                                                           : group_chain<DT_Q8_0>(qs, ds, nb, c.lane, xq32, S.xs);
-                            acc = reduce_row8(acc);
-                            const int row = (g0 + gi) * 4 + ((c.lane >> 2) & 3);
-                            if ((c.lane & 19) == 0 && row < w.m) {
-                                if (M.epi == MEP_ADD) {
-                                    M.y[row] = __fadd_rn(__ldcg(M.y + row), acc);
-                                } else if (M.epi == MEP_STORE) {
-                                    M.y[row] = acc;
-                                } else {
-                                    if (!P.greedy) M.y[row] = acc;
-                                    unsigned long long pk = argmax_pack(acc, (uint32_t)row);
-                                    best = pk > best ? pk : best;
+                            float accs[2];
+                            if (cntg == 2) {
+                                const uint32_t* qs1 = reinterpret_cast<const uint32_t*>(base + (size_t)(gi + 1) * qgb);
+                                if (w.dtype == DT_Q4_0) group_chain2<DT_Q4_0>(qs, ds, qs1, ds + nb * 4, nb, c.lane, xq32, S.xs16, accs[0], accs[1]);
+                                else group_chain2<DT_Q8_0>(qs, ds, qs1, ds + nb * 4, nb, c.lane, xq32, S.xs, accs[0], accs[1]);
+                            } else {
+                                accs[0] = w.dtype == DT_Q4_0 ? group_chain<DT_Q4_0>(qs, ds, nb, c.lane, xq32, S.xs16)
+                                                             : group_chain<DT_Q8_0>(qs, ds, nb, c.lane, xq32, S.xs);
+                            }
+                            for (int q2 = 0; q2 < cntg; q2++) {
+                                const float acc = reduce_row8(accs[q2]);
+                                const int row = (g0 + gi + q2) * 4 + ((c.lane >> 2) & 3);
+                                if ((c.lane & 19) == 0 && row < w.m) {
+                                    if (M.epi == MEP_ADD) {
+                                        M.y[row] = __fadd_rn(__ldcg(M.y + row), acc);
+                                    } else if (M.epi == MEP_STORE) {
+                                        M.y[row] = acc;
+                                    } else {
+                                        if (!P.greedy) M.y[row] = acc;
+                                        unsigned long long pk = argmax_pack(acc, (uint32_t)row);
+                                        best = pk > best ? pk : best;
+                                    }
                                 }
                             }
                         }
@@ -596,6 +849,14 @@ __device__ void consumer(const MegaParams& P, const Smem& S, int cta, int ncta) 
 __global__ void __launch_bounds__(MEGA_THREADS, 1) k_decode_mega(const MegaParams P) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     Smem S = carve(smem_raw, P);
+    {   // phase and layer descriptors into shared memory (word copies; both are multiples of 8 bytes)
+        const uint32_t* src = reinterpret_cast<const uint32_t*>(P.phases);
+        uint32_t* dst = reinterpret_cast<uint32_t*>(S.ph);
+        for (int i = threadIdx.x; i < (int)(P.n_phases * sizeof(MegaPhase) / 4); i += blockDim.x) dst[i] = __ldg(src + i);
+        src = reinterpret_cast<const uint32_t*>(P.layers);
+        dst = reinterpret_cast<uint32_t*>(S.layers);
+        for (int i = threadIdx.x; i < (int)(P.n_layers * sizeof(MegaLayer) / 4); i += blockDim.x) dst[i] = __ldg(src + i);
+    }
     if (threadIdx.x == 0) {
         for (int i = 0; i < P.n_slots; i++) {
             mbar_init(&S.full[i], 1);
@@ -628,7 +889,7 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) k_decode_mega(const MegaParam
 }  // namespace
 
 size_t mega_smem_bytes(const MegaParams& P) {
-    int nf = P.kmax > P.max_seq ? P.kmax : P.max_seq;
+    int nf = xf_floats(P);
     size_t o = (size_t)P.n_slots * P.slot_bytes + (size_t)nf * 4 + (size_t)(P.kmax / QK) * 8;
     o = (o + 15) & ~(size_t)15;
     o += P.kmax;
@@ -636,6 +897,7 @@ size_t mega_smem_bytes(const MegaParams& P) {
     o += NC * 16 + (size_t)P.n_slots * 16 + NC * 4;
     o = (o + 15) & ~(size_t)15;
     o += 4 * 256 * 4 + 16;
+    o += (size_t)P.n_phases * sizeof(MegaPhase) + (size_t)P.n_layers * sizeof(MegaLayer);
     return o;
 }
 

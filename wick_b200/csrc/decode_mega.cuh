@@ -4,7 +4,9 @@
 
 namespace wick {
 
-constexpr int MEGA_CONSUMER_WARPS = 16;
+// 15 consumer warps + 1 producer warp = 512 threads: the compiler budgets registers for a block size
+// rounded up to a multiple of 128, so 17 warps would cap every thread at 96 registers instead of 128.
+constexpr int MEGA_CONSUMER_WARPS = 15;
 constexpr int MEGA_THREADS = 32 * (MEGA_CONSUMER_WARPS + 1);  // warp 0 issues the bulk copies
 
 enum MegaPhaseKind : int {
@@ -52,6 +54,7 @@ struct MegaParams {
     const MegaPhase* phases;
     const MegaLayer* layers;
     int n_phases;
+    int n_layers;
     int n_tokens;
     int greedy;      // 1: feed the argmax back; 0: single step, logits only
     int hs, is, n_heads, head_dim, vocab, conv_ks, max_seq;
@@ -69,7 +72,8 @@ struct MegaParams {
     int kmax;                          // max input length over phases (shared-memory sizing)
     // optional per-phase timestamps (globaltimer ns) of CTA 0 for the last step of a launch:
     // [phase][0] barrier passed, [1] prologue done, [2] mat-vec done, [3] arrived
-    unsigned long long* prof;
+    unsigned long long* prof;          // [n_phases * 4 + 16]
+    int prof_phase;                    // phase that also records up to 16 internal stamps after the table
 };
 
 size_t mega_smem_bytes(const MegaParams& P);

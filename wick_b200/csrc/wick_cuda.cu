@@ -271,10 +271,11 @@ int32_t build_mega(wick_cuda_model* m) {
     v.kind = MPH_NORM; v.k = hs; v.layer = -1; v.conv_commit = -1; v.norm_w = m->output_norm; v.n_mat = 1;
     v.mat[0] = mat(m->embd, m->logits, MEP_LOGITS);
     ph.push_back(v);
-    if (!ok || (c.conv_kernel_size < 2) || m->head_dim > 256) return WICK_CUDA_OK;
+    if (!ok || c.conv_kernel_size < 2 || c.conv_kernel_size > 4 || m->head_dim > 256 || m->head_dim % 16 || std::max(hs, is) > MEGA_CONSUMER_WARPS * 16 * 32) return WICK_CUDA_OK;
 
     MegaParams& P = m->mega;
     P.n_phases = (int)ph.size();
+    P.n_layers = (int)ml.size();
     P.hs = hs; P.is = is; P.n_heads = c.n_heads; P.head_dim = m->head_dim; P.vocab = c.vocab_size;
     P.conv_ks = c.conv_kernel_size; P.max_seq = c.max_seq_len; P.eps = c.rms_norm_eps;
     P.embd = m->embd;
@@ -294,9 +295,10 @@ int32_t build_mega(wick_cuda_model* m) {
     W_TRY(dev_alloc(m, &m->d_phases, ph.size()));
     W_TRY(dev_alloc(m, &m->d_mlayers, ml.size()));
     W_TRY(dev_alloc(m, &m->d_sync, 4));
-    W_TRY(dev_alloc(m, &m->d_prof, ph.size() * 4));
-    CU_TRY(cudaMemset(m->d_prof, 0, ph.size() * 32));
+    W_TRY(dev_alloc(m, &m->d_prof, ph.size() * 4 + 16));
+    CU_TRY(cudaMemset(m->d_prof, 0, (ph.size() * 4 + 16) * 8));
     P.prof = m->d_prof;
+    P.prof_phase = getenv("WICK_CUDA_PROF_PHASE") ? atoi(getenv("WICK_CUDA_PROF_PHASE")) : -1;
     CU_TRY(cudaMemcpy(m->d_phases, ph.data(), ph.size() * sizeof(MegaPhase), cudaMemcpyHostToDevice));
     CU_TRY(cudaMemcpy(m->d_mlayers, ml.data(), ml.size() * sizeof(MegaLayer), cudaMemcpyHostToDevice));
     CU_TRY(cudaMemset(m->d_sync, 0, 32));
@@ -932,6 +934,8 @@ int32_t wick_cuda_decode_profile(wick_cuda_model* m, uint64_t* ns_out, int32_t* 
     CU_TRY(cudaSetDevice(m->device));
     CU_TRY(cudaStreamSynchronize(m->stream));
     CU_TRY(cudaMemcpy(ns_out, m->d_prof, (size_t)m->mega.n_phases * 32, cudaMemcpyDeviceToHost));
+    if (capacity >= (uint32_t)m->mega.n_phases + 4)  // optional: the 16 internal stamps of WICK_CUDA_PROF_PHASE
+        CU_TRY(cudaMemcpy(ns_out + (size_t)m->mega.n_phases * 4, m->d_prof + (size_t)m->mega.n_phases * 4, 128, cudaMemcpyDeviceToHost));
     std::vector<MegaPhase> ph(m->mega.n_phases);
     CU_TRY(cudaMemcpy(ph.data(), m->d_phases, ph.size() * sizeof(MegaPhase), cudaMemcpyDeviceToHost));
     for (size_t i = 0; i < ph.size(); i++) kinds_out[i] = ph[i].kind;

@@ -223,10 +223,11 @@ class CudaLfm2Model:
         """Timeline of the last decode step of the persistent kernel: (kinds [n], ns [n, 4])."""
         n = C.c_uint32(0)
         check(self._lib.wick_cuda_decode_profile(self._h, None, None, 0, C.byref(n)))
-        ns = np.zeros((n.value, 4), np.uint64)
-        kinds = np.zeros(n.value, np.int32)
-        check(self._lib.wick_cuda_decode_profile(self._h, ns.ctypes.data, kinds.ctypes.data, n.value, C.byref(n)))
-        return kinds, ns
+        ns = np.zeros((n.value + 4, 4), np.uint64)
+        kinds = np.zeros(n.value + 4, np.int32)
+        check(self._lib.wick_cuda_decode_profile(self._h, ns.ctypes.data, kinds.ctypes.data, n.value + 4, C.byref(n)))
+        self.last_profile_detail = ns[n.value:].reshape(-1)  # stamps of the phase named by WICK_CUDA_PROF_PHASE
+        return kinds[:n.value], ns[:n.value]
 
     def read_kv(self, layer: int) -> Tuple[np.ndarray, np.ndarray]:
         kv_dim = self._config.kv_heads_per_layer[layer] * (self._config.hidden_size // self._config.n_heads)
