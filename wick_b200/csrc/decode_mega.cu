@@ -29,6 +29,9 @@ namespace {
 
 constexpr int NC = MEGA_CONSUMER_WARPS;
 constexpr int NCT = NC * 32;
+constexpr int TEAM_WARPS = MEGA_TEAM_WARPS;  // consumer warps work on ring slots in teams
+constexpr int NTEAMS = MEGA_TEAMS;
+constexpr int TEAM_THREADS = TEAM_WARPS * 32;
 constexpr unsigned SPIN_LIMIT = 1u << 22;  // x ~0.25-1 us of back-off per iteration
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -144,16 +147,13 @@ __device__ __forceinline__ int share(int i, int n, int d) { return (int)((unsign
 
 // Work split of one phase for one CTA: a contiguous run [lo, hi) of the phase's row groups
 // (all matrices of the phase concatenated), cut into stages of at most `rg` groups (one ring
-// slot each).  EVERY consumer warp waits for EVERY stage in order and releases it, so a warp
-// can never wait two uses of a slot ahead (mbarrier parity would alias); inside a stage the
-// groups are dealt to the warps round-robin by their running index in the phase.
+// slot each).  Stages are dealt to the consumer teams round-robin through their ring slot.
 struct Plan {
     int lo, hi, rg;
-    bool pair;
 };
 __device__ __forceinline__ Plan plan_phase(const MegaPhase& ph, int cta, int ncta, int slot_bytes) {
     int gt = 0, gb = 1;
-    for (int i = 0; i < ph.n_mat; i++) {
+    for (int i = 0; i < (ph.pair ? 1 : ph.n_mat); i++) {  // a paired phase is split by the rows of ONE of its matrices
         gt += ph.mat[i].w.groups();
         int b = (int)(ph.mat[i].w.q_group_bytes() + ph.mat[i].w.d_group_bytes());
         gb = b > gb ? b : gb;
@@ -162,9 +162,10 @@ __device__ __forceinline__ Plan plan_phase(const MegaPhase& ph, int cta, int nct
     p.lo = share(cta, gt, ncta);
     p.hi = share(cta + 1, gt, ncta);
     int cap = slot_bytes / gb;
-    cap = cap < 1 ? 1 : cap;
-    p.pair = cap >= 2 && (p.hi - p.lo) > NC;
-    p.rg = p.pair ? (cap >= 4 ? 4 : 2) : (cap > 2 ? 2 : cap);
+    cap = cap < 1 ? 1 : (cap > 4 ? 4 : cap);
+    int rg = (p.hi - p.lo + NTEAMS - 1) / NTEAMS;  // spread a small phase over all teams
+    rg = rg < 1 ? 1 : rg;
+    p.rg = rg > cap ? cap : rg;
     return p;
 }
 
@@ -180,28 +181,32 @@ __device__ unsigned long long producer(const MegaParams& P, const Smem& S, int c
             const MegaPhase& ph = S.ph[pi];
             if (ph.kind == MPH_ATTN) continue;
             Plan pl = plan_phase(ph, cta, ncta, P.slot_bytes);
+            // stage list: per matrix its chunks in order; a paired phase alternates the two matrices chunk by chunk
+            const int n_seq = ph.pair ? 1 : ph.n_mat, n_alt = ph.pair ? 2 : 1;
             int off = 0;
-            for (int mi = 0; mi < ph.n_mat; mi++) {
-                const DevWeight& w = ph.mat[mi].w;
-                const int gm = w.groups();
+            for (int mi = 0; mi < n_seq; mi++) {
+                const int gm = ph.mat[mi].w.groups();
                 int a = (pl.lo > off ? pl.lo : off) - off, b = (pl.hi < off + gm ? pl.hi : off + gm) - off;
-                const uint32_t qgb = (uint32_t)w.q_group_bytes(), dgb = (uint32_t)w.d_group_bytes();
-                for (int g0 = a; g0 < b; g0 += pl.rg, cnt++, slot = slot + 1 == P.n_slots ? 0 : slot + 1, par ^= (slot == 0)) {
-                    int ng = pl.rg < b - g0 ? pl.rg : b - g0;
-                    unsigned spins = 0;
-                    while (!mbar_try_wait(&S.empty[slot], par ^ 1)) {
-                        if (*S.abort) return cnt;
-                        if (++spins > SPIN_LIMIT) {
-                            atomicOr(&P.ctl->error, 2u);
-                            *S.abort = 1;
-                            return cnt;
+                for (int g0 = a; g0 < b; g0 += pl.rg) {
+                    for (int alt = 0; alt < n_alt; alt++, cnt++, slot = slot + 1 == P.n_slots ? 0 : slot + 1, par ^= (slot == 0)) {
+                        const DevWeight& w = ph.mat[mi + alt].w;
+                        const uint32_t qgb = (uint32_t)w.q_group_bytes(), dgb = (uint32_t)w.d_group_bytes();
+                        int ng = pl.rg < b - g0 ? pl.rg : b - g0;
+                        unsigned spins = 0;
+                        while (!mbar_try_wait(&S.empty[slot], par ^ 1)) {
+                            if (*S.abort) return cnt;
+                            if (++spins > SPIN_LIMIT) {
+                                atomicOr(&P.ctl->error, 2u);
+                                *S.abort = 1;
+                                return cnt;
+                            }
+                            __nanosleep(64);
                         }
-                        __nanosleep(64);
+                        uint8_t* dst = S.ring + (size_t)slot * P.slot_bytes;
+                        mbar_expect_tx(&S.full[slot], ng * (qgb + dgb));
+                        bulk_g2s(dst, w.q + (size_t)g0 * qgb, ng * qgb, &S.full[slot], pol);
+                        bulk_g2s(dst + (size_t)ng * qgb, (const uint8_t*)w.d + (size_t)g0 * dgb, ng * dgb, &S.full[slot], pol);
                     }
-                    uint8_t* dst = S.ring + (size_t)slot * P.slot_bytes;
-                    mbar_expect_tx(&S.full[slot], ng * (qgb + dgb));
-                    bulk_g2s(dst, w.q + (size_t)g0 * qgb, ng * qgb, &S.full[slot], pol);
-                    bulk_g2s(dst + (size_t)ng * qgb, (const uint8_t*)w.d + (size_t)g0 * dgb, ng * dgb, &S.full[slot], pol);
                 }
                 off += gm;
             }
@@ -431,7 +436,7 @@ __device__ void prologue_quant(Ctx& c, const MegaPhase& ph) {
 #pragma unroll
         for (int j = 0; j < FASTJ; j++) {
             const int b = c.cw + j * NC;
-            v[j] = __ldcg(c.P.attn_out + (b < nb ? b : 0) * QK + c.lane);
+            v[j] = __ldcg(ph.src + (b < nb ? b : 0) * QK + c.lane);
         }
         quantize_blocks<FASTJ>(c, v, 0, nb);
     } else {
@@ -439,7 +444,7 @@ __device__ void prologue_quant(Ctx& c, const MegaPhase& ph) {
 #pragma unroll
         for (int j = 0; j < MAXJ; j++) {
             const int b = c.cw + j * NC;
-            v[j] = __ldcg(c.P.attn_out + (b < nb ? b : 0) * QK + c.lane);
+            v[j] = __ldcg(ph.src + (b < nb ? b : 0) * QK + c.lane);
         }
         quantize_blocks<MAXJ>(c, v, 0, nb);
     }
@@ -646,79 +651,92 @@ __device__ __forceinline__ float reduce_row8(float a) {
     return a;
 }
 
-// One 4-row group from a ring slot: lane = p*16 + r*4 + l owns chain (p, l) of row r.
-template <int DT>
-__device__ __forceinline__ float group_chain(const uint32_t* __restrict__ qs, const __half* __restrict__ ds, int nb, int lane,
-                                             const int* __restrict__ xq32, const float* __restrict__ xsc) {
-    const int p = lane >> 4, r = (lane >> 2) & 3, l = lane & 3;
-    float acc = 0.0f;
-    if (DT == DT_Q4_0) {
-        const uint32_t* qp = qs + (lane & 15);
-#pragma unroll 4
-        for (int b = p; b < nb; b += 2) {
-            uint32_t w = qp[b * 16];
-            float d = __fmul_rn(__half2float(ds[b * 4 + r]), xsc[b]);  // xsc = scale / 16
-            int hi = (int)((w & 0xF0F0F0F0u) ^ 0x80808080u);
-            int lo = (int)(((w << 4) & 0xF0F0F0F0u) ^ 0x80808080u);
-            int s16 = __dp4a(hi, xq32[b * 8 + 4 + l], __dp4a(lo, xq32[b * 8 + l], 0));  // 16 * lane sum
-            acc = __fadd_rn(acc, __fmul_rn((float)s16, d));
-        }
-    } else {
-        const uint32_t* qp = qs + lane;
-#pragma unroll 4
-        for (int b = p; b < nb; b += 2) {
-            int w_lo = (int)qp[(b >> 1) * 64], w_hi = (int)qp[(b >> 1) * 64 + 32];
-            float d = __fmul_rn(__half2float(ds[b * 4 + r]), xsc[b]);
-            int s = __dp4a(w_hi, xq32[b * 8 + 4 + l], __dp4a(w_lo, xq32[b * 8 + l], 0));
-            acc = __fadd_rn(acc, __fmul_rn((float)s, d));
-        }
-    }
-    return acc;
+// The mat-vec over one ring slot is done by a TEAM of three consumer warps in two steps.
+//  1. products: every (row, block, lane-word) term  float(p) * (f16(d_w) * d_x)  is independent of
+//     every other one, so the team's 96 threads compute them all in parallel and write each one
+//     over the weight word it came from (same size: 4 bytes; for Q8_0 over the low word of the pair);
+//  2. chains: one warp per 4-row group, lane = p*16 + r*4 + l, adds its chain's products in block
+//     order (the only part of the reference's arithmetic that is serial), then the three shuffle-adds.
+// Both steps touch shared memory as 32 consecutive words per warp access (no bank conflicts).
+__device__ __forceinline__ void team_sync(int team) {
+    asm volatile("bar.sync %0, %1;" ::"r"(2 + team), "n"(TEAM_THREADS) : "memory");
 }
 
-// Two 4-row groups at once: the same lane position in both, sharing every load of the
-// quantised input.  Doubles the independent work per thread (the chains themselves are serial).
-template <int DT>
-__device__ __forceinline__ void group_chain2(const uint32_t* __restrict__ qa, const __half* __restrict__ da,
-                                             const uint32_t* __restrict__ qb, const __half* __restrict__ db, int nb, int lane,
-                                             const int* __restrict__ xq32, const float* __restrict__ xsc, float& ra, float& rb) {
-    const int p = lane >> 4, r = (lane >> 2) & 3, l = lane & 3;
-    float acc0 = 0.0f, acc1 = 0.0f;
-    if (DT == DT_Q4_0) {
-        const int o = lane & 15;
-#pragma unroll 4
-        for (int b = p; b < nb; b += 2) {
-            const uint32_t w0 = qa[b * 16 + o], w1 = qb[b * 16 + o];
-            const float xs = xsc[b];
-            const int x_lo = xq32[b * 8 + l], x_hi = xq32[b * 8 + 4 + l];
-            const float d0 = __fmul_rn(__half2float(da[b * 4 + r]), xs), d1 = __fmul_rn(__half2float(db[b * 4 + r]), xs);
-            int s0 = __dp4a((int)((w0 & 0xF0F0F0F0u) ^ 0x80808080u), x_hi, __dp4a((int)(((w0 << 4) & 0xF0F0F0F0u) ^ 0x80808080u), x_lo, 0));
-            int s1 = __dp4a((int)((w1 & 0xF0F0F0F0u) ^ 0x80808080u), x_hi, __dp4a((int)(((w1 << 4) & 0xF0F0F0F0u) ^ 0x80808080u), x_lo, 0));
-            acc0 = __fadd_rn(acc0, __fmul_rn((float)s0, d0));
-            acc1 = __fadd_rn(acc1, __fmul_rn((float)s1, d1));
+// One thread takes one (block, row) of the group per step: its four lane-words are 16 contiguous
+// bytes (as are the matching input words), so weights, inputs and products move as 128-bit
+// shared-memory accesses and the scale product is formed once per four terms.
+template <int DT, int U = 2>
+__device__ __forceinline__ void stage_products(uint32_t* __restrict__ qs, const __half* __restrict__ ds, int nb, int tt,
+                                               const int* __restrict__ xq32, const float* __restrict__ xsc) {
+    const int ni = nb * 4;  // (block, row) items of the group
+    for (int i0 = tt; i0 < ni; i0 += TEAM_THREADS * U) {
+        uint4 wa[U], wb[U];
+        int4 xl[U], xh[U];
+        float d[U];
+        int at[U];
+#pragma unroll
+        for (int u = 0; u < U; u++) {  // every load of the U independent items first
+            const int i = i0 + u * TEAM_THREADS, is = i < ni ? i : i0;
+            const int b = is >> 2, r = is & 3;
+            at[u] = DT == DT_Q4_0 ? q4_word(b, r, 0) : q8_word(b, 0, r, 0);
+            wa[u] = *reinterpret_cast<const uint4*>(qs + at[u]);
+            if (DT == DT_Q8_0) wb[u] = *reinterpret_cast<const uint4*>(qs + at[u] + 32);
+            xl[u] = *reinterpret_cast<const int4*>(xq32 + b * 8);
+            xh[u] = *reinterpret_cast<const int4*>(xq32 + b * 8 + 4);
+            d[u] = __fmul_rn(__half2float(ds[is]), xsc[b]);  // scale plane index b*4 + r == item index
         }
-    } else {
-#pragma unroll 4
-        for (int b = p; b < nb; b += 2) {
-            const int i0 = (b >> 1) * 64 + lane;
-            const int a_lo = (int)qa[i0], a_hi = (int)qa[i0 + 32], b_lo = (int)qb[i0], b_hi = (int)qb[i0 + 32];
-            const float xs = xsc[b];
-            const int x_lo = xq32[b * 8 + l], x_hi = xq32[b * 8 + 4 + l];
-            const float d0 = __fmul_rn(__half2float(da[b * 4 + r]), xs), d1 = __fmul_rn(__half2float(db[b * 4 + r]), xs);
-            int s0 = __dp4a(a_hi, x_hi, __dp4a(a_lo, x_lo, 0));
-            int s1 = __dp4a(b_hi, x_hi, __dp4a(b_lo, x_lo, 0));
-            acc0 = __fadd_rn(acc0, __fmul_rn((float)s0, d0));
-            acc1 = __fadd_rn(acc1, __fmul_rn((float)s1, d1));
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            int s0, s1, s2, s3;
+            if (DT == DT_Q4_0) {  // 16 * lane sum; xsc already carries the 1/16
+#define WICK_Q4_TERM(w, lo_x, hi_x) \
+    __dp4a((int)(((w)&0xF0F0F0F0u) ^ 0x80808080u), hi_x, __dp4a((int)((((w) << 4) & 0xF0F0F0F0u) ^ 0x80808080u), lo_x, 0))
+                s0 = WICK_Q4_TERM(wa[u].x, xl[u].x, xh[u].x);
+                s1 = WICK_Q4_TERM(wa[u].y, xl[u].y, xh[u].y);
+                s2 = WICK_Q4_TERM(wa[u].z, xl[u].z, xh[u].z);
+                s3 = WICK_Q4_TERM(wa[u].w, xl[u].w, xh[u].w);
+#undef WICK_Q4_TERM
+            } else {
+                s0 = __dp4a((int)wb[u].x, xh[u].x, __dp4a((int)wa[u].x, xl[u].x, 0));
+                s1 = __dp4a((int)wb[u].y, xh[u].y, __dp4a((int)wa[u].y, xl[u].y, 0));
+                s2 = __dp4a((int)wb[u].z, xh[u].z, __dp4a((int)wa[u].z, xl[u].z, 0));
+                s3 = __dp4a((int)wb[u].w, xh[u].w, __dp4a((int)wa[u].w, xl[u].w, 0));
+            }
+            if (i0 + u * TEAM_THREADS < ni) {
+                uint4 o;
+                o.x = __float_as_uint(__fmul_rn((float)s0, d[u]));
+                o.y = __float_as_uint(__fmul_rn((float)s1, d[u]));
+                o.z = __float_as_uint(__fmul_rn((float)s2, d[u]));
+                o.w = __float_as_uint(__fmul_rn((float)s3, d[u]));
+                *reinterpret_cast<uint4*>(qs + at[u]) = o;
+            }
         }
     }
-    ra = acc0;
-    rb = acc1;
+}
+
+template <int DT>
+__device__ __forceinline__ float group_chain_sum(const uint32_t* __restrict__ qs, int nb, int lane) {
+    const int p = lane >> 4;
+    const uint32_t* pp = DT == DT_Q4_0 ? qs + (lane & 15) : qs + lane;
+    constexpr int U = 8;
+    float acc = 0.0f;
+    int b = p;
+    for (; b + 2 * (U - 1) < nb; b += 2 * U) {
+        float t[U];
+#pragma unroll
+        for (int u = 0; u < U; u++) t[u] = __uint_as_float(DT == DT_Q4_0 ? pp[(b + 2 * u) * 16] : pp[((b + 2 * u) >> 1) * 64]);
+#pragma unroll
+        for (int u = 0; u < U; u++) acc = __fadd_rn(acc, t[u]);
+    }
+    for (; b < nb; b += 2) acc = __fadd_rn(acc, __uint_as_float(DT == DT_Q4_0 ? pp[b * 16] : pp[(b >> 1) * 64]));
+    return acc;
 }
 
 __device__ void consumer(const MegaParams& P, const Smem& S, int cta, int ncta) {
     Ctx c{P, S, cta, ncta, (int)threadIdx.x - 32, ((int)threadIdx.x - 32) >> 5, (int)threadIdx.x & 31, nullptr};
     int slot = 0;
     uint32_t par = 0;
+    const int team = c.cw / TEAM_WARPS, tw = c.cw % TEAM_WARPS, tt = tw * 32 + c.lane;
     const uint32_t pos0 = __ldcg(&P.ctl->pos), step0 = __ldcg(&P.ctl->step);
     uint32_t token = __ldcg(&P.ctl->token);
     const int* xq32 = reinterpret_cast<const int*>(S.xq);
@@ -747,9 +765,68 @@ __device__ void consumer(const MegaParams& P, const Smem& S, int cta, int ncta) 
                 default: phase_attention(c, ph, pos); break;
             }
             if (prof) P.prof[pi * 4 + 1] = globaltimer_ns();
-            if (ph.kind != MPH_ATTN) {
+            if (ph.kind != MPH_ATTN && ph.pair) {
+                // gate / up as alternating stages: stage pair j goes to team j % NTEAMS, which keeps both
+                // slots until it has the two sums of each row and can apply SwiGLU (n_slots is a multiple of
+                // 2 * NTEAMS, so within the phase a slot always returns to the same team)
                 Plan pl = plan_phase(ph, cta, ncta, P.slot_bytes);
-                int off = 0, ls = 0;
+                const DevWeight& wg = ph.mat[0].w;
+                const DevWeight& wu = ph.mat[1].w;
+                const int nb = wg.k / QK;
+                const uint32_t qgb = (uint32_t)wg.q_group_bytes();
+                float* act = ph.mat[0].y;
+                int pj = 0;
+                for (int g0 = pl.lo; g0 < pl.hi; g0 += pl.rg, pj++) {
+                    const int slot_a = slot;
+                    const uint32_t par_a = par;
+                    slot = slot + 1 == P.n_slots ? 0 : slot + 1;
+                    par ^= (slot == 0);
+                    const int slot_b = slot;
+                    const uint32_t par_b = par;
+                    slot = slot + 1 == P.n_slots ? 0 : slot + 1;
+                    par ^= (slot == 0);
+                    if (pj % NTEAMS != team) continue;
+                    const int ng = pl.rg < pl.hi - g0 ? pl.rg : pl.hi - g0;
+                    uint8_t* bases[2] = {S.ring + (size_t)slot_a * P.slot_bytes, S.ring + (size_t)slot_b * P.slot_bytes};
+                    for (int half = 0; half < 2; half++) {
+                        unsigned spins = 0;
+                        while (!*S.abort && !mbar_try_wait(&S.full[half ? slot_b : slot_a], half ? par_b : par_a)) {
+                            if (++spins > SPIN_LIMIT) {
+                                atomicOr(&P.ctl->error, 4u);
+                                *S.abort = 1;
+                                break;
+                            }
+                            if (spins > 32) __nanosleep(32);
+                        }
+                        const DevWeight& w = half ? wu : wg;
+                        const __half* dbase = reinterpret_cast<const __half*>(bases[half] + (size_t)ng * qgb);
+                        for (int gi = 0; gi < ng; gi++) {
+                            uint32_t* qs = reinterpret_cast<uint32_t*>(bases[half] + (size_t)gi * qgb);
+                            if (w.dtype == DT_Q4_0) stage_products<DT_Q4_0>(qs, dbase + (size_t)gi * nb * 4, nb, tt, xq32, S.xs16);
+                            else stage_products<DT_Q8_0>(qs, dbase + (size_t)gi * nb * 4, nb, tt, xq32, S.xs);
+                        }
+                    }
+                    team_sync(team);
+                    for (int gi = tw; gi < ng; gi += TEAM_WARPS) {
+                        const uint32_t* qa = reinterpret_cast<const uint32_t*>(bases[0] + (size_t)gi * qgb);
+                        const uint32_t* qb = reinterpret_cast<const uint32_t*>(bases[1] + (size_t)gi * qgb);
+                        float ga = wg.dtype == DT_Q4_0 ? group_chain_sum<DT_Q4_0>(qa, nb, c.lane) : group_chain_sum<DT_Q8_0>(qa, nb, c.lane);
+                        float ua = wu.dtype == DT_Q4_0 ? group_chain_sum<DT_Q4_0>(qb, nb, c.lane) : group_chain_sum<DT_Q8_0>(qb, nb, c.lane);
+                        ga = reduce_row8(ga);
+                        ua = reduce_row8(ua);
+                        const int row = (g0 + gi) * 4 + ((c.lane >> 2) & 3);
+                        if ((c.lane & 19) == 0 && row < wg.m) act[row] = silu_mul_elem(ga, ua);  // cpu.rs:668-673
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    team_sync(team);
+                    if (tt == 0) {
+                        mbar_arrive(&S.empty[slot_a]);
+                        mbar_arrive(&S.empty[slot_b]);
+                    }
+                }
+            } else if (ph.kind != MPH_ATTN) {
+                Plan pl = plan_phase(ph, cta, ncta, P.slot_bytes);
+                int off = 0, nst = 0;
                 for (int mi = 0; mi < ph.n_mat; mi++) {
                     const MegaMat& M = ph.mat[mi];
                     const DevWeight& w = M.w;
@@ -757,7 +834,11 @@ __device__ void consumer(const MegaParams& P, const Smem& S, int cta, int ncta) 
                     int a = (pl.lo > off ? pl.lo : off) - off, b = (pl.hi < off + gm ? pl.hi : off + gm) - off;
                     const uint32_t qgb = (uint32_t)w.q_group_bytes();
                     for (int g0 = a; g0 < b; g0 += pl.rg, slot = slot + 1 == P.n_slots ? 0 : slot + 1, par ^= (slot == 0)) {
+                        // a slot always belongs to the same team (n_slots is a multiple of NTEAMS), so a team
+                        // never waits two uses of a slot ahead and mbarrier parity cannot alias
+                        if (slot % NTEAMS != team) continue;
                         int ng = pl.rg < b - g0 ? pl.rg : b - g0;
+                        if (c.stamp && nst < 4) c.stamp[nst * 4 + 0] = globaltimer_ns();
                         unsigned spins = 0;
                         while (!*S.abort && !mbar_try_wait(&S.full[slot], par)) {
                             if (++spins > SPIN_LIMIT) {
@@ -767,43 +848,40 @@ __device__ void consumer(const MegaParams& P, const Smem& S, int cta, int ncta) 
                             }
                             if (spins > 32) __nanosleep(32);
                         }
-                        const uint8_t* base = S.ring + (size_t)slot * P.slot_bytes;
+                        if (c.stamp && nst < 4) c.stamp[nst * 4 + 1] = globaltimer_ns();
+                        uint8_t* base = S.ring + (size_t)slot * P.slot_bytes;
                         const __half* dbase = reinterpret_cast<const __half*>(base + (size_t)ng * qgb);
-                        // groups are dealt to the warps one at a time, or two at a time once the
-                        // CTA has enough of them to keep every warp busy that way
-                        const int unit = pl.pair ? 2 : 1;
-                        for (int gi = 0; gi < ng; gi += unit, ls++) {
-                            if (ls % NC != c.cw) continue;
-                            const int cntg = unit < ng - gi ? unit : ng - gi;
+                        for (int gi = 0; gi < ng; gi++) {
+                            uint32_t* qs = reinterpret_cast<uint32_t*>(base + (size_t)gi * qgb);
+                            if (w.dtype == DT_Q4_0) stage_products<DT_Q4_0>(qs, dbase + (size_t)gi * nb * 4, nb, tt, xq32, S.xs16);
+                            else stage_products<DT_Q8_0>(qs, dbase + (size_t)gi * nb * 4, nb, tt, xq32, S.xs);
+                        }
+                        team_sync(team);
+                        if (c.stamp && nst < 4) c.stamp[nst * 4 + 2] = globaltimer_ns();
+                        for (int gi = tw; gi < ng; gi += TEAM_WARPS) {
                             const uint32_t* qs = reinterpret_cast<const uint32_t*>(base + (size_t)gi * qgb);
-                            const __half* ds = dbase + (size_t)gi * nb * 4;
-                            float accs[2];
-                            if (cntg == 2) {
-                                const uint32_t* qs1 = reinterpret_cast<const uint32_t*>(base + (size_t)(gi + 1) * qgb);
-                                if (w.dtype == DT_Q4_0) group_chain2<DT_Q4_0>(qs, ds, qs1, ds + nb * 4, nb, c.lane, xq32, S.xs16, accs[0], accs[1]);
-                                else group_chain2<DT_Q8_0>(qs, ds, qs1, ds + nb * 4, nb, c.lane, xq32, S.xs, accs[0], accs[1]);
-                            } else {
-                                accs[0] = w.dtype == DT_Q4_0 ? group_chain<DT_Q4_0>(qs, ds, nb, c.lane, xq32, S.xs16)
-                                                             : group_chain<DT_Q8_0>(qs, ds, nb, c.lane, xq32, S.xs);
-                            }
-                            for (int q2 = 0; q2 < cntg; q2++) {
-                                const float acc = reduce_row8(accs[q2]);
-                                const int row = (g0 + gi + q2) * 4 + ((c.lane >> 2) & 3);
-                                if ((c.lane & 19) == 0 && row < w.m) {
-                                    if (M.epi == MEP_ADD) {
-                                        M.y[row] = __fadd_rn(__ldcg(M.y + row), acc);
-                                    } else if (M.epi == MEP_STORE) {
-                                        M.y[row] = acc;
-                                    } else {
-                                        if (!P.greedy) M.y[row] = acc;
-                                        unsigned long long pk = argmax_pack(acc, (uint32_t)row);
-                                        best = pk > best ? pk : best;
-                                    }
+                            float acc = w.dtype == DT_Q4_0 ? group_chain_sum<DT_Q4_0>(qs, nb, c.lane) : group_chain_sum<DT_Q8_0>(qs, nb, c.lane);
+                            acc = reduce_row8(acc);
+                            const int row = (g0 + gi) * 4 + ((c.lane >> 2) & 3);
+                            if ((c.lane & 19) == 0 && row < w.m) {
+                                if (M.epi == MEP_ADD) {
+                                    M.y[row] = __fadd_rn(__ldcg(M.y + row), acc);
+                                } else if (M.epi == MEP_STORE) {
+                                    M.y[row] = acc;
+                                } else {
+                                    if (!P.greedy) M.y[row] = acc;
+                                    unsigned long long pk = argmax_pack(acc, (uint32_t)row);
+                                    best = pk > best ? pk : best;
                                 }
                             }
                         }
-                        __syncwarp();
-                        if (c.lane == 0) mbar_arrive(&S.empty[slot]);
+                        // the slot was written through the generic proxy (products); order that before the
+                        // bulk copy (async proxy) that will refill it
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                        team_sync(team);
+                        if (c.stamp && nst < 4) c.stamp[nst * 4 + 3] = globaltimer_ns();
+                        nst++;
+                        if (tt == 0) mbar_arrive(&S.empty[slot]);
                     }
                     off += gm;
                 }
@@ -860,7 +938,7 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) k_decode_mega(const MegaParam
     if (threadIdx.x == 0) {
         for (int i = 0; i < P.n_slots; i++) {
             mbar_init(&S.full[i], 1);
-            mbar_init(&S.empty[i], NC);  // every consumer warp releases every stage
+            mbar_init(&S.empty[i], 1);  // released by the team that owns the slot
         }
         *S.abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");

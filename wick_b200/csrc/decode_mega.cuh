@@ -7,20 +7,24 @@ namespace wick {
 // 15 consumer warps + 1 producer warp = 512 threads: the compiler budgets registers for a block size
 // rounded up to a multiple of 128, so 17 warps would cap every thread at 96 registers instead of 128.
 constexpr int MEGA_CONSUMER_WARPS = 15;
+constexpr int MEGA_TEAM_WARPS = 3;
+constexpr int MEGA_TEAMS = MEGA_CONSUMER_WARPS / MEGA_TEAM_WARPS;  // the ring has a multiple of this many slots
+static_assert(MEGA_CONSUMER_WARPS % MEGA_TEAM_WARPS == 0, "consumer warps must split into whole teams");
 constexpr int MEGA_THREADS = 32 * (MEGA_CONSUMER_WARPS + 1);  // warp 0 issues the bulk copies
 
 enum MegaPhaseKind : int {
     MPH_NORM = 0,   // input = RMSNorm(hidden) (first phase of a token: hidden = embedding row)
     MPH_CONV = 1,   // input = c * shortconv(b * x) from proj
     MPH_ATTN = 2,   // no matmul: QK-norm, RoPE, KV append, single-query attention per head
-    MPH_QUANT = 3,  // input = attn_out
-    MPH_SILU = 4,   // input = silu(gate) * up
+    MPH_QUANT = 3,  // input = a vector produced by the previous phase (attn_out, or the fused SwiGLU output)
+    MPH_SILU = 4,   // input = silu(gate) * up, recomputed by every CTA (when the fused form is unavailable)
 };
 
 enum MegaEpilogue : int {
     MEP_STORE = 0,   // y[row] = v
     MEP_ADD = 1,     // y[row] = y[row] + v          (residual add, cpu::add_inplace)
     MEP_LOGITS = 2,  // store (optional) + running argmax
+    MEP_SWIGLU = 3,  // paired phase: y[row] = silu(mat[0] row) * (mat[1] row)   (cpu::silu_mul_inplace)
 };
 
 struct MegaMat {
@@ -36,6 +40,9 @@ struct MegaPhase {
     int layer;          // conv / attention layer this phase belongs to (or -1)
     int embed;          // MPH_NORM: 1 = first phase of a token
     int conv_commit;    // MPH_NORM: layer whose conv state is advanced in this prologue, or -1
+    int pair;           // 1: mat[0] / mat[1] are gate / up of equal shape, streamed as alternating stages and
+                        //    combined row by row in the epilogue (MEP_SWIGLU)
+    const float* src;   // MPH_QUANT: the vector to quantise
     const float* norm_w;
     MegaMat mat[3];
 };

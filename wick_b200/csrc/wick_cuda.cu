@@ -252,18 +252,22 @@ int32_t build_mega(wick_cuda_model* m) {
             at.kind = MPH_ATTN; at.layer = (int)i; at.conv_commit = -1; at.k = hs;
             ph.push_back(at);
             MegaPhase o{};
-            o.kind = MPH_QUANT; o.k = hs; o.layer = (int)i; o.conv_commit = -1; o.n_mat = 1;
+            o.kind = MPH_QUANT; o.src = m->attn_out; o.k = hs; o.layer = (int)i; o.conv_commit = -1; o.n_mat = 1;
             o.mat[0] = mat(L.o, m->hidden, MEP_ADD);
             ph.push_back(o);
         }
         MegaPhase f{};
         f.kind = MPH_NORM; f.k = hs; f.layer = (int)i; f.conv_commit = pending_commit; f.norm_w = L.ffn_norm; f.n_mat = 2;
         pending_commit = -1;
-        f.mat[0] = mat(L.gate, m->gate, MEP_STORE);
-        f.mat[1] = mat(L.up, m->up, MEP_STORE);
+        // gate and up of equal shape and type are streamed as alternating stages and SwiGLU is applied
+        // by the thread that holds both sums of a row; `gate` then holds silu(gate) * up
+        const bool fuse = L.gate.m == L.up.m && L.gate.k == L.up.k && L.gate.dtype == L.up.dtype;
+        f.pair = fuse ? 1 : 0;
+        f.mat[0] = mat(L.gate, m->gate, fuse ? MEP_SWIGLU : MEP_STORE);
+        f.mat[1] = mat(L.up, m->up, fuse ? MEP_SWIGLU : MEP_STORE);
         ph.push_back(f);
         MegaPhase d{};
-        d.kind = MPH_SILU; d.k = is; d.layer = (int)i; d.conv_commit = -1; d.n_mat = 1;
+        d.kind = fuse ? MPH_QUANT : MPH_SILU; d.src = m->gate; d.k = is; d.layer = (int)i; d.conv_commit = -1; d.n_mat = 1;
         d.mat[0] = mat(L.down, m->hidden, MEP_ADD);
         ph.push_back(d);
     }
@@ -289,9 +293,14 @@ int32_t build_mega(wick_cuda_model* m) {
     int max_smem = 0;
     CU_TRY(cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, m->device));
     size_t fixed = mega_smem_bytes(P);
-    if (fixed + 4 * (size_t)P.slot_bytes + 64 * 4 > (size_t)max_smem) return WICK_CUDA_OK;
+    if (fixed + MEGA_TEAMS * ((size_t)P.slot_bytes + 16) + 64 * 4 > (size_t)max_smem) return WICK_CUDA_OK;
     P.n_slots = (int)(((size_t)max_smem - fixed - 64 * 4) / ((size_t)P.slot_bytes + 16));
-    if (P.n_slots > 32) P.n_slots = 32;
+    if (P.n_slots > 30) P.n_slots = 30;
+    P.n_slots -= P.n_slots % MEGA_TEAMS;  // each slot is always served by the same consumer team
+    if (P.n_slots % (2 * MEGA_TEAMS))       // paired (gate/up) phases need whole pairs per ring lap
+        for (auto& q : ph) if (q.pair) { q.pair = 0; q.mat[0].epi = q.mat[1].epi = MEP_STORE; }
+    for (size_t i = 0; i + 1 < ph.size(); i++)
+        if (ph[i].kind == MPH_NORM && ph[i].n_mat == 2 && !ph[i].pair && ph[i + 1].kind == MPH_QUANT && ph[i + 1].src == m->gate) ph[i + 1].kind = MPH_SILU;
     W_TRY(dev_alloc(m, &m->d_phases, ph.size()));
     W_TRY(dev_alloc(m, &m->d_mlayers, ml.size()));
     W_TRY(dev_alloc(m, &m->d_sync, 4));
