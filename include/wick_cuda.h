@@ -209,6 +209,20 @@ int32_t wick_cuda_shortconv(const float* proj_dev, const float* conv_w_dev, floa
 /* cpu_argmax (sampler.rs:8-19) of `count` logits -> *out_dev. */
 int32_t wick_cuda_argmax(const float* logits_dev, uint32_t count, uint32_t* out_dev, void* stream);
 
+/* ---- allocation-free variant ------------------------------------------------
+ * No counterpart in wick: this entry point exists for callers of this library that are not allowed
+ * to allocate (a host callback, a real-time thread, a process that has given its whole memory pool
+ * away).  Same result as wick_cuda_argmax(), but the scratch it needs lives in a fixed 32 KB array
+ * inside the library (held by every GPU that loads it, until the process exits) and no allocation
+ * routine is called.  At most WICK_CUDA_ARGMAX_NOALLOC_MAX logits; more is WICK_CUDA_ERR_BAD_ARG
+ * (message from wick_cuda_argmax_noalloc_last_error()).  The first call on each device looks up the
+ * array's device address, so make that first call outside any stream capture.  All calls share the
+ * one array: two calls whose kernels can overlap on the GPU (different streams) race; calls on one
+ * stream are safe, and nothing needs to be cleared between calls. */
+#define WICK_CUDA_ARGMAX_NOALLOC_MAX (4096 * 1024)
+int32_t wick_cuda_argmax_noalloc(const float* logits_dev, uint32_t count, uint32_t* out_dev, void* stream);
+const char* wick_cuda_argmax_noalloc_last_error(void);
+
 #ifdef __cplusplus
 }
 #endif

@@ -74,9 +74,10 @@ SIGNATURES = {
     "wick_cuda_attention_prefill": [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _i32, _vp],
     "wick_cuda_shortconv": [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _vp],
     "wick_cuda_argmax": [_vp, _u32, _vp, _vp],
+    "wick_cuda_argmax_noalloc": [_vp, _u32, _vp, _vp],
 }
 VOID_FUNCS = {"wick_cuda_model_destroy": [_vp], "wick_cuda_weight_destroy": [_vp]}
-ALL_SYMBOLS = sorted(list(SIGNATURES) + list(VOID_FUNCS) + ["wick_cuda_last_error"])
+ALL_SYMBOLS = sorted(list(SIGNATURES) + list(VOID_FUNCS) + ["wick_cuda_last_error", "wick_cuda_argmax_noalloc_last_error"])
 
 _lib = None
 
@@ -100,6 +101,8 @@ def load() -> C.CDLL:
         fn.restype = None
     lib.wick_cuda_last_error.argtypes = []
     lib.wick_cuda_last_error.restype = C.c_char_p
+    lib.wick_cuda_argmax_noalloc_last_error.argtypes = []
+    lib.wick_cuda_argmax_noalloc_last_error.restype = C.c_char_p
     _lib = lib
     return lib
 

@@ -134,3 +134,17 @@ def argmax(logits: torch.Tensor) -> torch.Tensor:
     out = torch.empty(1, dtype=torch.int32, device=logits.device)
     check(_lib.load().wick_cuda_argmax(_ptr(logits), logits.numel(), _ptr(out), _stream()))
     return out
+
+
+ARGMAX_NOALLOC_MAX = 4096 * 1024
+
+
+def argmax_noalloc(logits: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """Same result as argmax() for callers that may not allocate: the scratch is a fixed array inside
+    the library and the caller supplies `out` (one int32 on the device).  At most ARGMAX_NOALLOC_MAX
+    logits.  Calls share that array, so keep them on one stream."""
+    lib = _lib.load()
+    code = lib.wick_cuda_argmax_noalloc(_ptr(logits), logits.numel(), _ptr(out), _stream())
+    if code != 0:
+        raise _lib.WickCudaError(code, lib.wick_cuda_argmax_noalloc_last_error().decode())
+    return out
