@@ -43,7 +43,7 @@ FALLBACK_HBM_GBS = 6650.0
 
 # dram__bytes_read.sum + dram__bytes_write.sum per decoded token from an ncu capture of the decode
 # kernels (profiles/), keyed by (model, qtype); None until captured.
-NCU_TRAFFIC_BYTES_PER_TOKEN = {}
+NCU_TRAFFIC_BYTES_PER_TOKEN = {("lfm2.5-1.6b", "q4_0"): 595.6e6}
 
 
 def measured_peak():
@@ -209,6 +209,7 @@ def main():
     import torch
     import torch.distributed as dist
     from wick_b200 import gguf_synth as gs
+    from wick_b200 import sharding
     from wick_b200.model import CudaLfm2Model, InferenceState
 
     if not torch.cuda.is_available():
@@ -223,18 +224,13 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    def max_over_ranks(x: float) -> float:
-        if world == 1:
-            return x
-        t = torch.tensor([x], dtype=torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
-
     path, spec = model_file(args, rank, world)
     barrier()
     m = CudaLfm2Model(path, 4096, device=local_rank)
     st = InferenceState()
-    prompt = gs.random_prompt(PROMPT_TOKENS, spec.vocab, seed=1 + rank)  # one independent sequence per rank
+    # one independent sequence per rank (round-robin over `world` sequences), no data-path collective
+    seq_index = sharding.shard_sequences(world, world, rank)[0]
+    prompt = gs.random_prompt(PROMPT_TOKENS, spec.vocab, seed=sharding.prompt_seed(1, seq_index))
 
     def one_step(e2e: bool):
         """Returns (decode seconds, tokens)."""
@@ -271,11 +267,12 @@ def main():
     t_wall2 = time.time()
     clocks = sampler.stop(t_wall0, t_wall2)
 
-    dev_s = max_over_ranks(dev_s)
-    e2e_s = max_over_ranks(e2e_s)
-    tokens = args.steps * DECODE_TOKENS * world
-    value = tokens / dev_s
-    e2e = tokens / e2e_s
+    local_tokens = args.steps * DECODE_TOKENS
+    tot = sharding.job_totals(local_tokens, dev_s)          # tokens summed, device time max over ranks
+    tot_e2e = sharding.job_totals(local_tokens, e2e_s)
+    dev_s, e2e_s, tokens = tot.seconds, tot_e2e.seconds, tot.tokens
+    value = tot.tokens_per_second
+    e2e = tot_e2e.tokens_per_second
     ms_per_token = dev_s / (args.steps * DECODE_TOKENS) * 1e3
 
     if rank != 0:
