@@ -107,6 +107,16 @@ int32_t wick_cuda_forward_greedy(wick_cuda_model* m, uint32_t token, uint32_t po
  * (forward_prefill_chunked, mod.rs:111-140). */
 int32_t wick_cuda_forward_prefill(wick_cuda_model* m, const uint32_t* tokens_host, uint32_t n,
                                   uint32_t start_pos, float* logits_host);
+
+/* Which GEMM forward_prefill uses for chunks of >= 16 tokens.  EXACT: the CUDA-core kernel that
+ * reproduces the f32 accumulation order of gemm_q*_q8_0_neon (simd.rs:696-1019) bit for bit.
+ * TENSOR (default when hidden and feed-forward sizes are multiples of 128; env
+ * WICK_CUDA_PREFILL=exact selects EXACT at load): the tcgen05 kernel described at
+ * wick_cuda_gemm_q8_tc, whose logits agree to f32 rounding.  Decode is not affected. */
+#define WICK_CUDA_PREFILL_EXACT 0
+#define WICK_CUDA_PREFILL_TENSOR 1
+int32_t wick_cuda_set_prefill_mode(wick_cuda_model* m, int32_t mode);
+int32_t wick_cuda_prefill_mode(const wick_cuda_model* m, int32_t* mode);
 /* Greedy decode loop of Session::generate (wick/src/session.rs:1186-1257) kept on the GPU:
  * feeds `first_token`, then each step's argmax, for n_steps steps; out_tokens_host[i] is the
  * token chosen by step i.  Equivalent to n_steps wick_cuda_forward_greedy calls without the
@@ -177,6 +187,15 @@ int32_t wick_cuda_gemv_q8(const wick_cuda_weight* w, const float* xs_dev, const 
  * columns; the result is token-major out[j*m + i] (the reference writes out[i*n + j]). */
 int32_t wick_cuda_gemm_q8(const wick_cuda_weight* w, const float* bs_dev, const int8_t* bq_dev,
                           uint32_t n, float* out_dev, void* stream);
+/* The same product on the tensor cores (tcgen05 int8 MMA, one instruction per 32-element block, int32
+ * block sums in tensor memory, f32 scaling in the epilogue): the throughput path of forward_prefill.
+ * Block sums are the exact integers of simd.rs:806-842; the f32 accumulation is one fused chain per
+ * output in ascending block order, so `out` agrees with wick_cuda_gemm_q8 to f32 rounding, not bit for
+ * bit.  Needs k % 128 == 0.  block_sums_dev: optional [n][m][k/32] int32.  Unlike the other operator
+ * entry points this one synchronises `stream` before returning (it reports expired device waits as
+ * WICK_CUDA_ERR_TIMEOUT) and, on its first call for a weight, allocates that weight's int8 copy. */
+int32_t wick_cuda_gemm_q8_tc(wick_cuda_weight* w, const float* bs_dev, const int8_t* bq_dev, uint32_t n,
+                             float* out_dev, int32_t* block_sums_dev, void* stream);
 /* int32 block dot sums S[i][b] = sum over the 32 elements of block b of row i (the vdotq_s32
  * lanes of simd.rs:381-383 added up) against one quantised column. */
 int32_t wick_cuda_block_sums(const wick_cuda_weight* w, const int8_t* xq_dev, int32_t* s_dev, void* stream);

@@ -17,6 +17,12 @@ def wick(cuda_lib):
     return m
 
 
+@pytest.fixture(autouse=True)
+def exact_prefill(monkeypatch):
+    """This file checks the bit-exact paths; the tensor-core prefill has its own tests."""
+    monkeypatch.setenv("WICK_CUDA_PREFILL", "exact")
+
+
 def _model_path(model_dir, spec, qtype, seed=0, **kw):
     from wick_b200 import gguf_synth as gs
     return gs.cached_model(spec, qtype, seed, cache_dir=model_dir, **kw)

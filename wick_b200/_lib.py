@@ -48,6 +48,8 @@ SIGNATURES = {
     "wick_cuda_forward": [_vp, _u32, _u32, _vp],
     "wick_cuda_forward_greedy": [_vp, _u32, _u32, C.POINTER(_u32)],
     "wick_cuda_forward_prefill": [_vp, _vp, _u32, _u32, _vp],
+    "wick_cuda_set_prefill_mode": [_vp, _i32],
+    "wick_cuda_prefill_mode": [_vp, C.POINTER(_i32)],
     "wick_cuda_generate_greedy": [_vp, _u32, _u32, _vp],
     "wick_cuda_reset": [_vp],
     "wick_cuda_seq_len": [_vp, C.POINTER(_u32)],
@@ -65,6 +67,7 @@ SIGNATURES = {
     "wick_cuda_quantize_q8_0": [_vp, _u32, _u32, _vp, _vp, _vp],
     "wick_cuda_gemv_q8": [_vp, _vp, _vp, _vp, _vp],
     "wick_cuda_gemm_q8": [_vp, _vp, _vp, _u32, _vp, _vp],
+    "wick_cuda_gemm_q8_tc": [_vp, _vp, _vp, _u32, _vp, _vp, _vp],
     "wick_cuda_block_sums": [_vp, _vp, _vp, _vp],
     "wick_cuda_rmsnorm": [_vp, _vp, _u32, _u32, _f, _vp],
     "wick_cuda_silu_mul": [_vp, _vp, _u64, _vp],

@@ -1,0 +1,480 @@
+// Tensor-core prefill GEMM for sm_100a: int8 x int8 -> int32 block sums on tcgen05 with the
+// accumulator in tensor memory, operands staged by TMA, per-block f32 scaling in the epilogue warps.
+//
+// What it computes, for a weight matrix W [m rows][k] in Q4_0 / Q8_0 and n activation rows
+// quantised to Q8_0 (simd.rs:255-323):
+//     S_b[i][j]  = sum over the 32 elements of block b of  w_int[i][.] * x_int[j][.]        (int32, exact)
+//     out[j][i]  = sum over b, in ascending b, of  fma(float(S_b[i][j]), f16->f32(d_w[i][b]) * d_x[j][b], acc)
+// S_b is the same integer the NEON kernels produce per block (simd.rs:696-1019, the four lane
+// partials added up); what differs from them is the f32 accumulation: one fused chain per output in
+// block order instead of 2 x 4 unfused lane chains, so outputs agree to f32 rounding (~1e-6 relative),
+// not bit for bit.  The bit-exact order lives in k_gemm (kernels_gemv.cu); this kernel is the
+// throughput path of forward_prefill.
+//
+// One MMA instruction covers exactly one quantisation block (K = 32 int8), writes a fresh 128 x BN
+// int32 tile into one of 512/BN tensor-memory buffers and never accumulates across blocks, because
+// each block has its own scale pair.  The epilogue warps drain a buffer (tcgen05.ld), hand it back,
+// and apply the scales on the CUDA cores: 3 instructions per (output, block), which is what bounds the
+// kernel (the tensor pipe needs about 1/6 of that time).
+//
+// Roles in a CTA of 12 warps (one CTA per SM, persistent over output tiles):
+//   warp 0  lane 0: TMA producer, one K=128 stage (4 blocks) of W rows and activation rows per step
+//   warp 1  lane 0: issues tcgen05.mma / tcgen05.commit; the whole warp owns the TMEM allocation
+//   warp 2        : copies the stage's weight scales and (transposed) activation scales into smem
+//   warps 4..11   : epilogue; warp w reads TMEM lanes 32*(w%4).. and columns (w-4)/4 * BN/2 ..
+// Every wait is bounded: on expiry the kernel records an error code, all roles leave their loops and
+// the CTA frees its tensor memory and exits.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <mutex>
+
+#include "gemm_tc.cuh"
+
+namespace wick {
+
+namespace {
+
+constexpr int TC_BM = 128;          // weight rows per tile == TMEM lanes
+constexpr int TC_KSTAGE = 128;      // int8 elements (bytes) per row per stage == one 128B swizzle atom
+constexpr int TC_KB_PER_STAGE = TC_KSTAGE / QK;  // 4 quantisation blocks per stage
+constexpr int TC_STAGES = 4;
+constexpr int TC_THREADS = 384;
+constexpr int TC_EPI_WARPS = 8;
+constexpr uint32_t TC_SPIN_LIMIT = 1u << 18;  // try_wait itself suspends for a while, so this is of the order of a second
+
+template <int BN>
+struct alignas(1024) TcStage {
+    int8_t a[TC_BM * TC_KSTAGE];              // 16 KB, rows of 128 B, 128B-swizzled by TMA
+    int8_t b[BN * TC_KSTAGE];                 // BN rows of 128 B
+    float sw[TC_KB_PER_STAGE][TC_BM];         // weight scales of the stage's blocks
+    float sx[TC_KB_PER_STAGE][BN];            // activation scales, transposed to [block][token]
+};
+
+template <int BN>
+struct TcSmem {
+    TcStage<BN> stage[TC_STAGES];
+    unsigned long long full[TC_STAGES];       // TMA bytes landed + scales written
+    unsigned long long empty[TC_STAGES];      // MMAs of the stage retired + epilogue done with its scales
+    unsigned long long tmem_full[512 / BN];   // block sums of one k-block are in the buffer
+    unsigned long long tmem_empty[512 / BN];  // all epilogue warps have read the buffer
+    uint32_t tmem_base;
+    volatile uint32_t abort;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok;
+}
+
+// Bounded wait.  Returns false once the limit is hit or another role has already given up.
+template <int BN>
+__device__ __forceinline__ bool mbar_wait(TcSmem<BN>* sm, uint32_t bar, uint32_t parity, uint32_t* err, uint32_t code) {
+    for (uint32_t i = 0; i < TC_SPIN_LIMIT; i++) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 1023u) == 1023u && sm->abort) return false;
+    }
+    sm->abort = 1;
+    atomicCAS(err, 0u, code);
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+        "l"((unsigned long long)map), "r"(bar), "r"(x), "r"(y)
+        : "memory");
+}
+
+// K-major operand tile, rows of 128 bytes, 128B swizzle: 8-row atoms 1024 bytes apart.
+__device__ __forceinline__ unsigned long long umma_desc_sw128(uint32_t smem_addr) {
+    unsigned long long d = 0;
+    d |= (unsigned long long)((smem_addr >> 4) & 0x3FFF);  // start address
+    d |= 1ull << 16;                                        // leading byte offset (unused for swizzled K-major)
+    d |= (unsigned long long)(1024 >> 4) << 32;             // stride byte offset between 8-row atoms
+    d |= 1ull << 46;                                        // descriptor version of this architecture
+    d |= 2ull << 61;                                        // SWIZZLE_128B
+    return d;
+}
+
+__device__ __forceinline__ void umma_i8(uint32_t tmem_d, unsigned long long da, unsigned long long db, uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}" ::"r"(tmem_d),
+        "l"(da), "l"(db), "r"(idesc), "r"(0u), "r"(0u)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, int32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+}  // namespace
+
+namespace {
+
+template <int BN, bool SUMS>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+          const float* __restrict__ w_scales_t,  // [k/32][m_pad]
+          const float* __restrict__ x_scales,    // [n][k/32]
+          float* __restrict__ out,               // [n][m]
+          int32_t* __restrict__ sums,            // optional [n][m][k/32]
+          int m, int m_pad, int n, int k, uint32_t* err) {
+    extern __shared__ uint8_t tc_smem_raw[];
+    TcSmem<BN>* sm = reinterpret_cast<TcSmem<BN>*>((reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
+    constexpr int NBUF = 512 / BN;
+    constexpr int COLS = BN / 2;  // columns per epilogue thread
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nb = k / QK;
+    const int k_stages = k / TC_KSTAGE;
+    const int tiles_n = (n + BN - 1) / BN;
+    const int tiles = (m_pad / TC_BM) * tiles_n;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < TC_STAGES; s++) {
+            mbar_init(smem_u32(&sm->full[s]), 2);                 // producer (with tx bytes) + scale warp
+            mbar_init(smem_u32(&sm->empty[s]), 1 + TC_EPI_WARPS);  // MMA commit + epilogue warps
+        }
+        for (int b = 0; b < NBUF; b++) {
+            mbar_init(smem_u32(&sm->tmem_full[b]), 1);
+            mbar_init(smem_u32(&sm->tmem_empty[b]), TC_EPI_WARPS);
+        }
+        sm->abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm->tmem_base)), "r"(512u)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = sm->tmem_base;
+
+    if (warp == 0) {
+        // ── TMA producer ─────────────────────────────────────────────────────
+        if (lane == 0) {
+            uint32_t g = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
+                const int m0 = (t / tiles_n) * TC_BM, n0 = (t % tiles_n) * BN;
+                for (int ks = 0; ks < k_stages; ks++, g++) {
+                    const int s = g % TC_STAGES;
+                    const uint32_t u = g / TC_STAGES;
+                    ok = mbar_wait(sm, smem_u32(&sm->empty[s]), (u & 1) ^ 1, err, 1);
+                    if (!ok) break;
+                    const uint32_t bar = smem_u32(&sm->full[s]);
+                    mbar_arrive_expect_tx(bar, (TC_BM + BN) * TC_KSTAGE);
+                    tma_load_2d(smem_u32(sm->stage[s].a), &map_w, bar, ks * TC_KSTAGE, m0);
+                    tma_load_2d(smem_u32(sm->stage[s].b), &map_x, bar, ks * TC_KSTAGE, n0);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ── MMA issuer ───────────────────────────────────────────────────────
+        if (lane == 0) {
+            const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+            uint32_t g = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
+                for (int ks = 0; ks < k_stages && ok; ks++, g++) {
+                    const int s = g % TC_STAGES;
+                    const uint32_t u = g / TC_STAGES;
+                    ok = mbar_wait(sm, smem_u32(&sm->full[s]), u & 1, err, 2);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const unsigned long long da = umma_desc_sw128(smem_u32(sm->stage[s].a));
+                    const unsigned long long db = umma_desc_sw128(smem_u32(sm->stage[s].b));
+#pragma unroll
+                    for (int kk = 0; kk < TC_KB_PER_STAGE; kk++) {
+                        const uint32_t j = g * TC_KB_PER_STAGE + kk;
+                        const uint32_t buf = j % NBUF, ub = j / NBUF;
+                        ok = mbar_wait(sm, smem_u32(&sm->tmem_empty[buf]), (ub & 1) ^ 1, err, 3);
+                        if (!ok) break;
+                        tc_fence_after();
+                        // 32 bytes further along K inside the swizzle atom: +2 in the 16-byte address field
+                        umma_i8(tmem_base + buf * BN, da + (unsigned long long)(kk * 2), db + (unsigned long long)(kk * 2), idesc);
+                        umma_commit(smem_u32(&sm->tmem_full[buf]));
+                    }
+                    if (ok) umma_commit(smem_u32(&sm->empty[s]));
+                }
+            }
+        }
+    } else if (warp == 2) {
+        // ── scale loader ─────────────────────────────────────────────────────
+        uint32_t g = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
+            const int m0 = (t / tiles_n) * TC_BM, n0 = (t % tiles_n) * BN;
+            for (int ks = 0; ks < k_stages; ks++, g++) {
+                const int s = g % TC_STAGES;
+                const uint32_t u = g / TC_STAGES;
+                ok = mbar_wait(sm, smem_u32(&sm->empty[s]), (u & 1) ^ 1, err, 4);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                TcStage<BN>& st = sm->stage[s];
+                const int b0 = ks * TC_KB_PER_STAGE;
+#pragma unroll
+                for (int kk = 0; kk < TC_KB_PER_STAGE; kk++) {
+                    const float4 v = __ldg(reinterpret_cast<const float4*>(w_scales_t + (size_t)(b0 + kk) * m_pad + m0) + lane);
+                    reinterpret_cast<float4*>(st.sw[kk])[lane] = v;
+                }
+#pragma unroll
+                for (int c = lane; c < BN; c += 32) {
+                    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (n0 + c < n) v = __ldg(reinterpret_cast<const float4*>(x_scales + (size_t)(n0 + c) * nb + b0));
+                    st.sx[0][c] = v.x;
+                    st.sx[1][c] = v.y;
+                    st.sx[2][c] = v.z;
+                    st.sx[3][c] = v.w;
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&sm->full[s]));
+            }
+        }
+    } else if (warp >= 4) {
+        // ── epilogue ─────────────────────────────────────────────────────────
+        const int quarter = warp & 3, half = (warp - 4) >> 2;
+        const int row_in_tile = quarter * 32 + lane;
+        const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(half * COLS);
+        float acc[COLS];
+        uint32_t g = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
+            const int m0 = (t / tiles_n) * TC_BM, n0 = (t % tiles_n) * BN;
+            const int row = m0 + row_in_tile;
+#pragma unroll
+            for (int c = 0; c < COLS; c++) acc[c] = 0.f;
+            for (int ks = 0; ks < k_stages && ok; ks++, g++) {
+                const int s = g % TC_STAGES;
+                const uint32_t u = g / TC_STAGES;
+                ok = mbar_wait(sm, smem_u32(&sm->full[s]), u & 1, err, 5);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                const TcStage<BN>& st = sm->stage[s];
+#pragma unroll 1
+                for (int kk = 0; kk < TC_KB_PER_STAGE; kk++) {
+                    const uint32_t j = g * TC_KB_PER_STAGE + kk;
+                    const uint32_t buf = j % NBUF, ub = j / NBUF;
+                    ok = mbar_wait(sm, smem_u32(&sm->tmem_full[buf]), ub & 1, err, 6);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                    tc_fence_after();
+                    int32_t S[COLS];
+#pragma unroll
+                    for (int c = 0; c < COLS; c += 32) tmem_ld32(lane_base + buf * BN + c, S + c);
+                    tmem_ld_wait();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&sm->tmem_empty[buf]));
+                    const float sw = st.sw[kk][row_in_tile];
+                    const float4* sx4 = reinterpret_cast<const float4*>(&st.sx[kk][half * COLS]);
+#pragma unroll
+                    for (int c = 0; c < COLS; c += 4) {
+                        const float4 x = sx4[c >> 2];
+                        acc[c + 0] = __fmaf_rn(__int2float_rn(S[c + 0]), __fmul_rn(sw, x.x), acc[c + 0]);
+                        acc[c + 1] = __fmaf_rn(__int2float_rn(S[c + 1]), __fmul_rn(sw, x.y), acc[c + 1]);
+                        acc[c + 2] = __fmaf_rn(__int2float_rn(S[c + 2]), __fmul_rn(sw, x.z), acc[c + 2]);
+                        acc[c + 3] = __fmaf_rn(__int2float_rn(S[c + 3]), __fmul_rn(sw, x.w), acc[c + 3]);
+                    }
+                    if (SUMS && row < m) {
+                        const int b = ks * TC_KB_PER_STAGE + kk;
+#pragma unroll
+                        for (int c = 0; c < COLS; c++) {
+                            const int tok = n0 + half * COLS + c;
+                            if (tok < n) sums[((size_t)tok * m + row) * nb + b] = S[c];
+                        }
+                    }
+                }
+                if (!ok) break;
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&sm->empty[s]));
+            }
+            if (ok && row < m) {
+#pragma unroll
+                for (int c = 0; c < COLS; c++) {
+                    const int tok = n0 + half * COLS + c;
+                    if (tok < n) out[(size_t)tok * m + row] = acc[c];
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        if (sm->abort) {
+            // copies issued before the failure may still be landing in this CTA's shared memory
+            for (int i = 0; i < 64; i++) __nanosleep(1000);
+        }
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    }
+}
+
+}  // namespace
+
+// ── host side ────────────────────────────────────────────────────────────────
+namespace {
+
+// One thread per (row, block): widen the block's quants to int8 and store its scale.
+__global__ void k_tc_unpack(DevWeight w, int8_t* __restrict__ q, float* __restrict__ scales_t, int m_pad) {
+    const int nb = w.k / QK;
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)w.m * nb) return;
+    const int row = (int)(idx / nb), b = (int)(idx % nb);
+    const int g = row >> 2, r = row & 3;
+    const __half* dg = w.d + (size_t)g * nb * 4;
+    const uint32_t* qg = reinterpret_cast<const uint32_t*>(w.q + (size_t)g * w.q_group_bytes());
+    scales_t[(size_t)b * m_pad + row] = __half2float(dg[b * 4 + r]);
+    uint32_t o[8];
+    if (w.dtype == DT_Q4_0) {
+#pragma unroll
+        for (int l = 0; l < 4; l++) {
+            const uint32_t v = qg[q4_word(b, r, l)];
+            // bytes of v: elements 4l..4l+3 in the low nibbles, 16+4l.. in the high nibbles
+            const uint32_t lo = v & 0x0F0F0F0Fu, hi = (v >> 4) & 0x0F0F0F0Fu;
+            o[l] = __vsub4(lo, 0x08080808u);
+            o[4 + l] = __vsub4(hi, 0x08080808u);
+        }
+    } else {
+#pragma unroll
+        for (int l = 0; l < 4; l++) {
+            o[l] = qg[q8_word(b, 0, r, l)];
+            o[4 + l] = qg[q8_word(b, 1, r, l)];
+        }
+    }
+    uint4* dst = reinterpret_cast<uint4*>(q + (size_t)row * w.k + (size_t)b * QK);
+    dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+    dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+// int8 matrix [rows][k] row-major; box = 128 bytes along k x box_rows rows; 128B swizzle.
+cudaError_t encode_rows_map(const void* base, int rows, int k, int box_rows, CUtensorMap* out) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return cudaErrorNotSupported;
+    cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)k};
+    cuuint32_t box[2] = {(cuuint32_t)TC_KSTAGE, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
+template <int BN>
+cudaError_t launch_tc(cudaStream_t st, const TcWeight& w, const CUtensorMap& map_x, const float* x_scales, int n, float* out,
+                      int32_t* sums, uint32_t* err) {
+    static int sm_count = 0;
+    static bool configured = false;
+    const size_t smem = sizeof(TcSmem<BN>) + 1024;
+    if (!configured) {
+        int dev = 0;
+        cudaError_t e = cudaGetDevice(&dev);
+        if (e != cudaSuccess) return e;
+        e = cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess) return e;
+        e = cudaFuncSetAttribute(k_gemm_tc<BN, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        e = cudaFuncSetAttribute(k_gemm_tc<BN, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    const int tiles = (w.m_pad / TC_BM) * ((n + BN - 1) / BN);
+    const int grid = tiles < sm_count ? tiles : sm_count;
+    g_kernel_launches++;
+    if (sums)
+        k_gemm_tc<BN, true><<<grid, TC_THREADS, smem, st>>>(w.map, map_x, w.scales_t, x_scales, out, sums, w.m, w.m_pad, n, w.k, err);
+    else
+        k_gemm_tc<BN, false><<<grid, TC_THREADS, smem, st>>>(w.map, map_x, w.scales_t, x_scales, out, sums, w.m, w.m_pad, n, w.k, err);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+bool tc_gemm_supported(int m, int k) { return m > 0 && k > 0 && k % TC_KSTAGE == 0; }
+
+int tc_gemm_bn(int n) { return n <= 64 ? 64 : 128; }
+
+cudaError_t tc_weight_fill(cudaStream_t st, const DevWeight& w, TcWeight* out) {
+    out->m = w.m;
+    out->k = w.k;
+    out->m_pad = (w.m + TC_BM - 1) / TC_BM * TC_BM;
+    cudaError_t e = cudaMemsetAsync(out->q, 0, out->q_bytes(), st);
+    if (e != cudaSuccess) return e;
+    e = cudaMemsetAsync(out->scales_t, 0, out->s_bytes(), st);
+    if (e != cudaSuccess) return e;
+    const size_t n_blocks = (size_t)w.m * (w.k / QK);
+    g_kernel_launches++;
+    k_tc_unpack<<<(unsigned)((n_blocks + 255) / 256), 256, 0, st>>>(w, out->q, out->scales_t, out->m_pad);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    return encode_rows_map(out->q, out->m_pad, out->k, TC_BM, &out->map);
+}
+
+cudaError_t tc_make_activation_map(const int8_t* xq, int rows_cap, int k, int bn, CUtensorMap* out) {
+    return encode_rows_map(xq, rows_cap, k, bn, out);
+}
+
+cudaError_t launch_gemm_tc(cudaStream_t st, const TcWeight& w, const CUtensorMap& map_x, const float* x_scales, int n,
+                           float* out, int32_t* sums, uint32_t* err) {
+    if (n <= 0) return cudaSuccess;
+    return tc_gemm_bn(n) == 64 ? launch_tc<64>(st, w, map_x, x_scales, n, out, sums, err)
+                               : launch_tc<128>(st, w, map_x, x_scales, n, out, sums, err);
+}
+
+}  // namespace wick

@@ -1,0 +1,40 @@
+// Tensor-core (tcgen05 + TMEM + TMA) prefill GEMM: host-side handles and launch wrappers (gemm_tc.cu).
+#pragma once
+#include <cuda.h>
+
+#include "kernels.cuh"
+
+namespace wick {
+
+// A second, GEMM-friendly copy of a quantised matrix: plain int8 values row-major (Q4_0 nibbles are
+// widened to nib - 8) so that TMA can place 128-byte row segments straight into the swizzled operand
+// layout, plus its scales as f32, block-major so that one k-block's 128 row scales are contiguous.
+struct TcWeight {
+    int8_t* q = nullptr;      // [m_pad][k]
+    float* scales_t = nullptr;  // [k/32][m_pad]
+    int m = 0, k = 0, m_pad = 0;
+    CUtensorMap map;          // rows of this matrix, box 128 bytes x 128 rows, 128B swizzle
+    size_t q_bytes() const { return (size_t)m_pad * k; }
+    size_t s_bytes() const { return (size_t)(k / QK) * m_pad * sizeof(float); }
+};
+
+// True when the shapes meet the kernel's requirements (k a multiple of 128).
+bool tc_gemm_supported(int m, int k);
+// Rows of tokens per tile the launcher will choose for n tokens (64 or 128).
+int tc_gemm_bn(int n);
+
+// Fills `out` (q / scales_t must already point at q_bytes() / s_bytes() of device memory, zeroed by
+// this call) from the grouped layout of `w`, and encodes its tensor map.  Returns cudaSuccess or the
+// failing CUDA error; a tensor-map failure is reported as cudaErrorInvalidValue.
+cudaError_t tc_weight_fill(cudaStream_t st, const DevWeight& w, TcWeight* out);
+
+// Tensor map over quantised activations xq [rows_cap][k] int8 with a box of bn rows.
+cudaError_t tc_make_activation_map(const int8_t* xq, int rows_cap, int k, int bn, CUtensorMap* out);
+
+// out[j][i] for j < n, i < m (token-major, like launch_gemm).  `map_x` must have been made with
+// tc_gemm_bn(n) rows per box.  sums: optional [n][m][k/32] int32 block sums.  err: device word
+// that receives a non-zero code if a bounded wait expired.
+cudaError_t launch_gemm_tc(cudaStream_t st, const TcWeight& w, const CUtensorMap& map_x, const float* x_scales, int n,
+                           float* out, int32_t* sums, uint32_t* err);
+
+}  // namespace wick

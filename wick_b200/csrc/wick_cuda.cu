@@ -15,6 +15,7 @@
 #include "../../include/wick_cuda.h"
 #include "gguf.hpp"
 #include "decode_mega.cuh"
+#include "gemm_tc.cuh"
 #include "kernels.cuh"
 
 using namespace wick;
@@ -46,6 +47,8 @@ struct Layer {
     int n_kv = 0;
     float *attn_norm = nullptr, *ffn_norm = nullptr, *q_norm = nullptr, *k_norm = nullptr, *conv_w = nullptr;
     DevWeight in_proj, out_proj, q, k, v, o, gate, up, down;
+    // int8 copies for the tensor-core prefill GEMM (gemm_tc.cu); q == nullptr when unavailable
+    TcWeight tc_in_proj, tc_out_proj, tc_q, tc_k, tc_v, tc_o, tc_gate, tc_up, tc_down;
     float *k_cache = nullptr, *v_cache = nullptr;  // [max_seq][kv_dim]
     float* conv_state = nullptr;                   // [d_conv][hidden]
 };
@@ -55,6 +58,8 @@ struct Layer {
 struct wick_cuda_weight {
     DevWeight w;
     int device = 0;
+    TcWeight tc;                // filled by the first wick_cuda_gemm_q8_tc call
+    uint32_t* tc_err = nullptr;
 };
 
 struct wick_cuda_model {
@@ -67,6 +72,11 @@ struct wick_cuda_model {
     float* output_norm = nullptr;
     float *rope_cos = nullptr, *rope_sin = nullptr;
     int max_chunk = 0;  // tokens of scratch
+    // tensor-core prefill path: available when every matrix meets tc_gemm_supported(); `prefill_tc`
+    // selects it (default) or the bit-exact CUDA-core GEMM
+    bool tc_ok = false, prefill_tc = false;
+    CUtensorMap map_x_hs[2], map_x_is[2];  // activations [max_chunk][hs | is], box of 64 / 128 rows
+    uint32_t* tc_err = nullptr;
     // scratch, token-major
     float *hidden = nullptr, *block_out = nullptr, *ffn_out = nullptr, *proj = nullptr, *qbuf = nullptr, *kbuf = nullptr,
           *vbuf = nullptr, *attn_out = nullptr, *gate = nullptr, *up = nullptr, *logits = nullptr;
@@ -427,19 +437,32 @@ void enqueue_prefill_chunk(wick_cuda_model* m, int n, int start_pos, bool flash,
     cudaStream_t st = m->stream;
     const int hs = m->cfg.hidden_size, is = m->cfg.intermediate_size, hd = m->head_dim;
     const float eps = m->cfg.rms_norm_eps;
+    // tensor-core path for chunks wide enough to fill an MMA tile; the exact kernel otherwise
+    const bool tc = m->prefill_tc && m->tc_ok && n >= 16;
+    const int bi = tc_gemm_bn(n) == 64 ? 0 : 1;
+    auto launch_gemm = [&](cudaStream_t s_, const DevWeight& w, const float* bs, const int8_t* bq, int n_, float* out,
+                           const TcWeight* t = nullptr) {
+        if (tc && t && t->q) {
+            const CUtensorMap& mx = w.k == hs ? m->map_x_hs[bi] : m->map_x_is[bi];
+            cudaError_t e = launch_gemm_tc(s_, *t, mx, bs, n_, out, nullptr, m->tc_err);
+            (void)e;  // surfaced by the cudaGetLastError() check after the chunk
+        } else {
+            wick::launch_gemm(s_, w, bs, bq, n_, out);
+        }
+    };
     launch_embed(st, m->embd, m->tokens_dev, nullptr, m->hidden, n);
     const float* pending = nullptr;
     for (size_t li = 0; li < m->layers.size(); li++) {
         Layer& L = m->layers[li];
         launch_add_rmsnorm_quant(st, m->hidden, pending, L.attn_norm, eps, n, hs, m->q8s, m->q8q, nullptr);
         if (!L.is_attn) {
-            launch_gemm(st, L.in_proj, m->q8s, m->q8q, n, m->proj);
+            launch_gemm(st, L.in_proj, m->q8s, m->q8q, n, m->proj, &L.tc_in_proj);
             launch_shortconv(st, m->proj, L.conv_w, L.conv_state, n, hs, m->cfg.conv_kernel_size, nullptr, m->q8s, m->q8q);
-            launch_gemm(st, L.out_proj, m->q8s, m->q8q, n, m->block_out);
+            launch_gemm(st, L.out_proj, m->q8s, m->q8q, n, m->block_out, &L.tc_out_proj);
         } else {
-            launch_gemm(st, L.q, m->q8s, m->q8q, n, m->qbuf);
-            launch_gemm(st, L.k, m->q8s, m->q8q, n, m->kbuf);
-            launch_gemm(st, L.v, m->q8s, m->q8q, n, m->vbuf);
+            launch_gemm(st, L.q, m->q8s, m->q8q, n, m->qbuf, &L.tc_q);
+            launch_gemm(st, L.k, m->q8s, m->q8q, n, m->kbuf, &L.tc_k);
+            launch_gemm(st, L.v, m->q8s, m->q8q, n, m->vbuf, &L.tc_v);
             launch_qknorm_rope_kv(st, m->qbuf, m->kbuf, m->vbuf, L.q_norm, L.k_norm, eps, m->rope_cos, m->rope_sin, L.k_cache,
                                   L.v_cache, n, start_pos, nullptr, m->cfg.n_heads, L.n_kv, hd);
             if (flash)
@@ -448,13 +471,13 @@ void enqueue_prefill_chunk(wick_cuda_model* m, int n, int start_pos, bool flash,
                 launch_attention_naive(st, m->qbuf, L.k_cache, L.v_cache, m->attn_out, n, start_pos, nullptr, m->cfg.n_heads,
                                        L.n_kv, hd, m->cfg.max_seq_len);
             launch_quant_rows(st, m->attn_out, n, hs, m->q8s, m->q8q);
-            launch_gemm(st, L.o, m->q8s, m->q8q, n, m->block_out);
+            launch_gemm(st, L.o, m->q8s, m->q8q, n, m->block_out, &L.tc_o);
         }
         launch_add_rmsnorm_quant(st, m->hidden, m->block_out, L.ffn_norm, eps, n, hs, m->q8s, m->q8q, nullptr);
-        launch_gemm(st, L.gate, m->q8s, m->q8q, n, m->gate);
-        launch_gemm(st, L.up, m->q8s, m->q8q, n, m->up);
+        launch_gemm(st, L.gate, m->q8s, m->q8q, n, m->gate, &L.tc_gate);
+        launch_gemm(st, L.up, m->q8s, m->q8q, n, m->up, &L.tc_up);
         launch_silu_mul_quant(st, m->gate, m->up, n, is, m->q8s, m->q8q, nullptr);
-        launch_gemm(st, L.down, m->q8s, m->q8q, n, m->ffn_out);
+        launch_gemm(st, L.down, m->q8s, m->q8q, n, m->ffn_out, &L.tc_down);
         pending = m->ffn_out;
     }
     if (want_logits) {
@@ -465,6 +488,49 @@ void enqueue_prefill_chunk(wick_cuda_model* m, int n, int start_pos, bool flash,
         lg.count = 1; lg.w[0] = m->embd; lg.y[0] = m->logits;
         launch_gemv(st, lg, m->q8s, m->q8q);
     }
+}
+
+// int8 copies of the layer matrices + activation tensor maps for the tensor-core prefill GEMM.
+int32_t build_tc(wick_cuda_model* m) {
+    const int hs = m->cfg.hidden_size, is = m->cfg.intermediate_size;
+    m->tc_ok = false;
+    const char* mode = getenv("WICK_CUDA_PREFILL");
+    const bool want = !(mode && strcmp(mode, "exact") == 0);
+    bool ok = tc_gemm_supported(hs, hs) && tc_gemm_supported(hs, is);
+    if (!ok) return WICK_CUDA_OK;
+    W_TRY(dev_alloc(m, &m->tc_err, 1));
+    CU_TRY(cudaMemset(m->tc_err, 0, 4));
+    auto fill = [&](const DevWeight& w, TcWeight* t) -> int32_t {
+        t->m_pad = (w.m + 127) / 128 * 128;
+        t->m = w.m;
+        t->k = w.k;
+        W_TRY(dev_alloc(m, &t->q, t->q_bytes()));
+        W_TRY(dev_alloc(m, &t->scales_t, t->s_bytes() / sizeof(float)));
+        CU_TRY(tc_weight_fill(m->stream, w, t));
+        return WICK_CUDA_OK;
+    };
+    for (Layer& L : m->layers) {
+        if (L.is_attn) {
+            W_TRY(fill(L.q, &L.tc_q));
+            W_TRY(fill(L.k, &L.tc_k));
+            W_TRY(fill(L.v, &L.tc_v));
+            W_TRY(fill(L.o, &L.tc_o));
+        } else {
+            W_TRY(fill(L.in_proj, &L.tc_in_proj));
+            W_TRY(fill(L.out_proj, &L.tc_out_proj));
+        }
+        W_TRY(fill(L.gate, &L.tc_gate));
+        W_TRY(fill(L.up, &L.tc_up));
+        W_TRY(fill(L.down, &L.tc_down));
+    }
+    for (int i = 0; i < 2; i++) {
+        CU_TRY(tc_make_activation_map(m->q8q, m->max_chunk, hs, i ? 128 : 64, &m->map_x_hs[i]));
+        CU_TRY(tc_make_activation_map(m->q8q, m->max_chunk, is, i ? 128 : 64, &m->map_x_is[i]));
+    }
+    CU_TRY(cudaStreamSynchronize(m->stream));
+    m->tc_ok = true;
+    m->prefill_tc = want;
+    return WICK_CUDA_OK;
 }
 
 int32_t reset_sequence(wick_cuda_model* m) {
@@ -614,6 +680,7 @@ int32_t build_model(wick_cuda_model* m, const GgufImage& g, uint32_t context_siz
     }
     CU_TRY(cudaEventCreate(&m->ev0));
     CU_TRY(cudaEventCreate(&m->ev1));
+    W_TRY(build_tc(m));
     W_TRY(build_mega(m));
     W_TRY(capture_graph(m, false, &m->g_logits, &m->nodes_logits));
     W_TRY(capture_graph(m, true, &m->g_greedy, &m->nodes_greedy));
@@ -819,10 +886,34 @@ int32_t wick_cuda_forward_prefill(wick_cuda_model* m, const uint32_t* tokens_hos
     memcpy(m->h_u32, newpos, 8);
     CU_TRY(cudaMemcpyAsync(&m->ctl->pos, m->h_u32 + 1, 4, cudaMemcpyHostToDevice, m->stream));
     CU_TRY(cudaMemcpyAsync(m->h_logits, m->logits, (size_t)m->cfg.vocab_size * 4, cudaMemcpyDeviceToHost, m->stream));
+    m->h_u32[2] = 0;
+    if (m->tc_err) CU_TRY(cudaMemcpyAsync(m->h_u32 + 2, m->tc_err, 4, cudaMemcpyDeviceToHost, m->stream));
     CU_TRY(cudaEventRecord(m->ev1, m->stream));
     CU_TRY(cudaStreamSynchronize(m->stream));
+    if (m->h_u32[2] != 0) {
+        const uint32_t code = m->h_u32[2];
+        cudaMemsetAsync(m->tc_err, 0, 4, m->stream);
+        return fail(WICK_CUDA_ERR_TIMEOUT, "tensor-core prefill GEMM: a bounded wait expired (role code " + std::to_string(code) + ")");
+    }
     memcpy(logits_host, m->h_logits, (size_t)m->cfg.vocab_size * 4);
     m->seq_len = start_pos + n;
+    return WICK_CUDA_OK;
+}
+
+int32_t wick_cuda_set_prefill_mode(wick_cuda_model* m, int32_t mode) {
+    W_TRY(check_model(m));
+    if (mode != WICK_CUDA_PREFILL_EXACT && mode != WICK_CUDA_PREFILL_TENSOR)
+        return fail(WICK_CUDA_ERR_BAD_ARG, "unknown prefill mode " + std::to_string(mode));
+    if (mode == WICK_CUDA_PREFILL_TENSOR && !m->tc_ok)
+        return fail(WICK_CUDA_ERR_BAD_ARG, "tensor-core prefill needs hidden and feed-forward sizes that are multiples of 128");
+    m->prefill_tc = mode == WICK_CUDA_PREFILL_TENSOR;
+    return WICK_CUDA_OK;
+}
+
+int32_t wick_cuda_prefill_mode(const wick_cuda_model* m, int32_t* mode) {
+    W_TRY(check_model(m));
+    if (!mode) return fail(WICK_CUDA_ERR_BAD_ARG, "mode is NULL");
+    *mode = m->prefill_tc ? WICK_CUDA_PREFILL_TENSOR : WICK_CUDA_PREFILL_EXACT;
     return WICK_CUDA_OK;
 }
 
@@ -1024,6 +1115,9 @@ void wick_cuda_weight_destroy(wick_cuda_weight* w) {
     if (!w) return;
     cudaFree((void*)w->w.q);
     cudaFree((void*)w->w.d);
+    cudaFree(w->tc.q);
+    cudaFree(w->tc.scales_t);
+    cudaFree(w->tc_err);
     delete w;
 }
 
@@ -1053,6 +1147,37 @@ int32_t wick_cuda_gemm_q8(const wick_cuda_weight* w, const float* bs_dev, const 
     if (!w || !bs_dev || !bq_dev || !out_dev) return fail(WICK_CUDA_ERR_BAD_ARG, "NULL argument");
     launch_gemm((cudaStream_t)stream, w->w, bs_dev, bq_dev, (int)n, out_dev);
     OP_END();
+}
+
+int32_t wick_cuda_gemm_q8_tc(wick_cuda_weight* w, const float* bs_dev, const int8_t* bq_dev, uint32_t n, float* out_dev,
+                             int32_t* block_sums_dev, void* stream) {
+    if (!w || !bs_dev || !bq_dev || !out_dev) return fail(WICK_CUDA_ERR_BAD_ARG, "NULL argument");
+    if (!tc_gemm_supported(w->w.m, w->w.k)) return fail(WICK_CUDA_ERR_BAD_ARG, "tensor-core GEMM needs k to be a multiple of 128");
+    if (n == 0) return WICK_CUDA_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (!w->tc.q) {
+        TcWeight t;
+        t.m = w->w.m;
+        t.k = w->w.k;
+        t.m_pad = (w->w.m + 127) / 128 * 128;
+        CU_TRY(cudaMalloc((void**)&t.q, t.q_bytes()));
+        CU_TRY(cudaMalloc((void**)&t.scales_t, t.s_bytes()));
+        CU_TRY(cudaMalloc((void**)&w->tc_err, 4));
+        CU_TRY(cudaMemsetAsync(w->tc_err, 0, 4, st));
+        w->tc = t;
+        CU_TRY(tc_weight_fill(st, w->w, &w->tc));
+    }
+    CUtensorMap map_x;
+    CU_TRY(tc_make_activation_map(bq_dev, (int)n, w->w.k, tc_gemm_bn((int)n), &map_x));
+    CU_TRY(launch_gemm_tc(st, w->tc, map_x, bs_dev, (int)n, out_dev, block_sums_dev, w->tc_err));
+    uint32_t code = 0;
+    CU_TRY(cudaMemcpyAsync(&code, w->tc_err, 4, cudaMemcpyDeviceToHost, st));
+    CU_TRY(cudaStreamSynchronize(st));
+    if (code != 0) {
+        cudaMemsetAsync(w->tc_err, 0, 4, st);
+        return fail(WICK_CUDA_ERR_TIMEOUT, "tensor-core GEMM: a bounded wait expired (role code " + std::to_string(code) + ")");
+    }
+    return WICK_CUDA_OK;
 }
 
 int32_t wick_cuda_block_sums(const wick_cuda_weight* w, const int8_t* xq_dev, int32_t* s_dev, void* stream) {

@@ -219,6 +219,17 @@ class CudaLfm2Model:
         check(self._lib.wick_cuda_decode_path(self._h, C.byref(v)))
         return "persistent" if v.value else "graph"
 
+    def prefill_mode(self) -> str:
+        """'tensor' (tcgen05 int8 GEMM, logits equal to f32 rounding) or 'exact' (bit-exact CUDA-core GEMM)."""
+        v = C.c_int32(0)
+        check(self._lib.wick_cuda_prefill_mode(self._h, C.byref(v)))
+        return "tensor" if v.value else "exact"
+
+    def set_prefill_mode(self, mode: str) -> None:
+        if mode not in ("exact", "tensor"):
+            raise ValueError("prefill mode must be 'exact' or 'tensor'")
+        check(self._lib.wick_cuda_set_prefill_mode(self._h, 1 if mode == "tensor" else 0))
+
     def decode_profile(self):
         """Timeline of the last decode step of the persistent kernel: (kinds [n], ns [n, 4])."""
         n = C.c_uint32(0)

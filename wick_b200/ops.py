@@ -79,6 +79,17 @@ def gemm_q8(w: QuantWeight, bs: torch.Tensor, bq: torch.Tensor, out: torch.Tenso
     return out
 
 
+def gemm_q8_tc(w: QuantWeight, bs: torch.Tensor, bq: torch.Tensor, want_sums: bool = False):
+    """The tensor-core (tcgen05) form of gemm_q8: exact int32 block sums, one fused f32 chain per output
+    in block order.  Returns out [n, m] (and the block sums [n, m, k/32] when asked).  Synchronises."""
+    n = bq.shape[0]
+    out = torch.empty((n, w.m), dtype=torch.float32, device=bq.device)
+    sums = torch.empty((n, w.m, w.k // 32), dtype=torch.int32, device=bq.device) if want_sums else None
+    check(_lib.load().wick_cuda_gemm_q8_tc(w._h, _ptr(bs), _ptr(bq), n, _ptr(out), _ptr(sums) if want_sums else None,
+                                           _stream()))
+    return (out, sums) if want_sums else out
+
+
 def block_sums(w: QuantWeight, xq: torch.Tensor) -> torch.Tensor:
     s = torch.empty((w.m, w.k // 32), dtype=torch.int32, device=xq.device)
     check(_lib.load().wick_cuda_block_sums(w._h, _ptr(xq), _ptr(s), _stream()))
