@@ -312,17 +312,43 @@ def main():
         line["cpu_baseline"] = {"value": cpu_tps, "unit": "tok/s", "cores": cores, "kind": "port",
                                 "sample": f"{PROMPT_TOKENS}-token prefill (untimed) + {sample_tokens} greedy decode tokens of the same model and prompt"}
     if world == 1 and not args.no_extra:
+        # side measurements (not the headline): prefill in both GEMM modes, and decode at tg512
         extra = {}
-        for n in (128, 1024, 4096):
-            toks = gs.random_prompt(n, spec.vocab, seed=7)
-            m.forward_prefill_chunked(toks, 0, st, 512)          # warm
-            t0 = time.perf_counter()
-            m.forward_prefill_chunked(toks, 0, st, 512)          # Session::append_tokens, ubatch 512
-            extra[f"prefill_p{n}_tok_s"] = n / (time.perf_counter() - t0)
+        gemm_flop_per_token = 2.0 * sum(
+            (3 * spec.hidden * spec.ffn) + ((spec.hidden * spec.hidden * 2 + 2 * spec.hidden * spec.kv_dim) if i in spec.attn_layers
+                                            else 4 * spec.hidden * spec.hidden)
+            for i in range(spec.n_layers))
+        tensor_peak = None
+        try:
+            with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+                tensor_peak = 2.0 * float(json.load(f)["bf16_tflops_sustained"])   # int8 dense = 2 x bf16 on this part
+        except Exception:
+            pass
+        for mode in ("exact", "tensor"):
+            try:
+                m.set_prefill_mode(mode)
+            except Exception as e:                      # tensor mode needs sizes that are multiples of 128
+                extra[f"prefill_{mode}"] = f"unavailable: {e}"
+                continue
+            for n, ub in ((128, 512), (1024, 512), (4096, 512), (4096, 0)):
+                toks = gs.random_prompt(n, spec.vocab, seed=7)
+                m.forward_prefill_chunked(toks, 0, st, ub)          # warm
+                t0 = time.perf_counter()
+                m.forward_prefill_chunked(toks, 0, st, ub)          # Session::append_tokens; ubatch 512 is wick's default
+                tps = n / (time.perf_counter() - t0)
+                key = f"prefill_{mode}_p{n}" + ("_one_call" if ub == 0 else "") + "_tok_s"
+                extra[key] = tps
+                if mode == "tensor" and n == 4096 and tensor_peak:
+                    extra[key.replace("_tok_s", "_gemm_frac_of_int8_peak")] = tps * gemm_flop_per_token / 1e12 / tensor_peak
+        m.set_prefill_mode("exact")
+        extra["int8_peak_tflops_used"] = tensor_peak
+        extra["int8_peak_source"] = "2 x bf16_tflops_sustained of MEASURED_PEAKS.json (no int8 figure is measured)"
+        extra["gemm_gflop_per_token"] = gemm_flop_per_token / 1e9
         logits = m.forward_prefill(prompt, 0, st)
         m.generate_greedy(int(np.argmax(logits)), 512, st)
         extra["decode_tg512_tok_s"] = 512 / (m.last_elapsed_ms() * 1e-3)
-        extra["prefill_path"] = "exact-order CUDA-core integer GEMM + exact-order attention"
+        extra["prefill_paths"] = {"exact": "bit-exact CUDA-core integer GEMM + exact-order attention (default)",
+                                  "tensor": "tcgen05 int8 GEMM (exact block sums, fused f32 chain) + exact-order attention"}
         line["extra"] = extra
     print(json.dumps(line))
     if world > 1:

@@ -108,11 +108,15 @@ int32_t wick_cuda_forward_greedy(wick_cuda_model* m, uint32_t token, uint32_t po
 int32_t wick_cuda_forward_prefill(wick_cuda_model* m, const uint32_t* tokens_host, uint32_t n,
                                   uint32_t start_pos, float* logits_host);
 
-/* Which GEMM forward_prefill uses for chunks of >= 16 tokens.  EXACT: the CUDA-core kernel that
- * reproduces the f32 accumulation order of gemm_q*_q8_0_neon (simd.rs:696-1019) bit for bit.
- * TENSOR (default when hidden and feed-forward sizes are multiples of 128; env
- * WICK_CUDA_PREFILL=exact selects EXACT at load): the tcgen05 kernel described at
- * wick_cuda_gemm_q8_tc, whose logits agree to f32 rounding.  Decode is not affected. */
+/* Which GEMM forward_prefill uses for chunks of >= 16 tokens.
+ * EXACT (default): the CUDA-core kernel that reproduces the f32 accumulation order of
+ * gemm_q*_q8_0_neon (simd.rs:696-1019) bit for bit, so logits and greedy tokens equal wick's CPU path.
+ * TENSOR (env WICK_CUDA_PREFILL=tensor at load, or this call; needs hidden and feed-forward sizes that
+ * are multiples of 128): the tcgen05 kernel described at wick_cuda_gemm_q8_tc.  Each product agrees
+ * with EXACT to f32 rounding, but the first last-bit difference that flips one Q8_0 rounding of a later
+ * activation (simd.rs:285-300) moves that activation by a whole quantisation step, so over a long
+ * prompt the logits end up one quantisation-noise realisation away from the CPU path's (a few 1e-2 on
+ * logits of order 1), like wick's own GPU backends.  Decode is not affected by this switch. */
 #define WICK_CUDA_PREFILL_EXACT 0
 #define WICK_CUDA_PREFILL_TENSOR 1
 int32_t wick_cuda_set_prefill_mode(wick_cuda_model* m, int32_t mode);

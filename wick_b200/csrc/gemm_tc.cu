@@ -17,15 +17,17 @@
 // and apply the scales on the CUDA cores: 3 instructions per (output, block), which is what bounds the
 // kernel (the tensor pipe needs about 1/6 of that time).
 //
-// Roles in a CTA of 12 warps (one CTA per SM, persistent over output tiles):
+// Roles in a CTA of 20 warps (one CTA per SM, persistent over output tiles):
 //   warp 0  lane 0: TMA producer, one K=128 stage (4 blocks) of W rows and activation rows per step
 //   warp 1  lane 0: issues tcgen05.mma / tcgen05.commit; the whole warp owns the TMEM allocation
 //   warp 2        : copies the stage's weight scales and (transposed) activation scales into smem
-//   warps 4..11   : epilogue; warp w reads TMEM lanes 32*(w%4).. and columns (w-4)/4 * BN/2 ..
+//   warps 4..19   : epilogue; warp w reads TMEM lanes 32*(w%4).. and columns (w-4)/4 * BN/4 ..; four
+//                   warps per scheduler hide the tensor-memory load and barrier latencies
 // Every wait is bounded: on expiry the kernel records an error code, all roles leave their loops and
 // the CTA frees its tensor memory and exits.
 #include <cuda.h>
 #include <cuda_runtime.h>
+#include <cstring>
 #include <mutex>
 
 #include "gemm_tc.cuh"
@@ -38,8 +40,9 @@ constexpr int TC_BM = 128;          // weight rows per tile == TMEM lanes
 constexpr int TC_KSTAGE = 128;      // int8 elements (bytes) per row per stage == one 128B swizzle atom
 constexpr int TC_KB_PER_STAGE = TC_KSTAGE / QK;  // 4 quantisation blocks per stage
 constexpr int TC_STAGES = 4;
-constexpr int TC_THREADS = 384;
-constexpr int TC_EPI_WARPS = 8;
+constexpr int TC_COL_GROUPS = 4;    // epilogue warps per TMEM lane quarter; each takes BN/4 columns
+constexpr int TC_EPI_WARPS = 4 * TC_COL_GROUPS;
+constexpr int TC_THREADS = 32 * (4 + TC_EPI_WARPS);
 constexpr uint32_t TC_SPIN_LIMIT = 1u << 18;  // try_wait itself suspends for a while, so this is of the order of a second
 
 template <int BN>
@@ -140,29 +143,57 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, int32_t* r) {
         : "r"(taddr)
         : "memory");
 }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, int32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+template <int COLS>
+__device__ __forceinline__ void tmem_ld(uint32_t taddr, int32_t* r) {
+    static_assert(COLS == 16 || COLS == 32, "one tcgen05.ld per k-block");
+    if constexpr (COLS == 16) tmem_ld16(taddr, r);
+    else tmem_ld32(taddr, r);
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 }  // namespace
 
+
 namespace {
+
+// Which matrix and which 128 x BN output tile a linear tile index means.  Tiles of one matrix are
+// consecutive, token tiles fastest, so CTAs running side by side share a weight tile in L2.
+struct TcTile {
+    int mat, m0, n0;
+};
+__device__ __forceinline__ TcTile tc_decode_tile(const TcJob& job, int t, int tiles_n, int bn) {
+    TcTile r;
+    r.mat = (t >= job.tile_start[1] ? 1 : 0) + (t >= job.tile_start[2] ? 1 : 0);
+    const int local = t - job.tile_start[r.mat];
+    r.m0 = (local / tiles_n) * TC_BM;
+    r.n0 = (local % tiles_n) * bn;
+    return r;
+}
 
 template <int BN, bool SUMS>
 __global__ void __launch_bounds__(TC_THREADS, 1)
-k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-          const float* __restrict__ w_scales_t,  // [k/32][m_pad]
-          const float* __restrict__ x_scales,    // [n][k/32]
-          float* __restrict__ out,               // [n][m]
-          int32_t* __restrict__ sums,            // optional [n][m][k/32]
-          int m, int m_pad, int n, int k, uint32_t* err) {
+k_gemm_tc(const __grid_constant__ TcJob job, const __grid_constant__ CUtensorMap map_x,
+          const float* __restrict__ x_scales,  // [n][k/32]
+          int32_t* __restrict__ sums,          // optional [n][m][k/32] (single-matrix jobs only)
+          int n, int k, uint32_t* err) {
     extern __shared__ uint8_t tc_smem_raw[];
     TcSmem<BN>* sm = reinterpret_cast<TcSmem<BN>*>((reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
     constexpr int NBUF = 512 / BN;
-    constexpr int COLS = BN / 2;  // columns per epilogue thread
+    constexpr int COLS = BN / TC_COL_GROUPS;  // columns per epilogue thread
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nb = k / QK;
     const int k_stages = k / TC_KSTAGE;
     const int tiles_n = (n + BN - 1) / BN;
-    const int tiles = (m_pad / TC_BM) * tiles_n;
+    const int tiles = job.tile_start[job.count];
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < TC_STAGES; s++) {
@@ -193,7 +224,8 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
             uint32_t g = 0;
             bool ok = true;
             for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
-                const int m0 = (t / tiles_n) * TC_BM, n0 = (t % tiles_n) * BN;
+                const TcTile tl = tc_decode_tile(job, t, tiles_n, BN);
+                const CUtensorMap* mw = &job.map_w[tl.mat];
                 for (int ks = 0; ks < k_stages; ks++, g++) {
                     const int s = g % TC_STAGES;
                     const uint32_t u = g / TC_STAGES;
@@ -201,8 +233,8 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                     if (!ok) break;
                     const uint32_t bar = smem_u32(&sm->full[s]);
                     mbar_arrive_expect_tx(bar, (TC_BM + BN) * TC_KSTAGE);
-                    tma_load_2d(smem_u32(sm->stage[s].a), &map_w, bar, ks * TC_KSTAGE, m0);
-                    tma_load_2d(smem_u32(sm->stage[s].b), &map_x, bar, ks * TC_KSTAGE, n0);
+                    tma_load_2d(smem_u32(sm->stage[s].a), mw, bar, ks * TC_KSTAGE, tl.m0);
+                    tma_load_2d(smem_u32(sm->stage[s].b), &map_x, bar, ks * TC_KSTAGE, tl.n0);
                 }
             }
         }
@@ -241,7 +273,9 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
         uint32_t g = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
-            const int m0 = (t / tiles_n) * TC_BM, n0 = (t % tiles_n) * BN;
+            const TcTile tl = tc_decode_tile(job, t, tiles_n, BN);
+            const float* wst = job.scales_t[tl.mat];
+            const int m_pad = job.m_pad[tl.mat];
             for (int ks = 0; ks < k_stages; ks++, g++) {
                 const int s = g % TC_STAGES;
                 const uint32_t u = g / TC_STAGES;
@@ -252,13 +286,13 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                 const int b0 = ks * TC_KB_PER_STAGE;
 #pragma unroll
                 for (int kk = 0; kk < TC_KB_PER_STAGE; kk++) {
-                    const float4 v = __ldg(reinterpret_cast<const float4*>(w_scales_t + (size_t)(b0 + kk) * m_pad + m0) + lane);
+                    const float4 v = __ldg(reinterpret_cast<const float4*>(wst + (size_t)(b0 + kk) * m_pad + tl.m0) + lane);
                     reinterpret_cast<float4*>(st.sw[kk])[lane] = v;
                 }
 #pragma unroll
                 for (int c = lane; c < BN; c += 32) {
                     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (n0 + c < n) v = __ldg(reinterpret_cast<const float4*>(x_scales + (size_t)(n0 + c) * nb + b0));
+                    if (tl.n0 + c < n) v = __ldg(reinterpret_cast<const float4*>(x_scales + (size_t)(tl.n0 + c) * nb + b0));
                     st.sx[0][c] = v.x;
                     st.sx[1][c] = v.y;
                     st.sx[2][c] = v.z;
@@ -270,15 +304,16 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
         }
     } else if (warp >= 4) {
         // ── epilogue ─────────────────────────────────────────────────────────
-        const int quarter = warp & 3, half = (warp - 4) >> 2;
+        const int quarter = warp & 3, cg = (warp - 4) >> 2;
         const int row_in_tile = quarter * 32 + lane;
-        const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(half * COLS);
+        const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(cg * COLS);
         float acc[COLS];
         uint32_t g = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
-            const int m0 = (t / tiles_n) * TC_BM, n0 = (t % tiles_n) * BN;
-            const int row = m0 + row_in_tile;
+            const TcTile tl = tc_decode_tile(job, t, tiles_n, BN);
+            const int m = job.m[tl.mat];
+            const int row = tl.m0 + row_in_tile;
 #pragma unroll
             for (int c = 0; c < COLS; c++) acc[c] = 0.f;
             for (int ks = 0; ks < k_stages && ok; ks++, g++) {
@@ -297,14 +332,13 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                     if (!ok) break;
                     tc_fence_after();
                     int32_t S[COLS];
-#pragma unroll
-                    for (int c = 0; c < COLS; c += 32) tmem_ld32(lane_base + buf * BN + c, S + c);
+                    tmem_ld<COLS>(lane_base + buf * BN, S);
                     tmem_ld_wait();
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(smem_u32(&sm->tmem_empty[buf]));
                     const float sw = st.sw[kk][row_in_tile];
-                    const float4* sx4 = reinterpret_cast<const float4*>(&st.sx[kk][half * COLS]);
+                    const float4* sx4 = reinterpret_cast<const float4*>(&st.sx[kk][cg * COLS]);
 #pragma unroll
                     for (int c = 0; c < COLS; c += 4) {
                         const float4 x = sx4[c >> 2];
@@ -317,7 +351,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                         const int b = ks * TC_KB_PER_STAGE + kk;
 #pragma unroll
                         for (int c = 0; c < COLS; c++) {
-                            const int tok = n0 + half * COLS + c;
+                            const int tok = tl.n0 + cg * COLS + c;
                             if (tok < n) sums[((size_t)tok * m + row) * nb + b] = S[c];
                         }
                     }
@@ -327,9 +361,10 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                 if (lane == 0) mbar_arrive(smem_u32(&sm->empty[s]));
             }
             if (ok && row < m) {
+                float* out = job.out[tl.mat];
 #pragma unroll
                 for (int c = 0; c < COLS; c++) {
-                    const int tok = n0 + half * COLS + c;
+                    const int tok = tl.n0 + cg * COLS + c;
                     if (tok < n) out[(size_t)tok * m + row] = acc[c];
                 }
             }
@@ -417,7 +452,7 @@ cudaError_t encode_rows_map(const void* base, int rows, int k, int box_rows, CUt
 }
 
 template <int BN>
-cudaError_t launch_tc(cudaStream_t st, const TcWeight& w, const CUtensorMap& map_x, const float* x_scales, int n, float* out,
+cudaError_t launch_tc(cudaStream_t st, const TcJob& job, const CUtensorMap& map_x, const float* x_scales, int n, int k,
                       int32_t* sums, uint32_t* err) {
     static int sm_count = 0;
     static bool configured = false;
@@ -434,13 +469,13 @@ cudaError_t launch_tc(cudaStream_t st, const TcWeight& w, const CUtensorMap& map
         if (e != cudaSuccess) return e;
         configured = true;
     }
-    const int tiles = (w.m_pad / TC_BM) * ((n + BN - 1) / BN);
+    const int tiles = job.tile_start[job.count];
     const int grid = tiles < sm_count ? tiles : sm_count;
     g_kernel_launches++;
     if (sums)
-        k_gemm_tc<BN, true><<<grid, TC_THREADS, smem, st>>>(w.map, map_x, w.scales_t, x_scales, out, sums, w.m, w.m_pad, n, w.k, err);
+        k_gemm_tc<BN, true><<<grid, TC_THREADS, smem, st>>>(job, map_x, x_scales, sums, n, k, err);
     else
-        k_gemm_tc<BN, false><<<grid, TC_THREADS, smem, st>>>(w.map, map_x, w.scales_t, x_scales, out, sums, w.m, w.m_pad, n, w.k, err);
+        k_gemm_tc<BN, false><<<grid, TC_THREADS, smem, st>>>(job, map_x, x_scales, sums, n, k, err);
     return cudaGetLastError();
 }
 
@@ -448,7 +483,12 @@ cudaError_t launch_tc(cudaStream_t st, const TcWeight& w, const CUtensorMap& map
 
 bool tc_gemm_supported(int m, int k) { return m > 0 && k > 0 && k % TC_KSTAGE == 0; }
 
-int tc_gemm_bn(int n) { return n <= 64 ? 64 : 128; }
+int tc_gemm_bn(int n, int row_tiles) {
+    // 128-token tiles halve the weight-tile traffic; 64-token tiles are used while the wider ones
+    // would leave the grid at less than two tiles per SM
+    if (n <= 64) return 64;
+    return row_tiles * ((n + 127) / 128) < 2 * 148 ? 64 : 128;
+}
 
 cudaError_t tc_weight_fill(cudaStream_t st, const DevWeight& w, TcWeight* out) {
     out->m = w.m;
@@ -470,11 +510,33 @@ cudaError_t tc_make_activation_map(const int8_t* xq, int rows_cap, int k, int bn
     return encode_rows_map(xq, rows_cap, k, bn, out);
 }
 
-cudaError_t launch_gemm_tc(cudaStream_t st, const TcWeight& w, const CUtensorMap& map_x, const float* x_scales, int n,
-                           float* out, int32_t* sums, uint32_t* err) {
-    if (n <= 0) return cudaSuccess;
-    return tc_gemm_bn(n) == 64 ? launch_tc<64>(st, w, map_x, x_scales, n, out, sums, err)
-                               : launch_tc<128>(st, w, map_x, x_scales, n, out, sums, err);
+cudaError_t launch_gemm_tc(cudaStream_t st, const TcWeight* const* w, float* const* out, int count, const CUtensorMap* map_x,
+                           const float* x_scales, int n, int32_t* sums, uint32_t* err) {
+    if (n <= 0 || count <= 0) return cudaSuccess;
+    if (count > 3 || (sums && count != 1)) return cudaErrorInvalidValue;
+    int rows = 0;
+    for (int i = 0; i < count; i++) rows += w[i]->m_pad / TC_BM;
+    const int bn = tc_gemm_bn(n, rows);
+    const int tiles_n = (n + bn - 1) / bn;
+    TcJob job;
+    memset(&job, 0, sizeof(job));
+    job.count = count;
+    int t = 0;
+    for (int i = 0; i < 3; i++) {
+        job.tile_start[i] = t;
+        if (i >= count) continue;
+        if (w[i]->k != w[0]->k) return cudaErrorInvalidValue;
+        job.map_w[i] = w[i]->map;
+        job.scales_t[i] = w[i]->scales_t;
+        job.out[i] = out[i];
+        job.m[i] = w[i]->m;
+        job.m_pad[i] = w[i]->m_pad;
+        t += (w[i]->m_pad / TC_BM) * tiles_n;
+    }
+    job.tile_start[3] = t;
+    for (int i = count; i < 3; i++) job.tile_start[i] = t;  // unused matrices own no tiles
+    return bn == 64 ? launch_tc<64>(st, job, map_x[0], x_scales, n, w[0]->k, sums, err)
+                    : launch_tc<128>(st, job, map_x[1], x_scales, n, w[0]->k, sums, err);
 }
 
 }  // namespace wick

@@ -18,10 +18,21 @@ struct TcWeight {
     size_t s_bytes() const { return (size_t)(k / QK) * m_pad * sizeof(float); }
 };
 
+// Up to three matrices with the same k that share one set of quantised activations (gate + up, or
+// Q + K + V): their tiles are scheduled as one grid so that narrow matrices do not leave SMs idle.
+struct TcJob {
+    CUtensorMap map_w[3];
+    const float* scales_t[3];
+    float* out[3];        // [n][m[i]] each
+    int m[3], m_pad[3];
+    int tile_start[4];    // first linear tile of each matrix; [count..3] = total
+    int count;
+};
+
 // True when the shapes meet the kernel's requirements (k a multiple of 128).
 bool tc_gemm_supported(int m, int k);
-// Rows of tokens per tile the launcher will choose for n tokens (64 or 128).
-int tc_gemm_bn(int n);
+// Tokens per tile (64 or 128) the launcher chooses for n tokens and `row_tiles` 128-row tiles.
+int tc_gemm_bn(int n, int row_tiles);
 
 // Fills `out` (q / scales_t must already point at q_bytes() / s_bytes() of device memory, zeroed by
 // this call) from the grouped layout of `w`, and encodes its tensor map.  Returns cudaSuccess or the
@@ -31,10 +42,11 @@ cudaError_t tc_weight_fill(cudaStream_t st, const DevWeight& w, TcWeight* out);
 // Tensor map over quantised activations xq [rows_cap][k] int8 with a box of bn rows.
 cudaError_t tc_make_activation_map(const int8_t* xq, int rows_cap, int k, int bn, CUtensorMap* out);
 
-// out[j][i] for j < n, i < m (token-major, like launch_gemm).  `map_x` must have been made with
-// tc_gemm_bn(n) rows per box.  sums: optional [n][m][k/32] int32 block sums.  err: device word
-// that receives a non-zero code if a bounded wait expired.
-cudaError_t launch_gemm_tc(cudaStream_t st, const TcWeight& w, const CUtensorMap& map_x, const float* x_scales, int n,
-                           float* out, int32_t* sums, uint32_t* err);
+// out[i][j][r] for matrix i < count (<= 3, equal k), token j < n, row r < m_i (token-major, like
+// launch_gemm).  map_x[0] / map_x[1]: activation maps with 64 / 128 rows per box.  sums: optional
+// [n][m][k/32] int32 block sums (count == 1 only).  err: device word that receives a non-zero code
+// if a bounded wait expired.
+cudaError_t launch_gemm_tc(cudaStream_t st, const TcWeight* const* w, float* const* out, int count, const CUtensorMap* map_x,
+                           const float* x_scales, int n, int32_t* sums, uint32_t* err);
 
 }  // namespace wick

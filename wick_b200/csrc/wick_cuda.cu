@@ -8,6 +8,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <fstream>
+#include <initializer_list>
 #include <memory>
 #include <string>
 #include <vector>
@@ -73,7 +74,7 @@ struct wick_cuda_model {
     float *rope_cos = nullptr, *rope_sin = nullptr;
     int max_chunk = 0;  // tokens of scratch
     // tensor-core prefill path: available when every matrix meets tc_gemm_supported(); `prefill_tc`
-    // selects it (default) or the bit-exact CUDA-core GEMM
+    // selects it instead of the bit-exact CUDA-core GEMM (the default)
     bool tc_ok = false, prefill_tc = false;
     CUtensorMap map_x_hs[2], map_x_is[2];  // activations [max_chunk][hs | is], box of 64 / 128 rows
     uint32_t* tc_err = nullptr;
@@ -437,17 +438,28 @@ void enqueue_prefill_chunk(wick_cuda_model* m, int n, int start_pos, bool flash,
     cudaStream_t st = m->stream;
     const int hs = m->cfg.hidden_size, is = m->cfg.intermediate_size, hd = m->head_dim;
     const float eps = m->cfg.rms_norm_eps;
-    // tensor-core path for chunks wide enough to fill an MMA tile; the exact kernel otherwise
+    // tensor-core path for chunks wide enough to fill an MMA tile; the exact kernel otherwise.
+    // Up to three matrices that read the same quantised input go out as one launch.
     const bool tc = m->prefill_tc && m->tc_ok && n >= 16;
-    const int bi = tc_gemm_bn(n) == 64 ? 0 : 1;
-    auto launch_gemm = [&](cudaStream_t s_, const DevWeight& w, const float* bs, const int8_t* bq, int n_, float* out,
-                           const TcWeight* t = nullptr) {
-        if (tc && t && t->q) {
-            const CUtensorMap& mx = w.k == hs ? m->map_x_hs[bi] : m->map_x_is[bi];
-            cudaError_t e = launch_gemm_tc(s_, *t, mx, bs, n_, out, nullptr, m->tc_err);
+    struct G {
+        const DevWeight* w;
+        const TcWeight* t;
+        float* out;
+    };
+    auto gemms = [&](std::initializer_list<G> list) {
+        if (tc) {
+            const TcWeight* tw[3];
+            float* outs[3];
+            int c = 0;
+            for (const G& g : list) {
+                tw[c] = g.t;
+                outs[c++] = g.out;
+            }
+            const CUtensorMap* mx = tw[0]->k == hs ? m->map_x_hs : m->map_x_is;
+            cudaError_t e = launch_gemm_tc(st, tw, outs, c, mx, m->q8s, n, nullptr, m->tc_err);
             (void)e;  // surfaced by the cudaGetLastError() check after the chunk
         } else {
-            wick::launch_gemm(s_, w, bs, bq, n_, out);
+            for (const G& g : list) launch_gemm(st, *g.w, m->q8s, m->q8q, n, g.out);
         }
     };
     launch_embed(st, m->embd, m->tokens_dev, nullptr, m->hidden, n);
@@ -456,13 +468,11 @@ void enqueue_prefill_chunk(wick_cuda_model* m, int n, int start_pos, bool flash,
         Layer& L = m->layers[li];
         launch_add_rmsnorm_quant(st, m->hidden, pending, L.attn_norm, eps, n, hs, m->q8s, m->q8q, nullptr);
         if (!L.is_attn) {
-            launch_gemm(st, L.in_proj, m->q8s, m->q8q, n, m->proj, &L.tc_in_proj);
+            gemms({{&L.in_proj, &L.tc_in_proj, m->proj}});
             launch_shortconv(st, m->proj, L.conv_w, L.conv_state, n, hs, m->cfg.conv_kernel_size, nullptr, m->q8s, m->q8q);
-            launch_gemm(st, L.out_proj, m->q8s, m->q8q, n, m->block_out, &L.tc_out_proj);
+            gemms({{&L.out_proj, &L.tc_out_proj, m->block_out}});
         } else {
-            launch_gemm(st, L.q, m->q8s, m->q8q, n, m->qbuf, &L.tc_q);
-            launch_gemm(st, L.k, m->q8s, m->q8q, n, m->kbuf, &L.tc_k);
-            launch_gemm(st, L.v, m->q8s, m->q8q, n, m->vbuf, &L.tc_v);
+            gemms({{&L.q, &L.tc_q, m->qbuf}, {&L.k, &L.tc_k, m->kbuf}, {&L.v, &L.tc_v, m->vbuf}});
             launch_qknorm_rope_kv(st, m->qbuf, m->kbuf, m->vbuf, L.q_norm, L.k_norm, eps, m->rope_cos, m->rope_sin, L.k_cache,
                                   L.v_cache, n, start_pos, nullptr, m->cfg.n_heads, L.n_kv, hd);
             if (flash)
@@ -471,13 +481,12 @@ void enqueue_prefill_chunk(wick_cuda_model* m, int n, int start_pos, bool flash,
                 launch_attention_naive(st, m->qbuf, L.k_cache, L.v_cache, m->attn_out, n, start_pos, nullptr, m->cfg.n_heads,
                                        L.n_kv, hd, m->cfg.max_seq_len);
             launch_quant_rows(st, m->attn_out, n, hs, m->q8s, m->q8q);
-            launch_gemm(st, L.o, m->q8s, m->q8q, n, m->block_out, &L.tc_o);
+            gemms({{&L.o, &L.tc_o, m->block_out}});
         }
         launch_add_rmsnorm_quant(st, m->hidden, m->block_out, L.ffn_norm, eps, n, hs, m->q8s, m->q8q, nullptr);
-        launch_gemm(st, L.gate, m->q8s, m->q8q, n, m->gate, &L.tc_gate);
-        launch_gemm(st, L.up, m->q8s, m->q8q, n, m->up, &L.tc_up);
+        gemms({{&L.gate, &L.tc_gate, m->gate}, {&L.up, &L.tc_up, m->up}});
         launch_silu_mul_quant(st, m->gate, m->up, n, is, m->q8s, m->q8q, nullptr);
-        launch_gemm(st, L.down, m->q8s, m->q8q, n, m->ffn_out, &L.tc_down);
+        gemms({{&L.down, &L.tc_down, m->ffn_out}});
         pending = m->ffn_out;
     }
     if (want_logits) {
@@ -495,7 +504,7 @@ int32_t build_tc(wick_cuda_model* m) {
     const int hs = m->cfg.hidden_size, is = m->cfg.intermediate_size;
     m->tc_ok = false;
     const char* mode = getenv("WICK_CUDA_PREFILL");
-    const bool want = !(mode && strcmp(mode, "exact") == 0);
+    const bool want = mode && strcmp(mode, "tensor") == 0;  // the bit-exact GEMM is the default
     bool ok = tc_gemm_supported(hs, hs) && tc_gemm_supported(hs, is);
     if (!ok) return WICK_CUDA_OK;
     W_TRY(dev_alloc(m, &m->tc_err, 1));
@@ -1167,9 +1176,12 @@ int32_t wick_cuda_gemm_q8_tc(wick_cuda_weight* w, const float* bs_dev, const int
         w->tc = t;
         CU_TRY(tc_weight_fill(st, w->w, &w->tc));
     }
-    CUtensorMap map_x;
-    CU_TRY(tc_make_activation_map(bq_dev, (int)n, w->w.k, tc_gemm_bn((int)n), &map_x));
-    CU_TRY(launch_gemm_tc(st, w->tc, map_x, bs_dev, (int)n, out_dev, block_sums_dev, w->tc_err));
+    CUtensorMap map_x[2];
+    CU_TRY(tc_make_activation_map(bq_dev, (int)n, w->w.k, 64, &map_x[0]));
+    CU_TRY(tc_make_activation_map(bq_dev, (int)n, w->w.k, 128, &map_x[1]));
+    const TcWeight* tw[1] = {&w->tc};
+    float* outs[1] = {out_dev};
+    CU_TRY(launch_gemm_tc(st, tw, outs, 1, map_x, bs_dev, (int)n, block_sums_dev, w->tc_err));
     uint32_t code = 0;
     CU_TRY(cudaMemcpyAsync(&code, w->tc_err, 4, cudaMemcpyDeviceToHost, st));
     CU_TRY(cudaStreamSynchronize(st));
