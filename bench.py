@@ -127,6 +127,7 @@ def cpu_baseline(path: str, spec, sample_tokens: int, warm: int = 2):
     from wick_b200 import gguf_synth as gs
     from oracle import oracle as orc
     orc.build()
+    orc.set_num_threads(len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1))
     om = orc.OracleModel(path, 4096)
     toks = gs.random_prompt(PROMPT_TOKENS, spec.vocab, seed=1)
     lg = om.forward_prefill(toks, 0)
@@ -144,6 +145,8 @@ def run_reference(args, rank: int, world: int):
     from wick_b200 import gguf_synth as gs
     from oracle import oracle as orc
     orc.build()
+    # all host threads this process may use (torchrun exports OMP_NUM_THREADS=1 for its workers)
+    orc.set_num_threads(len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1))
     path, spec = model_file(args, 0, 1)
     om = orc.OracleModel(path, 4096)
     toks = gs.random_prompt(PROMPT_TOKENS, spec.vocab, seed=1)
