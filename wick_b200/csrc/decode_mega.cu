@@ -257,31 +257,51 @@ __device__ void grid_arrive(Ctx& c) {
 constexpr int MAXJ = 16;  // blocks per warp: inputs up to NC * MAXJ * 32 = 7680 elements
 constexpr int FASTJ = 5;  // inputs of up to NC * FASTJ * 32 = 2400 elements take the short path
 
-// Quantises blocks cw + j*NC (j < J, those below nb) whose element `lane` is v[j].  The J
-// reductions are independent and interleaved by hand so their shuffle latencies overlap.
+// Quantises blocks cw + j*NC (j < J, those below nb) whose element `lane` is v[j].
+// The J block maxima are reduced "transposed": in every halving round a lane keeps half of its
+// values and hands the other half to its partner, so after log2(JP) rounds lane L holds the
+// maximum of block L >> SH only.  That costs JP + log2(32/JP) - 1 shuffles instead of 5 * J, and
+// each lane then performs the two IEEE divisions of ONE block instead of all J (the inverse
+// scales travel back by one shuffle per block).  max is exact, so the order does not matter.
 template <int J>
 __device__ __forceinline__ void quantize_blocks(Ctx& c, const float (&v)[J], int j0, int nb) {
-    float a[J];
+    static_assert(J >= 1 && J <= 16, "at most 16 blocks per call");
+    constexpr int JP = J <= 4 ? 4 : (J <= 8 ? 8 : 16);
+    constexpr int LOG = JP == 4 ? 2 : (JP == 8 ? 3 : 4);
+    constexpr int SH = 5 - LOG;  // lanes per block after the halving rounds: 1 << SH
+    float a[JP];
 #pragma unroll
-    for (int j = 0; j < J; j++) a[j] = fabsf(v[j]);
+    for (int j = 0; j < JP; j++) a[j] = j < J ? fabsf(v[j]) : 0.0f;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
+    for (int r = 0; r < LOG; r++) {
+        const int n = JP >> r, sft = 16 >> r;
+        const bool up = (c.lane & sft) != 0;
 #pragma unroll
-        for (int j = 0; j < J; j++) a[j] = fmaxf(a[j], __shfl_xor_sync(0xffffffffu, a[j], o));
+        for (int i = 0; i < n / 2; i++) {
+            const float keep = up ? a[i + n / 2] : a[i];
+            const float send = up ? a[i] : a[i + n / 2];
+            a[i] = fmaxf(keep, __shfl_xor_sync(0xffffffffu, send, sft));
+        }
+    }
+#pragma unroll
+    for (int sft = (16 >> LOG); sft > 0; sft >>= 1) a[0] = fmaxf(a[0], __shfl_xor_sync(0xffffffffu, a[0], sft));
+    // this lane's block
+    const int jm = c.lane >> SH;
+    const float d = __fdiv_rn(a[0], 127.0f);
+    const float id = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+    {
+        const int b = c.cw + (j0 + jm) * NC;
+        if ((c.lane & ((1 << SH) - 1)) == 0 && jm < J && b < nb) {
+            const float sc = __half2float(__float2half_rn(d));
+            c.S.xs[b] = sc;
+            c.S.xs16[b] = __fmul_rn(sc, 0.0625f);
+        }
     }
 #pragma unroll
     for (int j = 0; j < J; j++) {
+        const float idj = __shfl_sync(0xffffffffu, id, j << SH);
         const int b = c.cw + (j0 + j) * NC;
-        if (b < nb) {
-            const float d = __fdiv_rn(a[j], 127.0f);
-            const float id = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
-            c.S.xq[b * QK + c.lane] = (int8_t)__float2int_rn(__fmul_rn(v[j], id));
-            if (c.lane == 0) {
-                const float sc = __half2float(__float2half_rn(d));
-                c.S.xs[b] = sc;
-                c.S.xs16[b] = __fmul_rn(sc, 0.0625f);
-            }
-        }
+        if (b < nb) c.S.xq[b * QK + c.lane] = (int8_t)__float2int_rn(__fmul_rn(v[j], idj));
     }
 }
 
