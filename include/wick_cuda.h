@@ -108,19 +108,27 @@ int32_t wick_cuda_forward_greedy(wick_cuda_model* m, uint32_t token, uint32_t po
 int32_t wick_cuda_forward_prefill(wick_cuda_model* m, const uint32_t* tokens_host, uint32_t n,
                                   uint32_t start_pos, float* logits_host);
 
-/* Which GEMM forward_prefill uses for chunks of >= 16 tokens.
- * EXACT (default): the CUDA-core kernel that reproduces the f32 accumulation order of
- * gemm_q*_q8_0_neon (simd.rs:696-1019) bit for bit, so logits and greedy tokens equal wick's CPU path.
- * TENSOR (env WICK_CUDA_PREFILL=tensor at load, or this call; needs hidden and feed-forward sizes that
- * are multiples of 128): the tcgen05 kernel described at wick_cuda_gemm_q8_tc.  Each product agrees
- * with EXACT to f32 rounding, but the first last-bit difference that flips one Q8_0 rounding of a later
- * activation (simd.rs:285-300) moves that activation by a whole quantisation step, so over a long
- * prompt the logits end up one quantisation-noise realisation away from the CPU path's (a few 1e-2 on
- * logits of order 1), like wick's own GPU backends.  Decode is not affected by this switch. */
+/* Which GEMM forward_prefill uses for chunks of >= 16 tokens (shorter chunks always take the
+ * CUDA-core kernel).  Decode is not affected.
+ * EXACT (default): the arithmetic of gemm_q*_q8_0_neon (simd.rs:696-1019) bit for bit, so logits and
+ *   greedy tokens equal wick's CPU path.  When hidden and feed-forward sizes are multiples of 128 it
+ *   runs on the tensor cores: tcgen05 int8 MMAs against lane-group-masked activations produce the
+ *   four int32 lane partials of every block, and the epilogue keeps the reference's eight unfused f32
+ *   chains per output; otherwise on the CUDA-core kernel.
+ * EXACT_CUDA_CORES (env WICK_CUDA_PREFILL=exact-cuda-cores): always the CUDA-core kernel (same bits).
+ * TENSOR (env WICK_CUDA_PREFILL=tensor; needs the multiples of 128): the kernel described at
+ *   wick_cuda_gemm_q8_tc.  Each product agrees with EXACT to f32 rounding, but the first last-bit
+ *   difference that flips one Q8_0 rounding of a later activation (simd.rs:285-300) moves that
+ *   activation by a whole quantisation step, so over a long prompt the logits end up one
+ *   quantisation-noise realisation away from the CPU path's (a few 1e-2 on logits of order 1), like
+ *   wick's own GPU backends. */
 #define WICK_CUDA_PREFILL_EXACT 0
 #define WICK_CUDA_PREFILL_TENSOR 1
+#define WICK_CUDA_PREFILL_EXACT_CUDA_CORES 2
 int32_t wick_cuda_set_prefill_mode(wick_cuda_model* m, int32_t mode);
 int32_t wick_cuda_prefill_mode(const wick_cuda_model* m, int32_t* mode);
+/* 1 when the selected mode runs its GEMMs on the tensor cores for this model. */
+int32_t wick_cuda_prefill_uses_tensor_cores(const wick_cuda_model* m, int32_t* yes);
 /* Greedy decode loop of Session::generate (wick/src/session.rs:1186-1257) kept on the GPU:
  * feeds `first_token`, then each step's argmax, for n_steps steps; out_tokens_host[i] is the
  * token chosen by step i.  Equivalent to n_steps wick_cuda_forward_greedy calls without the
@@ -200,6 +208,11 @@ int32_t wick_cuda_gemm_q8(const wick_cuda_weight* w, const float* bs_dev, const 
  * WICK_CUDA_ERR_TIMEOUT) and, on its first call for a weight, allocates that weight's int8 copy. */
 int32_t wick_cuda_gemm_q8_tc(wick_cuda_weight* w, const float* bs_dev, const int8_t* bq_dev, uint32_t n,
                              float* out_dev, int32_t* block_sums_dev, void* stream);
+/* The bit-exact product on the tensor cores (the default GEMM of forward_prefill): same result as
+ * wick_cuda_gemm_q8, bit for bit.  Needs k % 128 == 0.  Allocates a temporary for the masked
+ * activations and synchronises `stream` (operator entry point for tests). */
+int32_t wick_cuda_gemm_q8_tc_exact(wick_cuda_weight* w, const float* bs_dev, const int8_t* bq_dev, uint32_t n,
+                                   float* out_dev, void* stream);
 /* int32 block dot sums S[i][b] = sum over the 32 elements of block b of row i (the vdotq_s32
  * lanes of simd.rs:381-383 added up) against one quantised column. */
 int32_t wick_cuda_block_sums(const wick_cuda_weight* w, const int8_t* xq_dev, int32_t* s_dev, void* stream);

@@ -79,6 +79,46 @@ def test_gemm_tc_matmul_sweep(ops, orc, dtype, n):
     check_against_oracle(ops, orc, dtype, 6912, 2048, n, seed=3, oracle_tokens=sorted({0, n - 1}))
 
 
+@pytest.mark.parametrize("dtype", ["q4_0", "q8_0"])
+@pytest.mark.parametrize("m,k,n", [
+    (128, 128, 16), (128, 512, 64), (256, 1152, 17), (384, 2048, 128), (200, 256, 37), (130, 384, 129), (64, 128, 1),
+    (6912, 2048, 8), (6912, 2048, 128), (2048, 6912, 130),
+])
+def test_gemm_tc_exact_is_bit_exact(ops, orc, dtype, m, k, n):
+    """The default prefill GEMM: tensor-core lane partials + the reference's eight chains.  Bit-equal to
+    the CUDA-core kernel for every output, and to the oracle for sampled tokens."""
+    rng = np.random.default_rng(m * 7 + k + n)
+    raw = rand_weights(rng, dtype, m, k)
+    x = rng.standard_normal((n, k), dtype=F32)
+    bs, bq = orc.quantize_q8_0(x)
+    dt = orc.QTYPE_ID[dtype]
+    w = ops.QuantWeight(dt, raw, m, k)
+    dbs, dbq = dev(bs), dev(bq)
+    out = host(ops.gemm_q8_tc_exact(w, dbs, dbq))
+    exact = host(ops.gemm_q8(w, dbs, dbq))
+    assert np.array_equal(out.view(np.uint32), exact.view(np.uint32)), \
+        f"{dtype} {m}x{k}x{n}: {int((out.view(np.uint32) != exact.view(np.uint32)).sum())} outputs differ"
+    for j in sorted({0, n // 2, n - 1}):
+        ref = orc.gemv(dt, raw, bs[j], bq[j], m, k)
+        assert np.array_equal(out[j].view(np.uint32), ref.view(np.uint32))
+
+
+def test_gemm_tc_exact_full_size_properties(ops, orc):
+    """n = 4096 (256 token tiles per row tile, CTAs loop over tiles): equals the CUDA-core kernel bit for
+    bit, and sampled tokens equal the oracle."""
+    m, k, n = 1024, 2048, 4096
+    rng = np.random.default_rng(21)
+    raw = rand_weights(rng, "q4_0", m, k)
+    x = rng.standard_normal((n, k), dtype=F32)
+    w = ops.QuantWeight(orc.DT_Q4_0, raw, m, k)
+    bs, bq = ops.quantize_f32_to_q8_0(dev(x))
+    out = ops.gemm_q8_tc_exact(w, bs, bq)
+    assert torch.equal(out, ops.gemm_q8(w, bs, bq))
+    for j in (0, 1777, 4095):
+        ref = orc.gemv(orc.DT_Q4_0, raw, host(bs[j]), host(bq[j]), m, k)
+        assert np.array_equal(host(out[j]).view(np.uint32), ref.view(np.uint32))
+
+
 def test_gemm_tc_extreme_values(ops, orc):
     """Largest possible block sums: all weights at -8 (Q4_0) against activations at +/-127."""
     m, k, n = 128, 256, 32

@@ -72,7 +72,7 @@ def test_mode_switch_and_exact_agreement(wick, orc, model_dir, monkeypatch):
     monkeypatch.delenv("WICK_CUDA_PREFILL", raising=False)
     path = _path(model_dir, "tiny-wide", "q4_0")
     m = wick.CudaLfm2Model(path, 1024)
-    assert m.prefill_mode() == "exact"
+    assert m.prefill_mode() == "exact" and m.prefill_uses_tensor_cores()
     st = wick.InferenceState()
     toks = gs.random_prompt(600, m.config().vocab_size, seed=9)
     lo = orc.OracleModel(path, 1024).forward_prefill(toks, 0)

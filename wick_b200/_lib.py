@@ -50,6 +50,7 @@ SIGNATURES = {
     "wick_cuda_forward_prefill": [_vp, _vp, _u32, _u32, _vp],
     "wick_cuda_set_prefill_mode": [_vp, _i32],
     "wick_cuda_prefill_mode": [_vp, C.POINTER(_i32)],
+    "wick_cuda_prefill_uses_tensor_cores": [_vp, C.POINTER(_i32)],
     "wick_cuda_generate_greedy": [_vp, _u32, _u32, _vp],
     "wick_cuda_reset": [_vp],
     "wick_cuda_seq_len": [_vp, C.POINTER(_u32)],
@@ -68,6 +69,7 @@ SIGNATURES = {
     "wick_cuda_gemv_q8": [_vp, _vp, _vp, _vp, _vp],
     "wick_cuda_gemm_q8": [_vp, _vp, _vp, _u32, _vp, _vp],
     "wick_cuda_gemm_q8_tc": [_vp, _vp, _vp, _u32, _vp, _vp, _vp],
+    "wick_cuda_gemm_q8_tc_exact": [_vp, _vp, _vp, _u32, _vp, _vp],
     "wick_cuda_block_sums": [_vp, _vp, _vp, _vp],
     "wick_cuda_rmsnorm": [_vp, _vp, _u32, _u32, _f, _vp],
     "wick_cuda_silu_mul": [_vp, _vp, _u64, _vp],

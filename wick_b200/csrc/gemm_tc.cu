@@ -179,7 +179,7 @@ __device__ __forceinline__ TcTile tc_decode_tile(const TcJob& job, int t, int ti
     return r;
 }
 
-template <int BN, bool SUMS>
+template <int BN, bool SUMS, bool EXACT>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 k_gemm_tc(const __grid_constant__ TcJob job, const __grid_constant__ CUtensorMap map_x,
           const float* __restrict__ x_scales,  // [n][k/32]
@@ -189,10 +189,15 @@ k_gemm_tc(const __grid_constant__ TcJob job, const __grid_constant__ CUtensorMap
     TcSmem<BN>* sm = reinterpret_cast<TcSmem<BN>*>((reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
     constexpr int NBUF = 512 / BN;
     constexpr int COLS = BN / TC_COL_GROUPS;  // columns per epilogue thread
+    // EXACT: a column is (token, NEON lane group); the activation rows arrive masked to one lane group
+    // each (tc_mask_expand), so a tile covers BN/4 tokens and the MMA yields the four lane partials
+    constexpr int TOK = EXACT ? BN / 4 : BN;  // tokens per tile
+    constexpr int XROWS = EXACT ? 4 : 1;      // rows of the activation operand per token
+    static_assert(!EXACT || (COLS == 16 && !SUMS), "exact epilogue: 4 tokens x 4 lane groups per thread");
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nb = k / QK;
     const int k_stages = k / TC_KSTAGE;
-    const int tiles_n = (n + BN - 1) / BN;
+    const int tiles_n = (n + TOK - 1) / TOK;
     const int tiles = job.tile_start[job.count];
 
     if (threadIdx.x == 0) {
@@ -224,7 +229,7 @@ k_gemm_tc(const __grid_constant__ TcJob job, const __grid_constant__ CUtensorMap
             uint32_t g = 0;
             bool ok = true;
             for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
-                const TcTile tl = tc_decode_tile(job, t, tiles_n, BN);
+                const TcTile tl = tc_decode_tile(job, t, tiles_n, TOK);
                 const CUtensorMap* mw = &job.map_w[tl.mat];
                 for (int ks = 0; ks < k_stages; ks++, g++) {
                     const int s = g % TC_STAGES;
@@ -234,7 +239,7 @@ k_gemm_tc(const __grid_constant__ TcJob job, const __grid_constant__ CUtensorMap
                     const uint32_t bar = smem_u32(&sm->full[s]);
                     mbar_arrive_expect_tx(bar, (TC_BM + BN) * TC_KSTAGE);
                     tma_load_2d(smem_u32(sm->stage[s].a), mw, bar, ks * TC_KSTAGE, tl.m0);
-                    tma_load_2d(smem_u32(sm->stage[s].b), &map_x, bar, ks * TC_KSTAGE, tl.n0);
+                    tma_load_2d(smem_u32(sm->stage[s].b), &map_x, bar, ks * TC_KSTAGE, tl.n0 * XROWS);
                 }
             }
         }
@@ -256,13 +261,18 @@ k_gemm_tc(const __grid_constant__ TcJob job, const __grid_constant__ CUtensorMap
 #pragma unroll
                     for (int kk = 0; kk < TC_KB_PER_STAGE; kk++) {
                         const uint32_t j = g * TC_KB_PER_STAGE + kk;
-                        const uint32_t buf = j % NBUF, ub = j / NBUF;
-                        ok = mbar_wait(sm, smem_u32(&sm->tmem_empty[buf]), (ub & 1) ^ 1, err, 3);
-                        if (!ok) break;
-                        tc_fence_after();
+                        const uint32_t buf = j % NBUF;
+                        if (!EXACT || (kk & 1) == 0) {
+                            // EXACT hands buffers over in (even block, odd block) pairs: barrier index = pair
+                            const uint32_t bi = EXACT ? buf >> 1 : buf, ub = EXACT ? (j >> 1) / (NBUF / 2) : j / NBUF;
+                            ok = mbar_wait(sm, smem_u32(&sm->tmem_empty[bi]), (ub & 1) ^ 1, err, 3);
+                            if (!ok) break;
+                            tc_fence_after();
+                        }
                         // 32 bytes further along K inside the swizzle atom: +2 in the 16-byte address field
                         umma_i8(tmem_base + buf * BN, da + (unsigned long long)(kk * 2), db + (unsigned long long)(kk * 2), idesc);
-                        umma_commit(smem_u32(&sm->tmem_full[buf]));
+                        if (!EXACT) umma_commit(smem_u32(&sm->tmem_full[buf]));
+                        else if (kk & 1) umma_commit(smem_u32(&sm->tmem_full[buf >> 1]));
                     }
                     if (ok) umma_commit(smem_u32(&sm->empty[s]));
                 }
@@ -273,7 +283,7 @@ k_gemm_tc(const __grid_constant__ TcJob job, const __grid_constant__ CUtensorMap
         uint32_t g = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
-            const TcTile tl = tc_decode_tile(job, t, tiles_n, BN);
+            const TcTile tl = tc_decode_tile(job, t, tiles_n, TOK);
             const float* wst = job.scales_t[tl.mat];
             const int m_pad = job.m_pad[tl.mat];
             for (int ks = 0; ks < k_stages; ks++, g++) {
@@ -290,7 +300,7 @@ k_gemm_tc(const __grid_constant__ TcJob job, const __grid_constant__ CUtensorMap
                     reinterpret_cast<float4*>(st.sw[kk])[lane] = v;
                 }
 #pragma unroll
-                for (int c = lane; c < BN; c += 32) {
+                for (int c = lane; c < TOK; c += 32) {
                     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
                     if (tl.n0 + c < n) v = __ldg(reinterpret_cast<const float4*>(x_scales + (size_t)(tl.n0 + c) * nb + b0));
                     st.sx[0][c] = v.x;
@@ -307,65 +317,132 @@ k_gemm_tc(const __grid_constant__ TcJob job, const __grid_constant__ CUtensorMap
         const int quarter = warp & 3, cg = (warp - 4) >> 2;
         const int row_in_tile = quarter * 32 + lane;
         const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(cg * COLS);
-        float acc[COLS];
         uint32_t g = 0;
         bool ok = true;
-        for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
-            const TcTile tl = tc_decode_tile(job, t, tiles_n, BN);
-            const int m = job.m[tl.mat];
-            const int row = tl.m0 + row_in_tile;
+        if constexpr (!EXACT) {
+            float acc[COLS];
+            for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
+                const TcTile tl = tc_decode_tile(job, t, tiles_n, TOK);
+                const int m = job.m[tl.mat];
+                const int row = tl.m0 + row_in_tile;
 #pragma unroll
-            for (int c = 0; c < COLS; c++) acc[c] = 0.f;
-            for (int ks = 0; ks < k_stages && ok; ks++, g++) {
-                const int s = g % TC_STAGES;
-                const uint32_t u = g / TC_STAGES;
-                ok = mbar_wait(sm, smem_u32(&sm->full[s]), u & 1, err, 5);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                const TcStage<BN>& st = sm->stage[s];
-#pragma unroll 1
-                for (int kk = 0; kk < TC_KB_PER_STAGE; kk++) {
-                    const uint32_t j = g * TC_KB_PER_STAGE + kk;
-                    const uint32_t buf = j % NBUF, ub = j / NBUF;
-                    ok = mbar_wait(sm, smem_u32(&sm->tmem_full[buf]), ub & 1, err, 6);
+                for (int c = 0; c < COLS; c++) acc[c] = 0.f;
+                for (int ks = 0; ks < k_stages && ok; ks++, g++) {
+                    const int s = g % TC_STAGES;
+                    const uint32_t u = g / TC_STAGES;
+                    ok = mbar_wait(sm, smem_u32(&sm->full[s]), u & 1, err, 5);
                     ok = __all_sync(0xffffffffu, ok);
                     if (!ok) break;
-                    tc_fence_after();
-                    int32_t S[COLS];
-                    tmem_ld<COLS>(lane_base + buf * BN, S);
-                    tmem_ld_wait();
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(smem_u32(&sm->tmem_empty[buf]));
-                    const float sw = st.sw[kk][row_in_tile];
-                    const float4* sx4 = reinterpret_cast<const float4*>(&st.sx[kk][cg * COLS]);
+                    const TcStage<BN>& st = sm->stage[s];
+#pragma unroll 1
+                    for (int kk = 0; kk < TC_KB_PER_STAGE; kk++) {
+                        const uint32_t j = g * TC_KB_PER_STAGE + kk;
+                        const uint32_t buf = j % NBUF, ub = j / NBUF;
+                        ok = mbar_wait(sm, smem_u32(&sm->tmem_full[buf]), ub & 1, err, 6);
+                        ok = __all_sync(0xffffffffu, ok);
+                        if (!ok) break;
+                        tc_fence_after();
+                        int32_t S[COLS];
+                        tmem_ld<COLS>(lane_base + buf * BN, S);
+                        tmem_ld_wait();
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(smem_u32(&sm->tmem_empty[buf]));
+                        const float sw = st.sw[kk][row_in_tile];
+                        const float4* sx4 = reinterpret_cast<const float4*>(&st.sx[kk][cg * COLS]);
 #pragma unroll
-                    for (int c = 0; c < COLS; c += 4) {
-                        const float4 x = sx4[c >> 2];
-                        acc[c + 0] = __fmaf_rn(__int2float_rn(S[c + 0]), __fmul_rn(sw, x.x), acc[c + 0]);
-                        acc[c + 1] = __fmaf_rn(__int2float_rn(S[c + 1]), __fmul_rn(sw, x.y), acc[c + 1]);
-                        acc[c + 2] = __fmaf_rn(__int2float_rn(S[c + 2]), __fmul_rn(sw, x.z), acc[c + 2]);
-                        acc[c + 3] = __fmaf_rn(__int2float_rn(S[c + 3]), __fmul_rn(sw, x.w), acc[c + 3]);
-                    }
-                    if (SUMS && row < m) {
-                        const int b = ks * TC_KB_PER_STAGE + kk;
+                        for (int c = 0; c < COLS; c += 4) {
+                            const float4 x = sx4[c >> 2];
+                            acc[c + 0] = __fmaf_rn(__int2float_rn(S[c + 0]), __fmul_rn(sw, x.x), acc[c + 0]);
+                            acc[c + 1] = __fmaf_rn(__int2float_rn(S[c + 1]), __fmul_rn(sw, x.y), acc[c + 1]);
+                            acc[c + 2] = __fmaf_rn(__int2float_rn(S[c + 2]), __fmul_rn(sw, x.z), acc[c + 2]);
+                            acc[c + 3] = __fmaf_rn(__int2float_rn(S[c + 3]), __fmul_rn(sw, x.w), acc[c + 3]);
+                        }
+                        if (SUMS && row < m) {
+                            const int b = ks * TC_KB_PER_STAGE + kk;
 #pragma unroll
-                        for (int c = 0; c < COLS; c++) {
-                            const int tok = tl.n0 + cg * COLS + c;
-                            if (tok < n) sums[((size_t)tok * m + row) * nb + b] = S[c];
+                            for (int c = 0; c < COLS; c++) {
+                                const int tok = tl.n0 + cg * COLS + c;
+                                if (tok < n) sums[((size_t)tok * m + row) * nb + b] = S[c];
+                            }
                         }
                     }
+                    if (!ok) break;
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&sm->empty[s]));
                 }
-                if (!ok) break;
-                __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&sm->empty[s]));
-            }
-            if (ok && row < m) {
-                float* out = job.out[tl.mat];
+                if (ok && row < m) {
+                    float* out = job.out[tl.mat];
 #pragma unroll
-                for (int c = 0; c < COLS; c++) {
-                    const int tok = tl.n0 + cg * COLS + c;
-                    if (tok < n) out[(size_t)tok * m + row] = acc[c];
+                    for (int c = 0; c < COLS; c++) {
+                        const int tok = tl.n0 + cg * COLS + c;
+                        if (tok < n) out[(size_t)tok * m + row] = acc[c];
+                    }
+                }
+            }
+        } else {
+            // The arithmetic of gemm_q*_q8_0_neon (simd.rs:696-1019) bit for bit: per output eight unfused
+            // chains acc[parity of the block][lane group] += float(lane partial) * (f16(d_w) * d_x), blocks
+            // in ascending order, combined at the end as ((a0+a1)+(a2+a3)) per parity, even + odd.
+            constexpr int TPT = COLS / 4;  // tokens per thread
+            float acc[TPT][2][4];
+            for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
+                const TcTile tl = tc_decode_tile(job, t, tiles_n, TOK);
+                const int m = job.m[tl.mat];
+                const int row = tl.m0 + row_in_tile;
+#pragma unroll
+                for (int i = 0; i < TPT; i++)
+#pragma unroll
+                    for (int l = 0; l < 4; l++) acc[i][0][l] = acc[i][1][l] = 0.f;
+                for (int ks = 0; ks < k_stages && ok; ks++, g++) {
+                    const int s = g % TC_STAGES;
+                    const uint32_t u = g / TC_STAGES;
+                    ok = mbar_wait(sm, smem_u32(&sm->full[s]), u & 1, err, 5);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                    const TcStage<BN>& st = sm->stage[s];
+#pragma unroll 1
+                    for (int kp = 0; kp < TC_KB_PER_STAGE / 2; kp++) {
+                        const uint32_t jp = g * (TC_KB_PER_STAGE / 2) + kp;
+                        const uint32_t pb = jp % (NBUF / 2), ub = jp / (NBUF / 2);
+                        ok = mbar_wait(sm, smem_u32(&sm->tmem_full[pb]), ub & 1, err, 6);
+                        ok = __all_sync(0xffffffffu, ok);
+                        if (!ok) break;
+                        tc_fence_after();
+                        int32_t S0[COLS], S1[COLS];
+                        tmem_ld<COLS>(lane_base + (2 * pb) * BN, S0);
+                        tmem_ld<COLS>(lane_base + (2 * pb + 1) * BN, S1);
+                        tmem_ld_wait();
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(smem_u32(&sm->tmem_empty[pb]));
+                        const float sw0 = st.sw[2 * kp][row_in_tile], sw1 = st.sw[2 * kp + 1][row_in_tile];
+                        const float4 x0 = *reinterpret_cast<const float4*>(&st.sx[2 * kp][cg * TPT]);
+                        const float4 x1 = *reinterpret_cast<const float4*>(&st.sx[2 * kp + 1][cg * TPT]);
+                        const float xs0[4] = {x0.x, x0.y, x0.z, x0.w}, xs1[4] = {x1.x, x1.y, x1.z, x1.w};
+#pragma unroll
+                        for (int i = 0; i < TPT; i++) {
+                            const float d0 = __fmul_rn(sw0, xs0[i]), d1 = __fmul_rn(sw1, xs1[i]);
+#pragma unroll
+                            for (int l = 0; l < 4; l++) {
+                                acc[i][0][l] = __fadd_rn(acc[i][0][l], __fmul_rn(__int2float_rn(S0[i * 4 + l]), d0));
+                                acc[i][1][l] = __fadd_rn(acc[i][1][l], __fmul_rn(__int2float_rn(S1[i * 4 + l]), d1));
+                            }
+                        }
+                    }
+                    if (!ok) break;
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&sm->empty[s]));
+                }
+                if (ok && row < m) {
+                    float* out = job.out[tl.mat];
+#pragma unroll
+                    for (int i = 0; i < TPT; i++) {
+                        const int tok = tl.n0 + cg * TPT + i;
+                        const float e = __fadd_rn(__fadd_rn(acc[i][0][0], acc[i][0][1]), __fadd_rn(acc[i][0][2], acc[i][0][3]));
+                        const float o = __fadd_rn(__fadd_rn(acc[i][1][0], acc[i][1][1]), __fadd_rn(acc[i][1][2], acc[i][1][3]));
+                        if (tok < n) out[(size_t)tok * m + row] = __fadd_rn(e, o);
+                    }
                 }
             }
         }
@@ -451,7 +528,7 @@ cudaError_t encode_rows_map(const void* base, int rows, int k, int box_rows, CUt
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
-template <int BN>
+template <int BN, bool EXACT>
 cudaError_t launch_tc(cudaStream_t st, const TcJob& job, const CUtensorMap& map_x, const float* x_scales, int n, int k,
                       int32_t* sums, uint32_t* err) {
     static int sm_count = 0;
@@ -463,20 +540,59 @@ cudaError_t launch_tc(cudaStream_t st, const TcJob& job, const CUtensorMap& map_
         if (e != cudaSuccess) return e;
         e = cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
         if (e != cudaSuccess) return e;
-        e = cudaFuncSetAttribute(k_gemm_tc<BN, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        e = cudaFuncSetAttribute(k_gemm_tc<BN, false, EXACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
-        e = cudaFuncSetAttribute(k_gemm_tc<BN, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return e;
+        if constexpr (!EXACT) {
+            e = cudaFuncSetAttribute(k_gemm_tc<BN, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return e;
+        }
         configured = true;
     }
     const int tiles = job.tile_start[job.count];
     const int grid = tiles < sm_count ? tiles : sm_count;
     g_kernel_launches++;
-    if (sums)
-        k_gemm_tc<BN, true><<<grid, TC_THREADS, smem, st>>>(job, map_x, x_scales, sums, n, k, err);
-    else
-        k_gemm_tc<BN, false><<<grid, TC_THREADS, smem, st>>>(job, map_x, x_scales, sums, n, k, err);
+    if constexpr (!EXACT) {
+        if (sums) {
+            k_gemm_tc<BN, true, false><<<grid, TC_THREADS, smem, st>>>(job, map_x, x_scales, sums, n, k, err);
+            return cudaGetLastError();
+        }
+    }
+    k_gemm_tc<BN, false, EXACT><<<grid, TC_THREADS, smem, st>>>(job, map_x, x_scales, nullptr, n, k, err);
     return cudaGetLastError();
+}
+
+// One thread per 16 input bytes (half a quantisation block): NEON lane group l owns bytes 4l..4l+3
+// of each half (simd.rs:381-383: vdotq_s32 lane l), so output row 4*j + l keeps word l and zeroes the rest.
+__global__ void k_tc_mask_expand(const uint4* __restrict__ xq, uint4* __restrict__ xm, size_t n_chunks, int chunks_per_row) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_chunks) return;
+    const uint4 v = xq[i];
+    const size_t row = i / chunks_per_row, c = i % chunks_per_row;
+    uint4* o = xm + (row * 4) * chunks_per_row + c;
+    o[0] = make_uint4(v.x, 0u, 0u, 0u);
+    o[(size_t)chunks_per_row] = make_uint4(0u, v.y, 0u, 0u);
+    o[(size_t)2 * chunks_per_row] = make_uint4(0u, 0u, v.z, 0u);
+    o[(size_t)3 * chunks_per_row] = make_uint4(0u, 0u, 0u, v.w);
+}
+
+cudaError_t fill_job(TcJob& job, const TcWeight* const* w, float* const* out, int count, int tiles_n) {
+    memset(&job, 0, sizeof(job));
+    job.count = count;
+    int t = 0;
+    for (int i = 0; i < 3; i++) {
+        job.tile_start[i] = t;
+        if (i >= count) continue;
+        if (w[i]->k != w[0]->k) return cudaErrorInvalidValue;
+        job.map_w[i] = w[i]->map;
+        job.scales_t[i] = w[i]->scales_t;
+        job.out[i] = out[i];
+        job.m[i] = w[i]->m;
+        job.m_pad[i] = w[i]->m_pad;
+        t += (w[i]->m_pad / TC_BM) * tiles_n;
+    }
+    job.tile_start[3] = t;
+    for (int i = count; i < 3; i++) job.tile_start[i] = t;  // unused matrices own no tiles
+    return cudaSuccess;
 }
 
 }  // namespace
@@ -517,26 +633,29 @@ cudaError_t launch_gemm_tc(cudaStream_t st, const TcWeight* const* w, float* con
     int rows = 0;
     for (int i = 0; i < count; i++) rows += w[i]->m_pad / TC_BM;
     const int bn = tc_gemm_bn(n, rows);
-    const int tiles_n = (n + bn - 1) / bn;
     TcJob job;
-    memset(&job, 0, sizeof(job));
-    job.count = count;
-    int t = 0;
-    for (int i = 0; i < 3; i++) {
-        job.tile_start[i] = t;
-        if (i >= count) continue;
-        if (w[i]->k != w[0]->k) return cudaErrorInvalidValue;
-        job.map_w[i] = w[i]->map;
-        job.scales_t[i] = w[i]->scales_t;
-        job.out[i] = out[i];
-        job.m[i] = w[i]->m;
-        job.m_pad[i] = w[i]->m_pad;
-        t += (w[i]->m_pad / TC_BM) * tiles_n;
-    }
-    job.tile_start[3] = t;
-    for (int i = count; i < 3; i++) job.tile_start[i] = t;  // unused matrices own no tiles
-    return bn == 64 ? launch_tc<64>(st, job, map_x[0], x_scales, n, w[0]->k, sums, err)
-                    : launch_tc<128>(st, job, map_x[1], x_scales, n, w[0]->k, sums, err);
+    cudaError_t e = fill_job(job, w, out, count, (n + bn - 1) / bn);
+    if (e != cudaSuccess) return e;
+    return bn == 64 ? launch_tc<64, false>(st, job, map_x[0], x_scales, n, w[0]->k, sums, err)
+                    : launch_tc<128, false>(st, job, map_x[1], x_scales, n, w[0]->k, sums, err);
+}
+
+void launch_tc_mask_expand(cudaStream_t st, const int8_t* xq, int n, int k, int8_t* xm) {
+    const size_t chunks = (size_t)n * (k / 16);
+    if (!chunks) return;
+    g_kernel_launches++;
+    k_tc_mask_expand<<<(unsigned)((chunks + 255) / 256), 256, 0, st>>>(reinterpret_cast<const uint4*>(xq), reinterpret_cast<uint4*>(xm),
+                                                                         chunks, k / 16);
+}
+
+cudaError_t launch_gemm_tc_exact(cudaStream_t st, const TcWeight* const* w, float* const* out, int count, const CUtensorMap& map_xm,
+                                 const float* x_scales, int n, uint32_t* err) {
+    if (n <= 0 || count <= 0) return cudaSuccess;
+    if (count > 3) return cudaErrorInvalidValue;
+    TcJob job;
+    cudaError_t e = fill_job(job, w, out, count, (n + TC_EXACT_TOKENS - 1) / TC_EXACT_TOKENS);
+    if (e != cudaSuccess) return e;
+    return launch_tc<4 * TC_EXACT_TOKENS, true>(st, job, map_xm, x_scales, n, w[0]->k, nullptr, err);
 }
 
 }  // namespace wick

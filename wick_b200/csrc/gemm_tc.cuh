@@ -49,4 +49,14 @@ cudaError_t tc_make_activation_map(const int8_t* xq, int rows_cap, int k, int bn
 cudaError_t launch_gemm_tc(cudaStream_t st, const TcWeight* const* w, float* const* out, int count, const CUtensorMap* map_x,
                            const float* x_scales, int n, int32_t* sums, uint32_t* err);
 
+// The bit-exact variant (the arithmetic of gemm_q*_q8_0_neon, simd.rs:696-1019, in its order): the
+// activation operand is the masked expansion xm [4 * n][k] of xq (row 4*j + l = token j with every
+// byte outside NEON lane group l zeroed), so that one MMA yields the four lane partials of a block
+// as four columns; the epilogue keeps the reference's eight unfused chains per output.
+constexpr int TC_EXACT_TOKENS = 16;  // tokens per tile (64 MMA columns)
+void launch_tc_mask_expand(cudaStream_t st, const int8_t* xq, int n, int k, int8_t* xm);
+// map_xm: tc_make_activation_map(xm, 4 * rows_cap, k, 64, ..).
+cudaError_t launch_gemm_tc_exact(cudaStream_t st, const TcWeight* const* w, float* const* out, int count, const CUtensorMap& map_xm,
+                                 const float* x_scales, int n, uint32_t* err);
+
 }  // namespace wick

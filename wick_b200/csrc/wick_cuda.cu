@@ -73,10 +73,13 @@ struct wick_cuda_model {
     float* output_norm = nullptr;
     float *rope_cos = nullptr, *rope_sin = nullptr;
     int max_chunk = 0;  // tokens of scratch
-    // tensor-core prefill path: available when every matrix meets tc_gemm_supported(); `prefill_tc`
-    // selects it instead of the bit-exact CUDA-core GEMM (the default)
-    bool tc_ok = false, prefill_tc = false;
+    // tensor-core prefill GEMMs: available when every matrix meets tc_gemm_supported(); prefill_mode
+    // picks the bit-exact one (default), the fused-chain one, or the bit-exact CUDA-core kernel
+    bool tc_ok = false;
+    int prefill_mode = WICK_CUDA_PREFILL_EXACT;
     CUtensorMap map_x_hs[2], map_x_is[2];  // activations [max_chunk][hs | is], box of 64 / 128 rows
+    int8_t* q8m = nullptr;                  // lane-group-masked activations [4 * max_chunk][hs | is] (exact tensor-core GEMM)
+    CUtensorMap map_xm_hs, map_xm_is;
     uint32_t* tc_err = nullptr;
     // scratch, token-major
     float *hidden = nullptr, *block_out = nullptr, *ffn_out = nullptr, *proj = nullptr, *qbuf = nullptr, *kbuf = nullptr,
@@ -440,7 +443,8 @@ void enqueue_prefill_chunk(wick_cuda_model* m, int n, int start_pos, bool flash,
     const float eps = m->cfg.rms_norm_eps;
     // tensor-core path for chunks wide enough to fill an MMA tile; the exact kernel otherwise.
     // Up to three matrices that read the same quantised input go out as one launch.
-    const bool tc = m->prefill_tc && m->tc_ok && n >= 16;
+    const bool tc = m->tc_ok && n >= 16 && m->prefill_mode != WICK_CUDA_PREFILL_EXACT_CUDA_CORES;
+    const bool tc_exact = tc && m->prefill_mode == WICK_CUDA_PREFILL_EXACT;
     struct G {
         const DevWeight* w;
         const TcWeight* t;
@@ -455,8 +459,14 @@ void enqueue_prefill_chunk(wick_cuda_model* m, int n, int start_pos, bool flash,
                 tw[c] = g.t;
                 outs[c++] = g.out;
             }
-            const CUtensorMap* mx = tw[0]->k == hs ? m->map_x_hs : m->map_x_is;
-            cudaError_t e = launch_gemm_tc(st, tw, outs, c, mx, m->q8s, n, nullptr, m->tc_err);
+            const bool is_hs = tw[0]->k == hs;
+            cudaError_t e;
+            if (tc_exact) {
+                launch_tc_mask_expand(st, m->q8q, n, tw[0]->k, m->q8m);
+                e = launch_gemm_tc_exact(st, tw, outs, c, is_hs ? m->map_xm_hs : m->map_xm_is, m->q8s, n, m->tc_err);
+            } else {
+                e = launch_gemm_tc(st, tw, outs, c, is_hs ? m->map_x_hs : m->map_x_is, m->q8s, n, nullptr, m->tc_err);
+            }
             (void)e;  // surfaced by the cudaGetLastError() check after the chunk
         } else {
             for (const G& g : list) launch_gemm(st, *g.w, m->q8s, m->q8q, n, g.out);
@@ -504,9 +514,14 @@ int32_t build_tc(wick_cuda_model* m) {
     const int hs = m->cfg.hidden_size, is = m->cfg.intermediate_size;
     m->tc_ok = false;
     const char* mode = getenv("WICK_CUDA_PREFILL");
-    const bool want = mode && strcmp(mode, "tensor") == 0;  // the bit-exact GEMM is the default
+    m->prefill_mode = WICK_CUDA_PREFILL_EXACT;
+    if (mode && strcmp(mode, "tensor") == 0) m->prefill_mode = WICK_CUDA_PREFILL_TENSOR;
+    if (mode && strcmp(mode, "exact-cuda-cores") == 0) m->prefill_mode = WICK_CUDA_PREFILL_EXACT_CUDA_CORES;
     bool ok = tc_gemm_supported(hs, hs) && tc_gemm_supported(hs, is);
-    if (!ok) return WICK_CUDA_OK;
+    if (!ok) {
+        if (m->prefill_mode == WICK_CUDA_PREFILL_TENSOR) m->prefill_mode = WICK_CUDA_PREFILL_EXACT;
+        return WICK_CUDA_OK;
+    }
     W_TRY(dev_alloc(m, &m->tc_err, 1));
     CU_TRY(cudaMemset(m->tc_err, 0, 4));
     auto fill = [&](const DevWeight& w, TcWeight* t) -> int32_t {
@@ -536,9 +551,11 @@ int32_t build_tc(wick_cuda_model* m) {
         CU_TRY(tc_make_activation_map(m->q8q, m->max_chunk, hs, i ? 128 : 64, &m->map_x_hs[i]));
         CU_TRY(tc_make_activation_map(m->q8q, m->max_chunk, is, i ? 128 : 64, &m->map_x_is[i]));
     }
+    W_TRY(dev_alloc(m, &m->q8m, (size_t)4 * m->max_chunk * std::max(hs, is)));
+    CU_TRY(tc_make_activation_map(m->q8m, 4 * m->max_chunk, hs, 64, &m->map_xm_hs));
+    CU_TRY(tc_make_activation_map(m->q8m, 4 * m->max_chunk, is, 64, &m->map_xm_is));
     CU_TRY(cudaStreamSynchronize(m->stream));
     m->tc_ok = true;
-    m->prefill_tc = want;
     return WICK_CUDA_OK;
 }
 
@@ -911,18 +928,25 @@ int32_t wick_cuda_forward_prefill(wick_cuda_model* m, const uint32_t* tokens_hos
 
 int32_t wick_cuda_set_prefill_mode(wick_cuda_model* m, int32_t mode) {
     W_TRY(check_model(m));
-    if (mode != WICK_CUDA_PREFILL_EXACT && mode != WICK_CUDA_PREFILL_TENSOR)
+    if (mode != WICK_CUDA_PREFILL_EXACT && mode != WICK_CUDA_PREFILL_TENSOR && mode != WICK_CUDA_PREFILL_EXACT_CUDA_CORES)
         return fail(WICK_CUDA_ERR_BAD_ARG, "unknown prefill mode " + std::to_string(mode));
     if (mode == WICK_CUDA_PREFILL_TENSOR && !m->tc_ok)
         return fail(WICK_CUDA_ERR_BAD_ARG, "tensor-core prefill needs hidden and feed-forward sizes that are multiples of 128");
-    m->prefill_tc = mode == WICK_CUDA_PREFILL_TENSOR;
+    m->prefill_mode = mode;
     return WICK_CUDA_OK;
 }
 
 int32_t wick_cuda_prefill_mode(const wick_cuda_model* m, int32_t* mode) {
     W_TRY(check_model(m));
     if (!mode) return fail(WICK_CUDA_ERR_BAD_ARG, "mode is NULL");
-    *mode = m->prefill_tc ? WICK_CUDA_PREFILL_TENSOR : WICK_CUDA_PREFILL_EXACT;
+    *mode = m->prefill_mode;
+    return WICK_CUDA_OK;
+}
+
+int32_t wick_cuda_prefill_uses_tensor_cores(const wick_cuda_model* m, int32_t* yes) {
+    W_TRY(check_model(m));
+    if (!yes) return fail(WICK_CUDA_ERR_BAD_ARG, "yes is NULL");
+    *yes = m->tc_ok && m->prefill_mode != WICK_CUDA_PREFILL_EXACT_CUDA_CORES;
     return WICK_CUDA_OK;
 }
 
@@ -1158,30 +1182,64 @@ int32_t wick_cuda_gemm_q8(const wick_cuda_weight* w, const float* bs_dev, const 
     OP_END();
 }
 
+// The int8 copy of an operator-API weight, made on first use.
+static int32_t ensure_tc_weight(wick_cuda_weight* w, cudaStream_t st) {
+    if (w->tc.q) return WICK_CUDA_OK;
+    TcWeight t;
+    t.m = w->w.m;
+    t.k = w->w.k;
+    t.m_pad = (w->w.m + 127) / 128 * 128;
+    CU_TRY(cudaMalloc((void**)&t.q, t.q_bytes()));
+    CU_TRY(cudaMalloc((void**)&t.scales_t, t.s_bytes()));
+    CU_TRY(cudaMalloc((void**)&w->tc_err, 4));
+    CU_TRY(cudaMemsetAsync(w->tc_err, 0, 4, st));
+    w->tc = t;
+    CU_TRY(tc_weight_fill(st, w->w, &w->tc));
+    return WICK_CUDA_OK;
+}
+
 int32_t wick_cuda_gemm_q8_tc(wick_cuda_weight* w, const float* bs_dev, const int8_t* bq_dev, uint32_t n, float* out_dev,
                              int32_t* block_sums_dev, void* stream) {
     if (!w || !bs_dev || !bq_dev || !out_dev) return fail(WICK_CUDA_ERR_BAD_ARG, "NULL argument");
     if (!tc_gemm_supported(w->w.m, w->w.k)) return fail(WICK_CUDA_ERR_BAD_ARG, "tensor-core GEMM needs k to be a multiple of 128");
     if (n == 0) return WICK_CUDA_OK;
     cudaStream_t st = (cudaStream_t)stream;
-    if (!w->tc.q) {
-        TcWeight t;
-        t.m = w->w.m;
-        t.k = w->w.k;
-        t.m_pad = (w->w.m + 127) / 128 * 128;
-        CU_TRY(cudaMalloc((void**)&t.q, t.q_bytes()));
-        CU_TRY(cudaMalloc((void**)&t.scales_t, t.s_bytes()));
-        CU_TRY(cudaMalloc((void**)&w->tc_err, 4));
-        CU_TRY(cudaMemsetAsync(w->tc_err, 0, 4, st));
-        w->tc = t;
-        CU_TRY(tc_weight_fill(st, w->w, &w->tc));
-    }
+    W_TRY(ensure_tc_weight(w, st));
     CUtensorMap map_x[2];
     CU_TRY(tc_make_activation_map(bq_dev, (int)n, w->w.k, 64, &map_x[0]));
     CU_TRY(tc_make_activation_map(bq_dev, (int)n, w->w.k, 128, &map_x[1]));
     const TcWeight* tw[1] = {&w->tc};
     float* outs[1] = {out_dev};
     CU_TRY(launch_gemm_tc(st, tw, outs, 1, map_x, bs_dev, (int)n, block_sums_dev, w->tc_err));
+    uint32_t code = 0;
+    CU_TRY(cudaMemcpyAsync(&code, w->tc_err, 4, cudaMemcpyDeviceToHost, st));
+    CU_TRY(cudaStreamSynchronize(st));
+    if (code != 0) {
+        cudaMemsetAsync(w->tc_err, 0, 4, st);
+        return fail(WICK_CUDA_ERR_TIMEOUT, "tensor-core GEMM: a bounded wait expired (role code " + std::to_string(code) + ")");
+    }
+    return WICK_CUDA_OK;
+}
+
+int32_t wick_cuda_gemm_q8_tc_exact(wick_cuda_weight* w, const float* bs_dev, const int8_t* bq_dev, uint32_t n, float* out_dev,
+                                   void* stream) {
+    if (!w || !bs_dev || !bq_dev || !out_dev) return fail(WICK_CUDA_ERR_BAD_ARG, "NULL argument");
+    if (!tc_gemm_supported(w->w.m, w->w.k)) return fail(WICK_CUDA_ERR_BAD_ARG, "tensor-core GEMM needs k to be a multiple of 128");
+    if (n == 0) return WICK_CUDA_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    W_TRY(ensure_tc_weight(w, st));
+    int8_t* xm = nullptr;
+    CU_TRY(cudaMalloc((void**)&xm, (size_t)4 * n * w->w.k));
+    struct Guard {
+        int8_t* p;
+        ~Guard() { cudaFree(p); }
+    } guard{xm};
+    launch_tc_mask_expand(st, bq_dev, (int)n, w->w.k, xm);
+    CUtensorMap map_xm;
+    CU_TRY(tc_make_activation_map(xm, 4 * (int)n, w->w.k, 64, &map_xm));
+    const TcWeight* tw[1] = {&w->tc};
+    float* outs[1] = {out_dev};
+    CU_TRY(launch_gemm_tc_exact(st, tw, outs, 1, map_xm, bs_dev, (int)n, w->tc_err));
     uint32_t code = 0;
     CU_TRY(cudaMemcpyAsync(&code, w->tc_err, 4, cudaMemcpyDeviceToHost, st));
     CU_TRY(cudaStreamSynchronize(st));

@@ -219,16 +219,25 @@ class CudaLfm2Model:
         check(self._lib.wick_cuda_decode_path(self._h, C.byref(v)))
         return "persistent" if v.value else "graph"
 
+    _PREFILL_MODES = {"exact": 0, "tensor": 1, "exact-cuda-cores": 2}
+
     def prefill_mode(self) -> str:
-        """'tensor' (tcgen05 int8 GEMM, logits equal to f32 rounding) or 'exact' (bit-exact CUDA-core GEMM)."""
+        """'exact' (default: bit-exact GEMM, on the tensor cores when the model's sizes allow),
+        'tensor' (fused-chain tcgen05 GEMM, logits equal to f32 rounding per product) or
+        'exact-cuda-cores' (the bit-exact CUDA-core GEMM)."""
         v = C.c_int32(0)
         check(self._lib.wick_cuda_prefill_mode(self._h, C.byref(v)))
-        return "tensor" if v.value else "exact"
+        return {n: k for k, n in self._PREFILL_MODES.items()}[v.value]
 
     def set_prefill_mode(self, mode: str) -> None:
-        if mode not in ("exact", "tensor"):
-            raise ValueError("prefill mode must be 'exact' or 'tensor'")
-        check(self._lib.wick_cuda_set_prefill_mode(self._h, 1 if mode == "tensor" else 0))
+        if mode not in self._PREFILL_MODES:
+            raise ValueError("prefill mode must be one of " + ", ".join(self._PREFILL_MODES))
+        check(self._lib.wick_cuda_set_prefill_mode(self._h, self._PREFILL_MODES[mode]))
+
+    def prefill_uses_tensor_cores(self) -> bool:
+        v = C.c_int32(0)
+        check(self._lib.wick_cuda_prefill_uses_tensor_cores(self._h, C.byref(v)))
+        return bool(v.value)
 
     def decode_profile(self):
         """Timeline of the last decode step of the persistent kernel: (kinds [n], ns [n, 4])."""

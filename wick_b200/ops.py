@@ -90,6 +90,14 @@ def gemm_q8_tc(w: QuantWeight, bs: torch.Tensor, bq: torch.Tensor, want_sums: bo
     return (out, sums) if want_sums else out
 
 
+def gemm_q8_tc_exact(w: QuantWeight, bs: torch.Tensor, bq: torch.Tensor) -> torch.Tensor:
+    """gemm_q8 on the tensor cores with the reference's accumulation order: bit-identical to gemm_q8."""
+    n = bq.shape[0]
+    out = torch.empty((n, w.m), dtype=torch.float32, device=bq.device)
+    check(_lib.load().wick_cuda_gemm_q8_tc_exact(w._h, _ptr(bs), _ptr(bq), n, _ptr(out), _stream()))
+    return out
+
+
 def block_sums(w: QuantWeight, xq: torch.Tensor) -> torch.Tensor:
     s = torch.empty((w.m, w.k // 32), dtype=torch.int32, device=xq.device)
     check(_lib.load().wick_cuda_block_sums(w._h, _ptr(xq), _ptr(s), _stream()))
