@@ -158,6 +158,26 @@ __device__ __forceinline__ void tmem_ld(uint32_t taddr, int32_t* r) {
     if constexpr (COLS == 16) tmem_ld16(taddr, r);
     else tmem_ld32(taddr, r);
 }
+// Two f32 lanes per instruction (sm_100 packed f32x2 arithmetic), used by the fused-chain epilogue,
+// which is bound by instruction issue: each half of a packed multiply or fused multiply-add is rounded
+// like the scalar instruction.
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pack2(float a, float b) {
+    f32x2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ void unpack2(f32x2 v, float& a, float& b) { asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v)); }
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
+    f32x2 r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+    f32x2 r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 }  // namespace
@@ -320,13 +340,13 @@ k_gemm_tc(const __grid_constant__ TcJob job, const __grid_constant__ CUtensorMap
         uint32_t g = 0;
         bool ok = true;
         if constexpr (!EXACT) {
-            float acc[COLS];
+            f32x2 acc[COLS / 2];
             for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
                 const TcTile tl = tc_decode_tile(job, t, tiles_n, TOK);
                 const int m = job.m[tl.mat];
                 const int row = tl.m0 + row_in_tile;
 #pragma unroll
-                for (int c = 0; c < COLS; c++) acc[c] = 0.f;
+                for (int c = 0; c < COLS / 2; c++) acc[c] = pack2(0.f, 0.f);
                 for (int ks = 0; ks < k_stages && ok; ks++, g++) {
                     const int s = g % TC_STAGES;
                     const uint32_t u = g / TC_STAGES;
@@ -349,14 +369,13 @@ k_gemm_tc(const __grid_constant__ TcJob job, const __grid_constant__ CUtensorMap
                         __syncwarp();
                         if (lane == 0) mbar_arrive(smem_u32(&sm->tmem_empty[buf]));
                         const float sw = st.sw[kk][row_in_tile];
+                        const f32x2 sw2 = pack2(sw, sw);
                         const float4* sx4 = reinterpret_cast<const float4*>(&st.sx[kk][cg * COLS]);
 #pragma unroll
                         for (int c = 0; c < COLS; c += 4) {
                             const float4 x = sx4[c >> 2];
-                            acc[c + 0] = __fmaf_rn(__int2float_rn(S[c + 0]), __fmul_rn(sw, x.x), acc[c + 0]);
-                            acc[c + 1] = __fmaf_rn(__int2float_rn(S[c + 1]), __fmul_rn(sw, x.y), acc[c + 1]);
-                            acc[c + 2] = __fmaf_rn(__int2float_rn(S[c + 2]), __fmul_rn(sw, x.z), acc[c + 2]);
-                            acc[c + 3] = __fmaf_rn(__int2float_rn(S[c + 3]), __fmul_rn(sw, x.w), acc[c + 3]);
+                            acc[c / 2 + 0] = fma2(pack2(__int2float_rn(S[c + 0]), __int2float_rn(S[c + 1])), mul2(sw2, pack2(x.x, x.y)), acc[c / 2 + 0]);
+                            acc[c / 2 + 1] = fma2(pack2(__int2float_rn(S[c + 2]), __int2float_rn(S[c + 3])), mul2(sw2, pack2(x.z, x.w)), acc[c / 2 + 1]);
                         }
                         if (SUMS && row < m) {
                             const int b = ks * TC_KB_PER_STAGE + kk;
@@ -374,9 +393,12 @@ k_gemm_tc(const __grid_constant__ TcJob job, const __grid_constant__ CUtensorMap
                 if (ok && row < m) {
                     float* out = job.out[tl.mat];
 #pragma unroll
-                    for (int c = 0; c < COLS; c++) {
+                    for (int c = 0; c < COLS; c += 2) {
                         const int tok = tl.n0 + cg * COLS + c;
-                        if (tok < n) out[(size_t)tok * m + row] = acc[c];
+                        float a0, a1;
+                        unpack2(acc[c / 2], a0, a1);
+                        if (tok < n) out[(size_t)tok * m + row] = a0;
+                        if (tok + 1 < n) out[(size_t)(tok + 1) * m + row] = a1;
                     }
                 }
             }
@@ -385,6 +407,8 @@ k_gemm_tc(const __grid_constant__ TcJob job, const __grid_constant__ CUtensorMap
             // chains acc[parity of the block][lane group] += float(lane partial) * (f16(d_w) * d_x), blocks
             // in ascending order, combined at the end as ((a0+a1)+(a2+a3)) per parity, even + odd.
             constexpr int TPT = COLS / 4;  // tokens per thread
+            // (scalar on purpose: ptxas contracts a packed mul.rn.f32x2 feeding an add.rn.f32x2 into one fused
+            // multiply-add even with contraction switched off, which changes the rounding)
             float acc[TPT][2][4];
             for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
                 const TcTile tl = tc_decode_tile(job, t, tiles_n, TOK);
