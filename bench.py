@@ -174,6 +174,47 @@ def run_reference(args, rank: int, world: int):
     print(json.dumps(line))
 
 
+def gemm_flop_per_token(spec) -> float:
+    """2 * (parameters of the per-layer matrices): the multiply-adds one prompt token costs in the GEMMs."""
+    return 2.0 * sum(
+        (3 * spec.hidden * spec.ffn) + ((spec.hidden * spec.hidden * 2 + 2 * spec.hidden * spec.kv_dim) if i in spec.attn_layers
+                                        else 4 * spec.hidden * spec.hidden)
+        for i in range(spec.n_layers))
+
+
+def int8_peak_tflops():
+    """int8 dense tensor peak used as the prefill roofline: 2 x the measured sustained bf16 figure (the
+    file holds no int8 measurement; int8 is twice bf16 on this part)."""
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return 2.0 * float(json.load(f)["bf16_tflops_sustained"]), "2 x bf16_tflops_sustained (measured)"
+    except Exception:
+        return 2.0 * 1400.0, "2 x 1400 (fallback)"
+
+
+def run_prefill_only(args, m, st, spec, gs):
+    """Profiling aid (single GPU): each step is one prompt of --prompt-tokens through
+    forward_prefill_chunked in --prefill-mode; prints a JSON line of its own, not the headline metric."""
+    m.set_prefill_mode(args.prefill_mode)
+    n = args.prompt_tokens
+    toks = gs.random_prompt(n, spec.vocab, seed=7)
+    for _ in range(args.warmup):
+        m.forward_prefill_chunked(toks, 0, st, args.ubatch)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        m.forward_prefill_chunked(toks, 0, st, args.ubatch)
+    dt = (time.perf_counter() - t0) / args.steps
+    peak, src = int8_peak_tflops()
+    tf = n / dt * gemm_flop_per_token(spec) / 1e12
+    print(json.dumps({
+        "metric": f"prefill tok/s @{n}", "value": n / dt, "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": dt * 1e3, "higher_is_better": True, "dtype": "int8", "data": "synthetic",
+        "config": {"workload": f"{spec.name} {args.qtype.upper()} prefill of {n} tokens, ubatch {args.ubatch}, mode {args.prefill_mode}"},
+        "roofline": {"bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s", "frac": tf / peak, "traffic": None,
+                     "peak_source": src, "note": "GEMM flops of the whole prefill over its wall time (attention and the small kernels included in the time)"},
+    }))
+
+
 def workload_config(args, spec):
     return {
         "workload": f"{spec.name} {args.qtype.upper()} bs=1: {PROMPT_TOKENS}-token uniform-random prompt prefill (untimed), "
@@ -197,9 +238,13 @@ def main():
     ap.add_argument("--decode-tokens", type=int, default=DECODE_TOKENS, help="profiling aid; the metric is quoted at 128")
     ap.add_argument("--no-extra", action="store_true", help="skip the prefill / tg512 side measurements")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--only", default="decode", choices=["decode", "prefill"],
+                    help="profiling aid: 'prefill' times forward_prefill_chunked of --prompt-tokens instead of the headline decode")
+    ap.add_argument("--prefill-mode", default="exact", choices=["exact", "tensor", "exact-cuda-cores"])
+    ap.add_argument("--ubatch", type=int, default=512, help="prefill chunk of --only prefill (0 = one call); wick's default is 512")
     args = ap.parse_args()
     PROMPT_TOKENS, DECODE_TOKENS = args.prompt_tokens, args.decode_tokens
-    args.warmup = max(args.warmup, 3) if args.impl == "cuda" else args.warmup
+    args.warmup = max(args.warmup, 3) if args.impl == "cuda" and args.only == "decode" else args.warmup
 
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -235,12 +280,20 @@ def main():
     seq_index = sharding.shard_sequences(world, world, rank)[0]
     prompt = gs.random_prompt(PROMPT_TOKENS, spec.vocab, seed=sharding.prompt_seed(1, seq_index))
 
+    if args.only == "prefill":
+        run_prefill_only(args, m, st, spec, gs)
+        return
+
+    counters = {"decode_launches": 0}
+
     def one_step(e2e: bool):
         """Returns (decode seconds, tokens)."""
         logits = m.forward_prefill(prompt, 0, st)
         first = int(np.argmax(logits))
         if not e2e:
+            before = m.kernel_launches()
             m.generate_greedy(first, DECODE_TOKENS, st)
+            counters["decode_launches"] += m.kernel_launches() - before
             return m.last_elapsed_ms() * 1e-3
         tok = first
         t0 = time.perf_counter()
@@ -252,6 +305,7 @@ def main():
         one_step(False)
     one_step(True)
 
+    counters["decode_launches"] = 0
     sampler = ClockSampler(local_rank)
     sampler.start()
     time.sleep(0.3)
@@ -302,11 +356,13 @@ def main():
         "warmup": args.warmup, "ms_per_step": dev_s / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "int8", "data": "synthetic", "config": workload_config(args, spec),
         "e2e": {"value": e2e, "unit": "tok/s", "h2d_bytes_per_step": 4 * DECODE_TOKENS, "d2h_bytes_per_step": 4 * DECODE_TOKENS},
-        "gpu_launches": int(args.steps * DECODE_TOKENS * (per_token_kernels or 0)),
+        # launches of this library's kernels inside the device-timed region on rank 0: the persistent decode
+        # kernel runs a whole generate call (all --decode-tokens steps) per launch
+        "gpu_launches": int(counters["decode_launches"]),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": NCU_TRAFFIC_BYTES_PER_TOKEN.get((args.model, args.qtype)), "peak_source": peak_kind,
-                     "kernel": "one decode step", "algorithmic_bytes_per_launch": bpt,
-                     "kernels_per_step": per_token_kernels},
+                     "kernel": "k_decode_mega (persistent: one launch = DECODE_TOKENS decode steps); figures are per decode step",
+                     "algorithmic_bytes_per_step": bpt, "launches_per_generate_call": per_token_kernels},
         "clocks": clocks,
     }
     if world == 1 and not args.no_cpu_baseline:
@@ -317,17 +373,9 @@ def main():
     if world == 1 and not args.no_extra:
         # side measurements (not the headline): prefill in both GEMM modes, and decode at tg512
         extra = {}
-        gemm_flop_per_token = 2.0 * sum(
-            (3 * spec.hidden * spec.ffn) + ((spec.hidden * spec.hidden * 2 + 2 * spec.hidden * spec.kv_dim) if i in spec.attn_layers
-                                            else 4 * spec.hidden * spec.hidden)
-            for i in range(spec.n_layers))
-        tensor_peak = None
-        try:
-            with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
-                tensor_peak = 2.0 * float(json.load(f)["bf16_tflops_sustained"])   # int8 dense = 2 x bf16 on this part
-        except Exception:
-            pass
-        for mode in ("exact", "tensor"):
+        flop_tok = gemm_flop_per_token(spec)
+        tensor_peak, peak_src = int8_peak_tflops()
+        for mode in ("exact", "tensor", "exact-cuda-cores"):
             try:
                 m.set_prefill_mode(mode)
             except Exception as e:                      # tensor mode needs sizes that are multiples of 128
@@ -341,17 +389,18 @@ def main():
                 tps = n / (time.perf_counter() - t0)
                 key = f"prefill_{mode}_p{n}" + ("_one_call" if ub == 0 else "") + "_tok_s"
                 extra[key] = tps
-                if mode == "tensor" and n == 4096 and tensor_peak:
-                    extra[key.replace("_tok_s", "_gemm_frac_of_int8_peak")] = tps * gemm_flop_per_token / 1e12 / tensor_peak
+                if n == 4096 and mode != "exact-cuda-cores":
+                    extra[key.replace("_tok_s", "_gemm_frac_of_int8_peak")] = tps * flop_tok / 1e12 / tensor_peak
         m.set_prefill_mode("exact")
         extra["int8_peak_tflops_used"] = tensor_peak
-        extra["int8_peak_source"] = "2 x bf16_tflops_sustained of MEASURED_PEAKS.json (no int8 figure is measured)"
-        extra["gemm_gflop_per_token"] = gemm_flop_per_token / 1e9
+        extra["int8_peak_source"] = peak_src
+        extra["gemm_gflop_per_token"] = flop_tok / 1e9
         logits = m.forward_prefill(prompt, 0, st)
         m.generate_greedy(int(np.argmax(logits)), 512, st)
         extra["decode_tg512_tok_s"] = 512 / (m.last_elapsed_ms() * 1e-3)
-        extra["prefill_paths"] = {"exact": "bit-exact CUDA-core integer GEMM + exact-order attention (default)",
-                                  "tensor": "tcgen05 int8 GEMM (exact block sums, fused f32 chain) + exact-order attention"}
+        extra["prefill_paths"] = {"exact": "default: bit-exact GEMM on tcgen05 (lane partials in tensor memory, eight unfused chains) + exact-order attention",
+                                  "tensor": "tcgen05 int8 GEMM (exact block sums, one fused f32 chain) + exact-order attention",
+                                  "exact-cuda-cores": "bit-exact CUDA-core integer GEMM + exact-order attention"}
         line["extra"] = extra
     print(json.dumps(line))
     if world > 1:
