@@ -108,6 +108,22 @@ int32_t wick_cuda_forward_greedy(wick_cuda_model* m, uint32_t token, uint32_t po
 int32_t wick_cuda_forward_prefill(wick_cuda_model* m, const uint32_t* tokens_host, uint32_t n,
                                   uint32_t start_pos, float* logits_host);
 
+/* Embedding-input methods of the trait (model/mod.rs:172-267; CPU model lfm2.rs:2291-2350, :2452-2500);
+ * supports_embedding_input() is true for this backend.  Inputs are host f32.
+ *  - forward_prefill_from_embeddings: frames [n][hidden] row-major instead of token ids; logits of the
+ *    last frame; same start_pos rules as forward_prefill.
+ *  - forward_from_embedding: one frame at the model's own position (`pos` is ignored, like forward) -> logits.
+ *  - forward_hidden_from_embedding / forward_embedding: one frame / one token id -> the output-normed
+ *    hidden row [hidden] (the vector the logit projection would read), no logits.
+ * All four advance seq_len and run the one-row or n-row prefill pipeline. */
+int32_t wick_cuda_forward_prefill_from_embeddings(wick_cuda_model* m, const float* embeddings_host, uint32_t n,
+                                                  uint32_t start_pos, float* logits_host);
+int32_t wick_cuda_forward_from_embedding(wick_cuda_model* m, const float* embedding_host, uint32_t pos,
+                                         float* logits_host);
+int32_t wick_cuda_forward_hidden_from_embedding(wick_cuda_model* m, const float* embedding_host, uint32_t pos,
+                                                float* hidden_host);
+int32_t wick_cuda_forward_embedding(wick_cuda_model* m, uint32_t token, uint32_t pos, float* hidden_host);
+
 /* Which GEMM forward_prefill uses for chunks of >= 16 tokens (shorter chunks always take the
  * CUDA-core kernel).  Decode is not affected.
  * EXACT (default): the arithmetic of gemm_q*_q8_0_neon (simd.rs:696-1019) bit for bit, so logits and

@@ -419,6 +419,30 @@ class OracleModel:
         lib().orc_model_forward_prefill(self.h, _p(t), C.c_int(t.size), C.c_int(start_pos), _p(logits))
         return logits
 
+    def forward_from_embedding(self, emb, want: str = "logits") -> np.ndarray:
+        """forward_from_embedding (want="logits") / forward_hidden_from_embedding (want="hidden"), lfm2.rs:2295-2350."""
+        e = np.ascontiguousarray(emb, np.float32)
+        assert e.size == self.hidden
+        logits = np.empty(self.vocab, np.float32) if want == "logits" else None
+        hid = np.empty(self.hidden, np.float32) if want == "hidden" else None
+        lib().orc_model_forward_from_embedding(self.h, _p(e), _p(logits) if logits is not None else None,
+                                               _p(hid) if hid is not None else None)
+        return logits if want == "logits" else hid
+
+    def forward_embedding(self, token: int) -> np.ndarray:
+        """forward_embedding (lfm2.rs:2326-2337): the output-normed hidden state of one token step."""
+        return self.forward(token, want_hidden=True)[1]
+
+    def forward_prefill_from_embeddings(self, emb, start_pos: int) -> np.ndarray:
+        """forward_prefill_from_embeddings (lfm2.rs:2452-2500): frames [n][hidden] row-major."""
+        e = np.ascontiguousarray(emb, np.float32)
+        assert e.ndim == 2 and e.shape[1] == self.hidden and e.shape[0] > 0
+        if start_pos == 0:
+            self.reset()
+        logits = np.empty(self.vocab, np.float32)
+        lib().orc_model_forward_prefill_from_embeddings(self.h, _p(e), C.c_int(e.shape[0]), C.c_int(start_pos), _p(logits))
+        return logits
+
     def forward_prefill_chunked(self, tokens, start_pos: int = 0, ubatch: int = 512) -> np.ndarray:
         """Default `forward_prefill_chunked` (model/mod.rs:111-140) without cancellation."""
         t = np.ascontiguousarray(tokens, np.uint32)

@@ -612,10 +612,13 @@ void quantize_scratch(OrcModel& M, const float* x, int k) {
 
 // run_layers, lfm2.rs:1020-1124 (aarch64 branch), then the tied-embedding logits
 // GEMV of forward(), lfm2.rs:2268-2288.
-void forward_token(OrcModel& M, uint32_t token, float* logits, float* hidden_out) {
+// `emb` != NULL: forward_from_embedding / forward_hidden_from_embedding (lfm2.rs:2295-2350), the
+// input vector replaces the embedding row.
+void forward_token(OrcModel& M, uint32_t token, float* logits, float* hidden_out, const float* emb = nullptr) {
     int hs = M.d.hidden, is = M.d.ffn;
     std::vector<float> hidden(hs), normed(hs), out(hs), gate(is), up(is);
-    dequant_row(M.d.embd.dtype, M.d.embd.data + (size_t)token * (hs / QK) * block_bytes(M.d.embd.dtype), hs, hidden.data());
+    if (emb) memcpy(hidden.data(), emb, hs * sizeof(float));
+    else dequant_row(M.d.embd.dtype, M.d.embd.data + (size_t)token * (hs / QK) * block_bytes(M.d.embd.dtype), hs, hidden.data());
     int pos = M.seq_len;
     for (int i = 0; i < M.d.n_layers; i++) {
         const OrcLayer& L = M.layers[i];
@@ -658,15 +661,18 @@ void gemm_tokens(const OrcWeight& w, const std::vector<float>& s, const std::vec
 }
 
 // prefill_layers_and_logits, lfm2.rs:1139-2213, aarch64 / non-BLAS branch.
-void forward_prefill(OrcModel& M, const uint32_t* tokens, int n, int start_pos, float* logits) {
+// `emb` != NULL: forward_prefill_from_embeddings (lfm2.rs:2452-2500), row-major frames [n][hs].
+void forward_prefill(OrcModel& M, const uint32_t* tokens, int n, int start_pos, float* logits, const float* emb = nullptr) {
     int hs = M.d.hidden, is = M.d.ffn, hd = M.head_dim();
     std::vector<float> hidden((size_t)n * hs), normed((size_t)n * hs), block_out((size_t)n * hs);
     std::vector<float> bs;
     std::vector<int8_t> bq;
     int eb = block_bytes(M.d.embd.dtype);
     // forward_prefill_inner, lfm2.rs:2238-2251
-    for (int j = 0; j < n; j++)
-        dequant_row(M.d.embd.dtype, M.d.embd.data + (size_t)tokens[j] * (hs / QK) * eb, hs, hidden.data() + (size_t)j * hs);
+    if (emb) memcpy(hidden.data(), emb, (size_t)n * hs * sizeof(float));
+    else
+        for (int j = 0; j < n; j++)
+            dequant_row(M.d.embd.dtype, M.d.embd.data + (size_t)tokens[j] * (hs / QK) * eb, hs, hidden.data() + (size_t)j * hs);
 
     for (int li = 0; li < M.d.n_layers; li++) {
         const OrcLayer& L = M.layers[li];
@@ -889,6 +895,14 @@ ORC_API void orc_model_forward(void* m, uint32_t token, float* logits, float* hi
 // does NOT reset here, the caller resets, as with a fresh InferenceState.
 ORC_API void orc_model_forward_prefill(void* m, const uint32_t* tokens, int n, int start_pos, float* logits) {
     forward_prefill(*(OrcModel*)m, tokens, n, start_pos, logits);
+}
+// forward_from_embedding (logits) / forward_hidden_from_embedding (hidden), lfm2.rs:2295-2350; either output may be NULL.
+ORC_API void orc_model_forward_from_embedding(void* m, const float* emb, float* logits, float* hidden) {
+    forward_token(*(OrcModel*)m, 0, logits, hidden, emb);
+}
+// forward_prefill_from_embeddings, lfm2.rs:2452-2500.
+ORC_API void orc_model_forward_prefill_from_embeddings(void* m, const float* emb, int n, int start_pos, float* logits) {
+    forward_prefill(*(OrcModel*)m, nullptr, n, start_pos, logits, emb);
 }
 // Greedy decode loop as Session::generate drives it (session.rs:1186-1257): feeds
 // `first`, writes n_steps argmax tokens.

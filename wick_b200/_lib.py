@@ -48,6 +48,10 @@ SIGNATURES = {
     "wick_cuda_forward": [_vp, _u32, _u32, _vp],
     "wick_cuda_forward_greedy": [_vp, _u32, _u32, C.POINTER(_u32)],
     "wick_cuda_forward_prefill": [_vp, _vp, _u32, _u32, _vp],
+    "wick_cuda_forward_prefill_from_embeddings": [_vp, _vp, _u32, _u32, _vp],
+    "wick_cuda_forward_from_embedding": [_vp, _vp, _u32, _vp],
+    "wick_cuda_forward_hidden_from_embedding": [_vp, _vp, _u32, _vp],
+    "wick_cuda_forward_embedding": [_vp, _u32, _u32, _vp],
     "wick_cuda_set_prefill_mode": [_vp, _i32],
     "wick_cuda_prefill_mode": [_vp, C.POINTER(_i32)],
     "wick_cuda_prefill_uses_tensor_cores": [_vp, C.POINTER(_i32)],

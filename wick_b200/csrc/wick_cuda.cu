@@ -80,6 +80,7 @@ struct wick_cuda_model {
     CUtensorMap map_x_hs[2], map_x_is[2];  // activations [max_chunk][hs | is], box of 64 / 128 rows
     int8_t* q8m = nullptr;                  // lane-group-masked activations [4 * max_chunk][hs | is] (exact tensor-core GEMM)
     CUtensorMap map_xm_hs, map_xm_is;
+    float* normed_last = nullptr;  // output-normed hidden row of the last prefilled token
     uint32_t* tc_err = nullptr;
     // scratch, token-major
     float *hidden = nullptr, *block_out = nullptr, *ffn_out = nullptr, *proj = nullptr, *qbuf = nullptr, *kbuf = nullptr,
@@ -437,7 +438,11 @@ int32_t capture_graph(wick_cuda_model* m, bool greedy, cudaGraphExec_t* out, uin
 
 // One internal prefill chunk of n <= max_chunk tokens already in m->tokens_dev
 // (prefill_layers_and_logits, lfm2.rs:1139-2213, aarch64 non-BLAS branch).
-void enqueue_prefill_chunk(wick_cuda_model* m, int n, int start_pos, bool flash, bool want_logits) {
+// `embed`: fill hidden from the token ids (false: the caller has copied input embeddings into m->hidden).
+// `last`: this chunk ends the call: the last row goes through the output norm and then, with `want_logits`,
+// through the vocabulary head (always leaving the normed row in m->normed_last).
+void enqueue_prefill_chunk(wick_cuda_model* m, int n, int start_pos, bool flash, bool last, bool embed = true,
+                           bool want_logits = true) {
     cudaStream_t st = m->stream;
     const int hs = m->cfg.hidden_size, is = m->cfg.intermediate_size, hd = m->head_dim;
     const float eps = m->cfg.rms_norm_eps;
@@ -472,7 +477,7 @@ void enqueue_prefill_chunk(wick_cuda_model* m, int n, int start_pos, bool flash,
             for (const G& g : list) launch_gemm(st, *g.w, m->q8s, m->q8q, n, g.out);
         }
     };
-    launch_embed(st, m->embd, m->tokens_dev, nullptr, m->hidden, n);
+    if (embed) launch_embed(st, m->embd, m->tokens_dev, nullptr, m->hidden, n);
     const float* pending = nullptr;
     for (size_t li = 0; li < m->layers.size(); li++) {
         Layer& L = m->layers[li];
@@ -499,13 +504,15 @@ void enqueue_prefill_chunk(wick_cuda_model* m, int n, int start_pos, bool flash,
         gemms({{&L.down, &L.tc_down, m->ffn_out}});
         pending = m->ffn_out;
     }
-    if (want_logits) {
+    if (last) {
         // last token only (lfm2.rs:2190-2212)
-        size_t last = (size_t)(n - 1) * hs;
-        launch_add_rmsnorm_quant(st, m->hidden + last, pending + last, m->output_norm, eps, 1, hs, m->q8s, m->q8q, nullptr);
-        GemvJob lg{};
-        lg.count = 1; lg.w[0] = m->embd; lg.y[0] = m->logits;
-        launch_gemv(st, lg, m->q8s, m->q8q);
+        size_t lastrow = (size_t)(n - 1) * hs;
+        launch_add_rmsnorm_quant(st, m->hidden + lastrow, pending + lastrow, m->output_norm, eps, 1, hs, m->q8s, m->q8q, m->normed_last);
+        if (want_logits) {
+            GemvJob lg{};
+            lg.count = 1; lg.w[0] = m->embd; lg.y[0] = m->logits;
+            launch_gemv(st, lg, m->q8s, m->q8q);
+        }
     }
 }
 
@@ -691,6 +698,7 @@ int32_t build_model(wick_cuda_model* m, const GgufImage& g, uint32_t context_siz
     W_TRY(dev_alloc(m, &m->q8s, N * (std::max(hs, is) / QK)));
     W_TRY(dev_alloc(m, &m->q8q, N * std::max(hs, is)));
     W_TRY(dev_alloc(m, &m->tokens_dev, N));
+    W_TRY(dev_alloc(m, &m->normed_last, (size_t)hs));
     W_TRY(dev_alloc(m, &m->ctl, 1));
     W_TRY(dev_alloc(m, &m->argmax_tok, 1));
     m->ring_len = (int)c.max_seq_len;
@@ -880,15 +888,17 @@ int32_t wick_cuda_generate_greedy(wick_cuda_model* m, uint32_t first_token, uint
     return WICK_CUDA_OK;
 }
 
-int32_t wick_cuda_forward_prefill(wick_cuda_model* m, const uint32_t* tokens_host, uint32_t n, uint32_t start_pos,
-                                  float* logits_host) {
-    W_TRY(check_model(m));
-    if (!tokens_host || !logits_host) return fail(WICK_CUDA_ERR_BAD_ARG, "NULL argument");
+// forward_prefill and its embedding-input relatives: exactly one of tokens_host / emb_host is given; the
+// result is the logits of the last position (logits_host) and / or its output-normed hidden row (hidden_host).
+static int32_t prefill_core(wick_cuda_model* m, const uint32_t* tokens_host, const float* emb_host, uint32_t n, uint32_t start_pos,
+                            float* logits_host, float* hidden_host) {
+    const int hs = m->cfg.hidden_size;
     if (n == 0) return fail(WICK_CUDA_ERR_BAD_ARG, "forward_prefill requires at least one token");
-    for (uint32_t i = 0; i < n; i++)
-        if (tokens_host[i] >= m->cfg.vocab_size)
-            return fail(WICK_CUDA_ERR_BAD_ARG, "token_id " + std::to_string(tokens_host[i]) + " out of range for vocab size " +
-                                                   std::to_string(m->cfg.vocab_size));
+    if (tokens_host)
+        for (uint32_t i = 0; i < n; i++)
+            if (tokens_host[i] >= m->cfg.vocab_size)
+                return fail(WICK_CUDA_ERR_BAD_ARG, "token_id " + std::to_string(tokens_host[i]) + " out of range for vocab size " +
+                                                       std::to_string(m->cfg.vocab_size));
     if (start_pos != 0 && start_pos != m->seq_len)
         return fail(WICK_CUDA_ERR_BAD_ARG, "start_pos " + std::to_string(start_pos) + " != model seq_len " + std::to_string(m->seq_len));
     if ((uint64_t)start_pos + n > m->cfg.max_seq_len)
@@ -900,10 +910,14 @@ int32_t wick_cuda_forward_prefill(wick_cuda_model* m, const uint32_t* tokens_hos
     CU_TRY(cudaEventRecord(m->ev0, m->stream));
     for (uint32_t c0 = 0; c0 < n; c0 += m->max_chunk) {
         uint32_t cn = std::min<uint32_t>(m->max_chunk, n - c0);
-        memcpy(m->h_u32, tokens_host + c0, (size_t)cn * 4);
-        CU_TRY(cudaMemcpyAsync(m->tokens_dev, m->h_u32, (size_t)cn * 4, cudaMemcpyHostToDevice, m->stream));
+        if (tokens_host) {
+            memcpy(m->h_u32, tokens_host + c0, (size_t)cn * 4);
+            CU_TRY(cudaMemcpyAsync(m->tokens_dev, m->h_u32, (size_t)cn * 4, cudaMemcpyHostToDevice, m->stream));
+        } else {
+            CU_TRY(cudaMemcpyAsync(m->hidden, emb_host + (size_t)c0 * hs, (size_t)cn * hs * 4, cudaMemcpyHostToDevice, m->stream));
+        }
         const unsigned long long before = g_kernel_launches;
-        enqueue_prefill_chunk(m, (int)cn, (int)(start_pos + c0), flash, c0 + cn == n);
+        enqueue_prefill_chunk(m, (int)cn, (int)(start_pos + c0), flash, c0 + cn == n, tokens_host != nullptr, logits_host != nullptr);
         m->launches += g_kernel_launches - before;
         CU_TRY(cudaGetLastError());
         CU_TRY(cudaStreamSynchronize(m->stream));  // h_u32 is reused by the next chunk
@@ -911,7 +925,7 @@ int32_t wick_cuda_forward_prefill(wick_cuda_model* m, const uint32_t* tokens_hos
     uint32_t newpos[2] = {0, start_pos + n};
     memcpy(m->h_u32, newpos, 8);
     CU_TRY(cudaMemcpyAsync(&m->ctl->pos, m->h_u32 + 1, 4, cudaMemcpyHostToDevice, m->stream));
-    CU_TRY(cudaMemcpyAsync(m->h_logits, m->logits, (size_t)m->cfg.vocab_size * 4, cudaMemcpyDeviceToHost, m->stream));
+    if (logits_host) CU_TRY(cudaMemcpyAsync(m->h_logits, m->logits, (size_t)m->cfg.vocab_size * 4, cudaMemcpyDeviceToHost, m->stream));
     m->h_u32[2] = 0;
     if (m->tc_err) CU_TRY(cudaMemcpyAsync(m->h_u32 + 2, m->tc_err, 4, cudaMemcpyDeviceToHost, m->stream));
     CU_TRY(cudaEventRecord(m->ev1, m->stream));
@@ -921,9 +935,48 @@ int32_t wick_cuda_forward_prefill(wick_cuda_model* m, const uint32_t* tokens_hos
         cudaMemsetAsync(m->tc_err, 0, 4, m->stream);
         return fail(WICK_CUDA_ERR_TIMEOUT, "tensor-core prefill GEMM: a bounded wait expired (role code " + std::to_string(code) + ")");
     }
-    memcpy(logits_host, m->h_logits, (size_t)m->cfg.vocab_size * 4);
+    if (logits_host) memcpy(logits_host, m->h_logits, (size_t)m->cfg.vocab_size * 4);
+    if (hidden_host) CU_TRY(cudaMemcpy(hidden_host, m->normed_last, (size_t)hs * 4, cudaMemcpyDeviceToHost));
     m->seq_len = start_pos + n;
     return WICK_CUDA_OK;
+}
+
+int32_t wick_cuda_forward_prefill(wick_cuda_model* m, const uint32_t* tokens_host, uint32_t n, uint32_t start_pos,
+                                  float* logits_host) {
+    W_TRY(check_model(m));
+    if (!tokens_host || !logits_host) return fail(WICK_CUDA_ERR_BAD_ARG, "NULL argument");
+    return prefill_core(m, tokens_host, nullptr, n, start_pos, logits_host, nullptr);
+}
+
+int32_t wick_cuda_forward_prefill_from_embeddings(wick_cuda_model* m, const float* embeddings_host, uint32_t n, uint32_t start_pos,
+                                                  float* logits_host) {
+    W_TRY(check_model(m));
+    if (!embeddings_host || !logits_host) return fail(WICK_CUDA_ERR_BAD_ARG, "NULL argument");
+    if (n == 0) return fail(WICK_CUDA_ERR_BAD_ARG, "forward_prefill_from_embeddings requires at least one frame");
+    return prefill_core(m, nullptr, embeddings_host, n, start_pos, logits_host, nullptr);
+}
+
+// The single-step embedding-input methods run the one-row prefill pipeline at the model's own
+// position (like forward, they ignore `pos`); a one-row prefill is bit-identical to a decode step.
+int32_t wick_cuda_forward_from_embedding(wick_cuda_model* m, const float* embedding_host, uint32_t pos, float* logits_host) {
+    (void)pos;
+    W_TRY(check_model(m));
+    if (!embedding_host || !logits_host) return fail(WICK_CUDA_ERR_BAD_ARG, "NULL argument");
+    return prefill_core(m, nullptr, embedding_host, 1, m->seq_len, logits_host, nullptr);
+}
+
+int32_t wick_cuda_forward_hidden_from_embedding(wick_cuda_model* m, const float* embedding_host, uint32_t pos, float* hidden_host) {
+    (void)pos;
+    W_TRY(check_model(m));
+    if (!embedding_host || !hidden_host) return fail(WICK_CUDA_ERR_BAD_ARG, "NULL argument");
+    return prefill_core(m, nullptr, embedding_host, 1, m->seq_len, nullptr, hidden_host);
+}
+
+int32_t wick_cuda_forward_embedding(wick_cuda_model* m, uint32_t token, uint32_t pos, float* hidden_host) {
+    (void)pos;
+    W_TRY(check_model(m));
+    if (!hidden_host) return fail(WICK_CUDA_ERR_BAD_ARG, "NULL argument");
+    return prefill_core(m, &token, nullptr, 1, m->seq_len, nullptr, hidden_host);
 }
 
 int32_t wick_cuda_set_prefill_mode(wick_cuda_model* m, int32_t mode) {

@@ -134,6 +134,50 @@ class CudaLfm2Model:
         state.seq_len = start_pos + t.size
         return logits
 
+    # ── embedding-input methods (mod.rs:172-267; lfm2.rs:2291-2350, :2452-2500) ─────────────────
+    def supports_embedding_input(self) -> bool:
+        return True
+
+    def forward_prefill_from_embeddings(self, embeddings, n_tokens: int, start_pos: int, state: InferenceState) -> np.ndarray:
+        """Frames [n_tokens][hidden] row-major instead of token ids; logits of the last frame."""
+        e = np.ascontiguousarray(embeddings, dtype=np.float32).reshape(-1)
+        assert n_tokens > 0, "forward_prefill_from_embeddings requires at least one frame"
+        assert e.size == n_tokens * self._config.hidden_size, \
+            f"embeddings.len() ({e.size}) != n_tokens ({n_tokens}) * hidden_size ({self._config.hidden_size})"
+        logits = np.empty(self._config.vocab_size, np.float32)
+        with self._lock:
+            check(self._lib.wick_cuda_forward_prefill_from_embeddings(self._h, e.ctypes.data, n_tokens, int(start_pos),
+                                                                      logits.ctypes.data))
+        state.seq_len = start_pos + n_tokens
+        return logits
+
+    def forward_from_embedding(self, embedding, pos: int, state: InferenceState) -> np.ndarray:
+        e = np.ascontiguousarray(embedding, dtype=np.float32).reshape(-1)
+        assert e.size == self._config.hidden_size
+        logits = np.empty(self._config.vocab_size, np.float32)
+        with self._lock:
+            check(self._lib.wick_cuda_forward_from_embedding(self._h, e.ctypes.data, int(pos), logits.ctypes.data))
+        state.seq_len += 1
+        return logits
+
+    def forward_hidden_from_embedding(self, embedding, pos: int, state: InferenceState) -> np.ndarray:
+        e = np.ascontiguousarray(embedding, dtype=np.float32).reshape(-1)
+        assert e.size == self._config.hidden_size
+        hid = np.empty(self._config.hidden_size, np.float32)
+        with self._lock:
+            check(self._lib.wick_cuda_forward_hidden_from_embedding(self._h, e.ctypes.data, int(pos), hid.ctypes.data))
+        state.seq_len += 1
+        return hid
+
+    def forward_embedding(self, tokens: Sequence[int], pos: int, state: InferenceState) -> np.ndarray:
+        """The output-normed hidden state of one token step, before the logit projection (mod.rs:172-184)."""
+        assert len(tokens) == 1
+        hid = np.empty(self._config.hidden_size, np.float32)
+        with self._lock:
+            check(self._lib.wick_cuda_forward_embedding(self._h, int(tokens[0]), int(pos), hid.ctypes.data))
+        state.seq_len += 1
+        return hid
+
     def forward_prefill_chunked(self, tokens: Sequence[int], start_pos: int, state: InferenceState, ubatch: int,
                                 cancel: Optional[threading.Event] = None) -> Tuple[int, Optional[np.ndarray]]:
         """Default trait method (mod.rs:111-140): ubatch-sized forward_prefill calls, cancel polled
@@ -158,9 +202,6 @@ class CudaLfm2Model:
         return out
 
     def supports_kv_shift(self) -> bool:
-        return False
-
-    def supports_embedding_input(self) -> bool:
         return False
 
     def turboquant_supported(self) -> bool:
