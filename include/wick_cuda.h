@@ -124,6 +124,14 @@ int32_t wick_cuda_forward_hidden_from_embedding(wick_cuda_model* m, const float*
                                                 float* hidden_host);
 int32_t wick_cuda_forward_embedding(wick_cuda_model* m, uint32_t token, uint32_t pos, float* hidden_host);
 
+/* Model::shift_kv, the n_keep context shift (model/mod.rs:145-170; CPU model lfm2.rs:2500-2516 ->
+ * InferenceState::shift_kv_with_rope, kv_cache.rs:601-715); supports_kv_shift() is true for this backend.
+ * Drops rows [n_keep, n_keep + shift) of every attention layer's K and V caches, slides the tail down and
+ * rotates the moved K rows by R(-shift) (apply_rope_delta_to_head, cpu.rs:2174-2187); conv buffers are left
+ * alone; seq_len -= shift.  The reference asserts shift > 0 and n_keep + shift <= seq_len; here those are
+ * WICK_CUDA_ERR_BAD_ARG. */
+int32_t wick_cuda_shift_kv(wick_cuda_model* m, uint32_t n_keep, uint32_t shift);
+
 /* Which GEMM forward_prefill uses for chunks of >= 16 tokens (shorter chunks always take the
  * CUDA-core kernel).  Decode is not affected.
  * EXACT (default): the arithmetic of gemm_q*_q8_0_neon (simd.rs:696-1019) bit for bit, so logits and

@@ -49,6 +49,7 @@ def lib() -> C.CDLL:
         _lib.orc_model_create.restype = C.c_void_p
         _lib.orc_model_seq_len.restype = C.c_int
         _lib.orc_model_kv_rows.restype = C.c_int
+        _lib.orc_model_shift_kv.restype = C.c_int
     return _lib
 
 
@@ -418,6 +419,11 @@ class OracleModel:
         logits = np.empty(self.vocab, np.float32)
         lib().orc_model_forward_prefill(self.h, _p(t), C.c_int(t.size), C.c_int(start_pos), _p(logits))
         return logits
+
+    def shift_kv(self, n_keep: int, shift: int) -> None:
+        """Model::shift_kv (lfm2.rs:2507-2516): n_keep context shift with RoPE re-rotation of the moved K rows."""
+        if lib().orc_model_shift_kv(self.h, C.c_int(n_keep), C.c_int(shift)) != 0:
+            raise ValueError(f"shift range out of bounds: n_keep={n_keep} + shift={shift} > seq_len={self.seq_len}")
 
     def forward_from_embedding(self, emb, want: str = "logits") -> np.ndarray:
         """forward_from_embedding (want="logits") / forward_hidden_from_embedding (want="hidden"), lfm2.rs:2295-2350."""

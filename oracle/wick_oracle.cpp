@@ -904,6 +904,40 @@ ORC_API void orc_model_forward_from_embedding(void* m, const float* emb, float* 
 ORC_API void orc_model_forward_prefill_from_embeddings(void* m, const float* emb, int n, int start_pos, float* logits) {
     forward_prefill(*(OrcModel*)m, nullptr, n, start_pos, logits, emb);
 }
+// Model::shift_kv -> InferenceState::shift_kv_with_rope (lfm2.rs:2507-2516, kv_cache.rs:601-715): drop rows
+// [n_keep, n_keep + shift) of every attention layer's K and V, slide the tail down, and rotate the moved K
+// rows by R(-shift) (apply_rope_delta_to_head, cpu.rs:2174-2187: iterative theta, libm sin / cos, unfused
+// products).  Conv buffers are left alone.  Returns 0, or -1 when the preconditions the reference asserts fail.
+ORC_API int orc_model_shift_kv(void* m, int n_keep, int shift) {
+    OrcModel& M = *(OrcModel*)m;
+    if (shift <= 0 || n_keep < 0 || n_keep + shift > M.seq_len) return -1;
+    const int hd = M.head_dim(), half = hd / 2, new_len = M.seq_len - shift;
+    const float theta_scale = powf(M.d.rope_theta, -2.0f / (float)hd);
+    for (int li = 0; li < M.d.n_layers; li++) {
+        const OrcLayer& L = M.layers[li];
+        if (!L.is_attn) continue;
+        const int kv_dim = L.n_kv_heads * hd;
+        std::vector<float>& kc = M.kc[li];
+        std::vector<float>& vc = M.vc[li];
+        if (kc.empty() && vc.empty()) continue;
+        kc.erase(kc.begin() + (size_t)n_keep * kv_dim, kc.begin() + (size_t)(n_keep + shift) * kv_dim);
+        vc.erase(vc.begin() + (size_t)n_keep * kv_dim, vc.begin() + (size_t)(n_keep + shift) * kv_dim);
+        for (int t = n_keep; t < new_len; t++)
+            for (int h = 0; h < L.n_kv_heads; h++) {
+                float* head = kc.data() + (size_t)t * kv_dim + (size_t)h * hd;
+                float theta = (float)(-shift);
+                for (int i = 0; i < half; i++) {
+                    const float sn = sinf(theta), cs = cosf(theta);
+                    const float x0 = head[i], x1 = head[i + half];
+                    head[i] = x0 * cs - x1 * sn;
+                    head[i + half] = x0 * sn + x1 * cs;
+                    theta *= theta_scale;
+                }
+            }
+    }
+    M.seq_len = new_len;
+    return 0;
+}
 // Greedy decode loop as Session::generate drives it (session.rs:1186-1257): feeds
 // `first`, writes n_steps argmax tokens.
 ORC_API void orc_model_generate_greedy(void* m, uint32_t first, int n_steps, uint32_t* out_tokens) {

@@ -145,7 +145,7 @@ def test_trait_semantics(wick, orc, model_dir):
     assert cfg.max_seq_len == 48 and cfg.n_layers == spec.n_layers and cfg.hidden_size == spec.hidden
     assert cfg.block_types == tuple("Attention" if i in spec.attn_layers else "GatedConv" for i in range(spec.n_layers))
     assert cfg.kv_heads_per_layer == tuple(spec.n_kv_heads if i in spec.attn_layers else 0 for i in range(spec.n_layers))
-    assert m.gpu_memory_bytes() > 0 and not m.supports_kv_shift() and m.supports_embedding_input()
+    assert m.gpu_memory_bytes() > 0 and m.supports_kv_shift() and m.supports_embedding_input()
     st = wick.InferenceState()
     toks = gs.random_prompt(40, cfg.vocab_size)
     with pytest.raises(WickCudaError) as e:                     # out-of-range token

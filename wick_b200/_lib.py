@@ -52,6 +52,7 @@ SIGNATURES = {
     "wick_cuda_forward_from_embedding": [_vp, _vp, _u32, _vp],
     "wick_cuda_forward_hidden_from_embedding": [_vp, _vp, _u32, _vp],
     "wick_cuda_forward_embedding": [_vp, _u32, _u32, _vp],
+    "wick_cuda_shift_kv": [_vp, _u32, _u32],
     "wick_cuda_set_prefill_mode": [_vp, _i32],
     "wick_cuda_prefill_mode": [_vp, C.POINTER(_i32)],
     "wick_cuda_prefill_uses_tensor_cores": [_vp, C.POINTER(_i32)],

@@ -67,6 +67,11 @@ void configure_naive_attention_smem(size_t bytes);
 void launch_attention_flash(cudaStream_t st, const float* q, const float* k_cache, const float* v_cache, float* out,
                             int n, int start_pos, int n_heads, int n_kv_heads, int head_dim);
 
+// n_keep context shift (kv_cache.rs:601-715): gathers cache rows [row0 + shift, row0 + shift + rows) into a
+// dense scratch, K rows rotated by the delta table (cos_delta / sin_delta of hd/2 entries), V rows as they are (NULL tables).
+void launch_kv_shift_gather(cudaStream_t st, const float* cache, float* scratch, int row0, int rows, int shift, int kv_dim, int hd,
+                            const float* cos_delta, const float* sin_delta);
+
 // Integer GEMV, up to three matrices sharing one quantised input (simd.rs:328-415, :440-524).
 struct GemvJob {
     DevWeight w[3];

@@ -366,4 +366,36 @@ void launch_decode_advance(cudaStream_t st, DecodeCtl* ctl, const uint32_t* argm
     k_decode_advance<<<1, 1, 0, st>>>(ctl, argmax_tok, ring, ring_len);
 }
 
+// ── n_keep context shift ────────────────────────────────────────────────────
+// Rows [row0, row0 + rows) of a K or V cache, read `shift` rows further up, into a dense scratch
+// [rows][kv_dim]; K rows are rotated by R(-shift) on the way (apply_rope_delta_to_head, cpu.rs:2174-2187:
+// unfused products, pair (i, i + hd/2)); cd / sd == NULL: plain copy (V).
+__global__ void k_kv_shift_gather(const float* __restrict__ cache, float* __restrict__ scratch, int row0, int rows, int shift,
+                                  int kv_dim, int hd, const float* __restrict__ cd, const float* __restrict__ sd) {
+    const int half = hd / 2, pairs_per_row = kv_dim / 2;
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)rows * pairs_per_row) return;
+    const int r = (int)(idx / pairs_per_row), pr = (int)(idx % pairs_per_row);
+    const int h = pr / half, i = pr % half;
+    const float* src = cache + (size_t)(row0 + r + shift) * kv_dim + (size_t)h * hd;
+    float* dst = scratch + (size_t)r * kv_dim + (size_t)h * hd;
+    const float x0 = src[i], x1 = src[i + half];
+    if (cd) {
+        const float c = cd[i], sn = sd[i];
+        dst[i] = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, sn));
+        dst[i + half] = __fadd_rn(__fmul_rn(x0, sn), __fmul_rn(x1, c));
+    } else {
+        dst[i] = x0;
+        dst[i + half] = x1;
+    }
+}
+
+void launch_kv_shift_gather(cudaStream_t st, const float* cache, float* scratch, int row0, int rows, int shift, int kv_dim, int hd,
+                            const float* cos_delta, const float* sin_delta) {
+    const size_t n = (size_t)rows * (kv_dim / 2);
+    if (!n) return;
+    g_kernel_launches++;
+    k_kv_shift_gather<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(cache, scratch, row0, rows, shift, kv_dim, hd, cos_delta, sin_delta);
+}
+
 }  // namespace wick

@@ -81,6 +81,7 @@ struct wick_cuda_model {
     int8_t* q8m = nullptr;                  // lane-group-masked activations [4 * max_chunk][hs | is] (exact tensor-core GEMM)
     CUtensorMap map_xm_hs, map_xm_is;
     float* normed_last = nullptr;  // output-normed hidden row of the last prefilled token
+    float* rope_delta = nullptr;   // [head_dim]: cos then sin of the n_keep shift rotation
     uint32_t* tc_err = nullptr;
     // scratch, token-major
     float *hidden = nullptr, *block_out = nullptr, *ffn_out = nullptr, *proj = nullptr, *qbuf = nullptr, *kbuf = nullptr,
@@ -699,6 +700,7 @@ int32_t build_model(wick_cuda_model* m, const GgufImage& g, uint32_t context_siz
     W_TRY(dev_alloc(m, &m->q8q, N * std::max(hs, is)));
     W_TRY(dev_alloc(m, &m->tokens_dev, N));
     W_TRY(dev_alloc(m, &m->normed_last, (size_t)hs));
+    W_TRY(dev_alloc(m, &m->rope_delta, (size_t)hd));
     W_TRY(dev_alloc(m, &m->ctl, 1));
     W_TRY(dev_alloc(m, &m->argmax_tok, 1));
     m->ring_len = (int)c.max_seq_len;
@@ -977,6 +979,55 @@ int32_t wick_cuda_forward_embedding(wick_cuda_model* m, uint32_t token, uint32_t
     W_TRY(check_model(m));
     if (!hidden_host) return fail(WICK_CUDA_ERR_BAD_ARG, "NULL argument");
     return prefill_core(m, &token, nullptr, 1, m->seq_len, nullptr, hidden_host);
+}
+
+// Model::shift_kv (mod.rs:158-170; lfm2.rs:2507-2516 -> kv_cache.rs:601-715).
+int32_t wick_cuda_shift_kv(wick_cuda_model* m, uint32_t n_keep, uint32_t shift) {
+    W_TRY(check_model(m));
+    if (shift == 0) return fail(WICK_CUDA_ERR_BAD_ARG, "shift must be > 0");
+    if ((uint64_t)n_keep + shift > m->seq_len)
+        return fail(WICK_CUDA_ERR_BAD_ARG, "shift range out of bounds: n_keep=" + std::to_string(n_keep) + " + shift=" +
+                                               std::to_string(shift) + " > seq_len=" + std::to_string(m->seq_len));
+    CU_TRY(cudaSetDevice(m->device));
+    const int hd = m->head_dim, half = hd / 2;
+    const uint32_t new_len = m->seq_len - shift;
+    const int retained = (int)(new_len - n_keep);
+    if (retained > 0) {
+        // delta rotation table with the host libm in the reference's order (cpu.rs:2174-2187)
+        std::vector<float> tab(hd);
+        const float theta_scale = powf(m->cfg.rope_theta, -2.0f / (float)hd);
+        float theta = (float)(-(int)shift);
+        for (int i = 0; i < half; i++) {
+            tab[i] = cosf(theta);
+            tab[half + i] = sinf(theta);
+            theta *= theta_scale;
+        }
+        CU_TRY(cudaMemcpyAsync(m->rope_delta, tab.data(), (size_t)hd * 4, cudaMemcpyHostToDevice, m->stream));
+        CU_TRY(cudaStreamSynchronize(m->stream));  // `tab` is pageable host memory
+        const size_t scratch_floats = (size_t)m->max_chunk * m->cfg.intermediate_size;
+        const unsigned long long before = g_kernel_launches;
+        for (Layer& L : m->layers) {
+            if (!L.is_attn) continue;
+            const int kv_dim = L.n_kv * hd;
+            const int rows_per_pass = (int)std::max<size_t>(1, scratch_floats / kv_dim);
+            // ascending passes: a pass only overwrites rows below the ones later passes still have to read
+            for (int r0 = 0; r0 < retained; r0 += rows_per_pass) {
+                const int rows = std::min(rows_per_pass, retained - r0);
+                const int row0 = (int)n_keep + r0;
+                launch_kv_shift_gather(m->stream, L.k_cache, m->gate, row0, rows, (int)shift, kv_dim, hd, m->rope_delta, m->rope_delta + half);
+                launch_kv_shift_gather(m->stream, L.v_cache, m->up, row0, rows, (int)shift, kv_dim, hd, nullptr, nullptr);
+                CU_TRY(cudaMemcpyAsync(L.k_cache + (size_t)row0 * kv_dim, m->gate, (size_t)rows * kv_dim * 4, cudaMemcpyDeviceToDevice, m->stream));
+                CU_TRY(cudaMemcpyAsync(L.v_cache + (size_t)row0 * kv_dim, m->up, (size_t)rows * kv_dim * 4, cudaMemcpyDeviceToDevice, m->stream));
+            }
+        }
+        m->launches += g_kernel_launches - before;
+        CU_TRY(cudaGetLastError());
+    }
+    m->h_u32[0] = new_len;
+    CU_TRY(cudaMemcpyAsync(&m->ctl->pos, m->h_u32, 4, cudaMemcpyHostToDevice, m->stream));
+    CU_TRY(cudaStreamSynchronize(m->stream));
+    m->seq_len = new_len;
+    return WICK_CUDA_OK;
 }
 
 int32_t wick_cuda_set_prefill_mode(wick_cuda_model* m, int32_t mode) {

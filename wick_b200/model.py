@@ -202,7 +202,14 @@ class CudaLfm2Model:
         return out
 
     def supports_kv_shift(self) -> bool:
-        return False
+        return True
+
+    def shift_kv(self, state: InferenceState, n_keep: int, shift: int) -> None:
+        """Model::shift_kv (mod.rs:158-170): drop KV cells [n_keep, n_keep + shift), re-rotate the moved K rows."""
+        assert shift > 0, "shift must be > 0"
+        with self._lock:
+            check(self._lib.wick_cuda_shift_kv(self._h, int(n_keep), int(shift)))
+        state.seq_len -= shift
 
     def turboquant_supported(self) -> bool:
         return False
