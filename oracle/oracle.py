@@ -22,9 +22,9 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB_PATH = os.path.join(_HERE, "_build", "libwick_oracle.so")
 
-DT_Q4_0, DT_Q8_0 = 2, 8
+DT_Q4_0, DT_Q8_0, DT_Q6_K = 2, 8, 14
 BLOCK_BYTES = {DT_Q4_0: 18, DT_Q8_0: 34}
-QTYPE_ID = {"q4_0": DT_Q4_0, "q8_0": DT_Q8_0}
+QTYPE_ID = {"q4_0": DT_Q4_0, "q8_0": DT_Q8_0, "q6_k": DT_Q6_K}
 
 
 def build(force: bool = False) -> str:
@@ -278,6 +278,8 @@ class GgufFile:
             size = n * 4
         elif tt in BLOCK_BYTES:
             size = n // 32 * BLOCK_BYTES[tt]
+        elif tt == DT_Q6_K:
+            size = n // 256 * 210
         else:
             raise ValueError(f"tensor {name}: unsupported ggml type {tt}")
         return np.frombuffer(self.buf, dtype=np.uint8, count=size, offset=off)
@@ -347,7 +349,7 @@ class OracleModel:
 
         def wref(name) -> _Weight:
             dims, tt, _ = g.tensors[name]
-            if tt not in BLOCK_BYTES:
+            if tt not in BLOCK_BYTES and not (tt == DT_Q6_K and name == "token_embd.weight"):
                 raise ValueError(f"{name}: unsupported dtype {tt}")
             a = g.tensor_bytes(name)
             self._keep.append(a)

@@ -50,6 +50,9 @@ namespace {
 constexpr int QK = 32;
 constexpr int DT_Q4_0 = 2;  // GGML type ids, wick/src/gguf.rs:36-44
 constexpr int DT_Q8_0 = 8;
+constexpr int DT_Q6_K = 14;
+constexpr int QK_K = 256;       // elements of a Q6_K super-block
+constexpr int Q6_K_BYTES = 210;  // ql[128] qh[64] scales[16] d (quant.rs:63-70)
 constexpr int GEMV_PAR_THRESHOLD = 256;  // wick/src/backend/cpu.rs:310
 
 int g_use_simd = 1;
@@ -111,6 +114,10 @@ inline uint16_t f32_to_f16(float f) {
 inline uint16_t load_u16(const uint8_t* p) { uint16_t v; memcpy(&v, p, 2); return v; }
 
 inline int block_bytes(int dtype) { return dtype == DT_Q4_0 ? 18 : 34; }
+// bytes of one row of k elements
+inline size_t row_bytes(int dtype, int k) {
+    return dtype == DT_Q6_K ? (size_t)(k / QK_K) * Q6_K_BYTES : (size_t)(k / QK) * block_bytes(dtype);
+}
 
 template <class F>
 inline void par_for(int n, bool parallel, F f) {
@@ -272,7 +279,52 @@ inline float row_dot(const uint8_t* row, const float* xs, const int8_t* xq, int 
 
 // gemv_q4_0_q8_0_neon / gemv_q8_0_q8_0_neon (simd.rs:328-415, :440-524); rows in
 // parallel once m >= 256 (cpu.rs:310), which does not change any result.
+// gemv_q6k_q8_0_neon (simd.rs:552-672): one serial f32 sum per row over 16-element sub-blocks in the
+// order (super-block, pass, half, {+0, +32, +64, +96}); each term is (d * scale * d_x) * float(int dot),
+// products evaluated left to right, the term's product and the add unfused.
+float row_dot_q6_k(const uint8_t* row, const float* xs, const int8_t* xq, int k) {
+    float sumf = 0.0f;
+    for (int bi = 0; bi < k / QK_K; bi++) {
+        const uint8_t* blk = row + (size_t)bi * Q6_K_BYTES;
+        const uint8_t *ql = blk, *qh = blk + 128;
+        const int8_t* sc = (const int8_t*)(blk + 192);
+        const float d = f16_to_f32(load_u16(blk + 208));
+        const int xq_off = bi * QK_K;
+        int sc_idx = 0, ql_p = 0, qh_p = 0, y_p = 0;
+        for (int pass = 0; pass < 2; pass++) {
+            for (int half = 0; half < 2; half++) {
+                const int l_off = half * 16;
+                for (int j = 0; j < 4; j++) {  // q1..q4
+                    int32_t dot = 0;
+                    for (int l = 0; l < 16; l++) {
+                        const uint8_t lo = ql[ql_p + l_off + l + (j & 1 ? 32 : 0)];
+                        const uint8_t h = qh[qh_p + l_off + l];
+                        const int nib = j < 2 ? (lo & 0x0F) : (lo >> 4);
+                        const int hi2 = (h >> (2 * j)) & 3;
+                        const int q = (nib | (hi2 << 4)) - 32;
+                        dot += q * (int)xq[xq_off + y_p + l_off + 32 * j + l];
+                    }
+                    const int q8_bi = (xq_off + y_p + l_off + 32 * j) / 32;
+                    const float dj = d * (float)sc[sc_idx + 2 * j] * xs[q8_bi];
+                    sumf += dj * (float)dot;
+                }
+                sc_idx += 1;
+            }
+            y_p += 128;
+            ql_p += 64;
+            qh_p += 32;
+            sc_idx = 8;
+        }
+    }
+    return sumf;
+}
+
 void gemv_preq(int dtype, const uint8_t* a, const float* xs, const int8_t* xq, float* y, int m, int k) {
+    if (dtype == DT_Q6_K) {
+        const size_t rb6 = row_bytes(dtype, k);
+        par_for(m, m >= GEMV_PAR_THRESHOLD, [&](int i) { y[i] = row_dot_q6_k(a + i * rb6, xs, xq, k); });
+        return;
+    }
     int nb = k / QK;
     size_t rb = (size_t)nb * block_bytes(dtype);
     par_for(m, m >= GEMV_PAR_THRESHOLD, [&](int i) {
@@ -471,6 +523,27 @@ uint32_t argmax(const float* x, int n) {
 
 // quant.rs:78-105, :154-177 (dequantize rows; the embedding lookup lfm2.rs:621-643)
 void dequant_row(int dtype, const uint8_t* row, int k, float* out) {
+    if (dtype == DT_Q6_K) {  // dequantize_q6_k_block, quant.rs:380-413: d * scale * q, left to right
+        for (int bi = 0; bi < k / QK_K; bi++) {
+            const uint8_t* blk = row + (size_t)bi * Q6_K_BYTES;
+            const uint8_t *ql = blk, *qh = blk + 128;
+            const int8_t* sc = (const int8_t*)(blk + 192);
+            const float d = f16_to_f32(load_u16(blk + 208));
+            float* o = out + (size_t)bi * QK_K;
+            for (int n = 0; n < 2; n++)
+                for (int l = 0; l < 32; l++) {
+                    const int is = l / 16;
+                    const uint8_t a = ql[64 * n + l], b = ql[64 * n + l + 32], h = qh[32 * n + l];
+                    const int q1 = ((a & 0xF) | ((h & 3) << 4)) - 32, q2 = ((b & 0xF) | (((h >> 2) & 3) << 4)) - 32;
+                    const int q3 = ((a >> 4) | (((h >> 4) & 3) << 4)) - 32, q4 = ((b >> 4) | (((h >> 6) & 3) << 4)) - 32;
+                    o[128 * n + l] = d * (float)sc[8 * n + is] * (float)q1;
+                    o[128 * n + l + 32] = d * (float)sc[8 * n + is + 2] * (float)q2;
+                    o[128 * n + l + 64] = d * (float)sc[8 * n + is + 4] * (float)q3;
+                    o[128 * n + l + 96] = d * (float)sc[8 * n + is + 6] * (float)q4;
+                }
+        }
+        return;
+    }
     int nb = k / QK;
     for (int b = 0; b < nb; b++) {
         const uint8_t* blk = row + (size_t)b * block_bytes(dtype);
@@ -618,7 +691,7 @@ void forward_token(OrcModel& M, uint32_t token, float* logits, float* hidden_out
     int hs = M.d.hidden, is = M.d.ffn;
     std::vector<float> hidden(hs), normed(hs), out(hs), gate(is), up(is);
     if (emb) memcpy(hidden.data(), emb, hs * sizeof(float));
-    else dequant_row(M.d.embd.dtype, M.d.embd.data + (size_t)token * (hs / QK) * block_bytes(M.d.embd.dtype), hs, hidden.data());
+    else dequant_row(M.d.embd.dtype, M.d.embd.data + (size_t)token * row_bytes(M.d.embd.dtype, hs), hs, hidden.data());
     int pos = M.seq_len;
     for (int i = 0; i < M.d.n_layers; i++) {
         const OrcLayer& L = M.layers[i];
@@ -667,12 +740,12 @@ void forward_prefill(OrcModel& M, const uint32_t* tokens, int n, int start_pos, 
     std::vector<float> hidden((size_t)n * hs), normed((size_t)n * hs), block_out((size_t)n * hs);
     std::vector<float> bs;
     std::vector<int8_t> bq;
-    int eb = block_bytes(M.d.embd.dtype);
+    const size_t erb = row_bytes(M.d.embd.dtype, hs);
     // forward_prefill_inner, lfm2.rs:2238-2251
     if (emb) memcpy(hidden.data(), emb, (size_t)n * hs * sizeof(float));
     else
         for (int j = 0; j < n; j++)
-            dequant_row(M.d.embd.dtype, M.d.embd.data + (size_t)tokens[j] * (hs / QK) * eb, hs, hidden.data() + (size_t)j * hs);
+            dequant_row(M.d.embd.dtype, M.d.embd.data + (size_t)tokens[j] * erb, hs, hidden.data() + (size_t)j * hs);
 
     for (int li = 0; li < M.d.n_layers; li++) {
         const OrcLayer& L = M.layers[li];

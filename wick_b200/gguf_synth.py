@@ -154,7 +154,62 @@ def dequantize(raw: np.ndarray, qtype: str, k: int) -> np.ndarray:
     return v.reshape(*raw.shape[:-1], k)
 
 
-QUANTIZERS = {"q4_0": (quantize_q4_0, GGML_Q4_0), "q8_0": (quantize_q8_0, GGML_Q8_0)}
+GGML_Q6_K = 14
+QK_K = 256          # elements of a Q6_K super-block
+Q6_K_BYTES = 210    # ql[128] + qh[64] + scales[16] (i8) + d (f16), wick/src/quant.rs:63-70
+
+
+def quantize_q6_k(x: np.ndarray) -> np.ndarray:
+    """f32 [..., k] -> uint8 [..., k/256*210] of Q6_K super-blocks.  The FORMAT is ggml's (decoded by
+    quant.rs:380-413); the choice of scales is a plain max-abs fit per 16-element sub-block, not ggml's
+    iterative search (any valid encoding exercises the same decode and dot-product code)."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    k = x.shape[-1]
+    assert k % QK_K == 0
+    sb = x.reshape(-1, 16, 16)                                    # [super-block][sub-block][16]
+    sub_scale = np.abs(sb).max(axis=2) / np.float32(31.0)         # element ~= q * sub_scale, q in [-32, 31]
+    d = (sub_scale.max(axis=1) / np.float32(127.0)).astype(np.float16).astype(np.float32)
+    with np.errstate(divide="ignore", invalid="ignore"):
+        sc = np.where(d[:, None] > 0, np.rint(sub_scale / d[:, None]), 0).astype(np.int32)
+    sc = np.clip(sc, 0, 127).astype(np.int8)
+    eff = d[:, None] * sc.astype(np.float32)                      # what the decoder multiplies by
+    with np.errstate(divide="ignore", invalid="ignore"):
+        q = np.where(eff[:, :, None] > 0, np.rint(sb / eff[:, :, None]), 0)
+    q = (np.clip(q, -32, 31).astype(np.int32) + 32).astype(np.uint8).reshape(-1, 256)   # 0..63
+    out = np.zeros((q.shape[0], Q6_K_BYTES), dtype=np.uint8)
+    ql, qh = out[:, :128], out[:, 128:192]
+    for n in range(2):                                            # two passes of 128 values (quant.rs:393-410)
+        base = q[:, 128 * n:128 * (n + 1)]
+        q1, q2, q3, q4 = base[:, 0:32], base[:, 32:64], base[:, 64:96], base[:, 96:128]
+        ql[:, 64 * n:64 * n + 32] = (q1 & 0xF) | ((q3 & 0xF) << 4)
+        ql[:, 64 * n + 32:64 * n + 64] = (q2 & 0xF) | ((q4 & 0xF) << 4)
+        qh[:, 32 * n:32 * n + 32] = (q1 >> 4) | ((q2 >> 4) << 2) | ((q3 >> 4) << 4) | ((q4 >> 4) << 6)
+    out[:, 192:208] = sc.view(np.uint8)
+    out[:, 208:210] = d.astype(np.float16).view(np.uint8).reshape(-1, 2)
+    return out.reshape(*x.shape[:-1], k // QK_K * Q6_K_BYTES)
+
+
+def dequantize_q6_k(raw: np.ndarray, k: int) -> np.ndarray:
+    """dequantize_q6_k_block (quant.rs:380-413) in numpy: d * scale * q, evaluated left to right in f32."""
+    b = np.ascontiguousarray(raw, dtype=np.uint8).reshape(-1, Q6_K_BYTES)
+    ql, qh = b[:, :128].astype(np.int32), b[:, 128:192].astype(np.int32)
+    sc = b[:, 192:208].copy().view(np.int8).astype(np.float32)
+    d = b[:, 208:210].copy().view(np.float16).astype(np.float32).reshape(-1)
+    out = np.empty((b.shape[0], 256), dtype=np.float32)
+    for n in range(2):
+        l, h = ql[:, 64 * n:64 * n + 64], qh[:, 32 * n:32 * n + 32]
+        q1 = ((l[:, :32] & 0xF) | ((h & 3) << 4)) - 32
+        q2 = ((l[:, 32:] & 0xF) | (((h >> 2) & 3) << 4)) - 32
+        q3 = ((l[:, :32] >> 4) | (((h >> 4) & 3) << 4)) - 32
+        q4 = ((l[:, 32:] >> 4) | (((h >> 6) & 3) << 4)) - 32
+        for j, qq in enumerate((q1, q2, q3, q4)):
+            scale = np.repeat(sc[:, 8 * n + 2 * j:8 * n + 2 * j + 2], 16, axis=1)      # is = l / 16
+            out[:, 128 * n + 32 * j:128 * n + 32 * j + 32] = (d[:, None] * scale) * qq.astype(np.float32)
+    return out.reshape(*raw.shape[:-1], k)
+
+
+QUANTIZERS = {"q4_0": (quantize_q4_0, GGML_Q4_0), "q8_0": (quantize_q8_0, GGML_Q8_0), "q6_k": (quantize_q6_k, GGML_Q6_K)}
+BLOCK_GEOMETRY = {"q4_0": (QK, 18), "q8_0": (QK, 34), "q6_k": (QK_K, Q6_K_BYTES)}  # elements, bytes per block
 
 
 # ── GGUF v3 writer ──────────────────────────────────────────────────────────
@@ -268,18 +323,21 @@ def _tensor_list(spec: Lfm2Spec) -> List[Tuple[str, Tuple[int, ...], str]]:
 
 
 def write_lfm2_gguf(path: str, spec: Lfm2Spec, qtype: str, seed: int = 0,
-                    weight_std: float = 0.02, norm_jitter: float = 0.0) -> str:
+                    weight_std: float = 0.02, norm_jitter: float = 0.0, embd_qtype: Optional[str] = None) -> str:
     """Write a random-init model.  Matmul weights and `token_embd` ~ N(0, weight_std)
     in f32 then quantised per 32-element block; norm weights 1.0 (plus an optional
     uniform jitter used by tests so that a dropped norm weight is noticed); conv
-    weights N(0, weight_std) kept in f32."""
-    quant_fn, gtype = QUANTIZERS[qtype]
-    bb = {"q4_0": 18, "q8_0": 34}[qtype]
+    weights N(0, weight_std) kept in f32.  `embd_qtype` ("q6_k": what llama.cpp's Q4_0 files carry)
+    overrides the type of `token_embd` only."""
+    def qt(name):
+        return embd_qtype if (embd_qtype and name == "token_embd.weight") else qtype
+
     tensors = _tensor_list(spec)
     plan = []
     for name, shape, kind in tensors:
         if kind == "quant":
-            plan.append((name, shape, gtype, shape[0] * (shape[1] // QK) * bb))
+            be, bb = BLOCK_GEOMETRY[qt(name)]
+            plan.append((name, shape, QUANTIZERS[qt(name)][1], shape[0] * (shape[1] // be) * bb))
         else:
             plan.append((name, shape, GGML_F32, int(np.prod(shape)) * 4))
     kv_heads = [spec.n_kv_heads if i in spec.attn_layers else 0 for i in range(spec.n_layers)]
@@ -306,7 +364,9 @@ def write_lfm2_gguf(path: str, spec: Lfm2Spec, qtype: str, seed: int = 0,
     for name, shape, kind in tensors:
         if kind == "quant":
             rows, k = shape
-            out = np.empty((rows, k // QK * bb), dtype=np.uint8)
+            be, bb = BLOCK_GEOMETRY[qt(name)]
+            quant_fn = QUANTIZERS[qt(name)][0]
+            out = np.empty((rows, k // be * bb), dtype=np.uint8)
             step = max(1, (1 << 24) // k)  # ~64 MB of f32 per chunk
             for r0 in range(0, rows, step):
                 r1 = min(rows, r0 + step)
