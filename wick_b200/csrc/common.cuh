@@ -41,6 +41,21 @@ struct DevWeight {
     size_t d_bytes() const { return (size_t)groups() * d_group_bytes(); }
 };
 
+// token_embd stored as Q6_K (ggml type 14; BlockQ6K, wick/src/quant.rs:63-70: 256 elements in ql[128] low
+// nibbles, qh[64] high bit pairs, 16 int8 sub-block scales, f16 d).  The 210-byte blocks are only 2-byte
+// aligned, so the four fields are split into planes at load; every row of every plane then starts on a
+// 16-byte boundary (k is a multiple of 256).
+constexpr int DT_Q6_K = 14;
+constexpr int QK_K = 256;
+struct DevQ6K {
+    const uint8_t* ql = nullptr;  // [m][k/2]
+    const uint8_t* qh = nullptr;  // [m][k/4]
+    const int8_t* sc = nullptr;   // [m][k/16]
+    const __half* d = nullptr;    // [m][k/256]
+    int m = 0, k = 0;
+    size_t bytes() const { return (size_t)m * (k / 2 + k / 4 + k / 16 + k / 256 * 2); }
+};
+
 // Word offsets inside a group (see DevWeight).
 __host__ __device__ __forceinline__ int q4_word(int b, int r, int l) { return b * 16 + r * 4 + l; }
 __host__ __device__ __forceinline__ int q8_word(int b, int half, int r, int l) {

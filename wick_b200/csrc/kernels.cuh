@@ -67,6 +67,14 @@ void configure_naive_attention_smem(size_t bytes);
 void launch_attention_flash(cudaStream_t st, const float* q, const float* k_cache, const float* v_cache, float* out,
                             int n, int start_pos, int n_heads, int n_kv_heads, int head_dim);
 
+// Q6_K vocabulary matrix (kernels_q6k.cu): re-layout of raw GGUF blocks into the planes of `w` (already
+// pointing at device memory), embedding rows, and the logits mat-vec y[m] (simd.rs:552-672).  The mat-vec
+// uses gemv_q6k_smem(k) bytes of dynamic shared memory (k <= 6144 stays under the 48 KB default).
+void launch_repack_q6k(cudaStream_t st, const uint8_t* raw, const DevQ6K& w);
+void launch_embed_q6k(cudaStream_t st, const DevQ6K& w, const uint32_t* tokens, const DecodeCtl* ctl, float* out, int n);
+size_t gemv_q6k_smem(int k);
+void launch_gemv_q6k(cudaStream_t st, const DevQ6K& w, const float* xs, const int8_t* xq, float* y);
+
 // n_keep context shift (kv_cache.rs:601-715): gathers cache rows [row0 + shift, row0 + shift + rows) into a
 // dense scratch, K rows rotated by the delta table (cos_delta / sin_delta of hd/2 entries), V rows as they are (NULL tables).
 void launch_kv_shift_gather(cudaStream_t st, const float* cache, float* scratch, int row0, int rows, int shift, int kv_dim, int hd,

@@ -70,6 +70,8 @@ struct wick_cuda_model {
     int head_dim = 0;
     std::vector<Layer> layers;
     DevWeight embd;
+    bool embd_q6k = false;  // token_embd is Q6_K: embd6 is used for the embedding rows and the logits, embd is empty
+    DevQ6K embd6;
     float* output_norm = nullptr;
     float *rope_cos = nullptr, *rope_sin = nullptr;
     int max_chunk = 0;  // tokens of scratch
@@ -203,6 +205,37 @@ int32_t upload_weight(wick_cuda_model* m, const GgufImage& g, const std::string&
     return WICK_CUDA_OK;
 }
 
+// token_embd in Q6_K: raw super-blocks to the device, then split into the planes of DevQ6K.
+int32_t upload_q6k(wick_cuda_model* m, const GgufImage& g, const std::string& name, int expect_m, int expect_k, uint8_t* staging,
+                   DevQ6K* out) {
+    const GgufTensor* t = g.tensor(name);
+    if (!t) return fail(WICK_CUDA_ERR_BAD_GGUF, "tensor not found: " + name);
+    int k = t->dims.size() > 0 ? (int)t->dims[0] : 1;
+    int rows = t->dims.size() > 1 ? (int)t->dims[1] : 1;
+    if (rows != expect_m || k != expect_k || k % QK_K)
+        return fail(WICK_CUDA_ERR_BAD_GGUF, "tensor " + name + ": Q6_K shape [" + std::to_string(k) + "," + std::to_string(rows) +
+                                                "] does not match the model config (row length must be a multiple of 256)");
+    if (gemv_q6k_smem(k) > 48 * 1024) return fail(WICK_CUDA_ERR_UNSUPPORTED_DTYPE, "Q6_K rows longer than 6144 elements are not supported");
+    DevQ6K w;
+    w.m = rows;
+    w.k = k;
+    uint8_t *ql = nullptr, *qh = nullptr;
+    int8_t* sc = nullptr;
+    __half* d = nullptr;
+    W_TRY(dev_alloc(m, &ql, (size_t)rows * (k / 2)));
+    W_TRY(dev_alloc(m, &qh, (size_t)rows * (k / 4)));
+    W_TRY(dev_alloc(m, &sc, (size_t)rows * (k / 16)));
+    W_TRY(dev_alloc(m, &d, (size_t)rows * (k / QK_K)));
+    w.ql = ql; w.qh = qh; w.sc = sc; w.d = d;
+    const size_t raw_bytes = (size_t)rows * (k / QK_K) * 210;
+    CU_TRY(cudaMemcpyAsync(staging, g.data() + t->offset, raw_bytes, cudaMemcpyHostToDevice, m->stream));
+    launch_repack_q6k(m->stream, staging, w);
+    CU_TRY(cudaGetLastError());
+    CU_TRY(cudaStreamSynchronize(m->stream));
+    *out = w;
+    return WICK_CUDA_OK;
+}
+
 // cos / sin of every (position, pair) evaluated with the host libm in the reference's order
 // (cpu.rs:2145-2158): theta starts at pos as f32 and is multiplied by powf(base, -2/hd).
 void fill_rope_table(int n_pos, int hd, float base, std::vector<float>& c, std::vector<float>& s) {
@@ -227,6 +260,7 @@ int32_t build_mega(wick_cuda_model* m) {
     int coop = 0;
     CU_TRY(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, m->device));
     if (!coop) return WICK_CUDA_OK;
+    if (m->embd_q6k) return WICK_CUDA_OK;  // the persistent kernel streams Q4_0 / Q8_0 planes only: decode runs as the captured graph
     const wick_cuda_config& c = m->cfg;
     const int hs = c.hidden_size, is = c.intermediate_size;
     std::vector<MegaPhase> ph;
@@ -367,10 +401,27 @@ size_t naive_attn_smem(const wick_cuda_model* m) { return (size_t)(m->head_dim +
 
 // One decode step on the stream; token and position come from m->ctl (run_layers,
 // lfm2.rs:1020-1124, then the tied-embedding logits GEMV, lfm2.rs:2268-2288).
+// Embedding rows into m->hidden and the tied-embedding logits from the quantised normed row in m->q8*
+// (lfm2.rs:621-643, :2268-2288), for either storage type of token_embd.
+void embed_rows(wick_cuda_model* m, const uint32_t* tokens_dev, const DecodeCtl* ctl, int n) {
+    if (m->embd_q6k) launch_embed_q6k(m->stream, m->embd6, tokens_dev, ctl, m->hidden, n);
+    else launch_embed(m->stream, m->embd, tokens_dev, ctl, m->hidden, n);
+}
+
+void logits_matvec(wick_cuda_model* m) {
+    if (m->embd_q6k) {
+        launch_gemv_q6k(m->stream, m->embd6, m->q8s, m->q8q, m->logits);
+    } else {
+        GemvJob lg{};
+        lg.count = 1; lg.w[0] = m->embd; lg.y[0] = m->logits;
+        launch_gemv(m->stream, lg, m->q8s, m->q8q);
+    }
+}
+
 void enqueue_decode(wick_cuda_model* m, bool greedy) {
     cudaStream_t st = m->stream;
     const int hs = m->cfg.hidden_size, is = m->cfg.intermediate_size, hd = m->head_dim;
-    launch_embed(st, m->embd, nullptr, m->ctl, m->hidden, 1);
+    embed_rows(m, nullptr, m->ctl, 1);
     const float* pending = nullptr;  // block output not yet added to the residual stream
     for (size_t li = 0; li < m->layers.size(); li++) {
         Layer& L = m->layers[li];
@@ -412,9 +463,7 @@ void enqueue_decode(wick_cuda_model* m, bool greedy) {
         pending = m->ffn_out;
     }
     launch_add_rmsnorm_quant(st, m->hidden, pending, m->output_norm, m->cfg.rms_norm_eps, 1, hs, m->q8s, m->q8q, nullptr);
-    GemvJob lg{};
-    lg.count = 1; lg.w[0] = m->embd; lg.y[0] = m->logits;
-    launch_gemv(st, lg, m->q8s, m->q8q);
+    logits_matvec(m);
     if (greedy) {
         launch_argmax(st, m->logits, m->cfg.vocab_size, &m->ctl->argmax, m->argmax_tok);
         launch_decode_advance(st, m->ctl, m->argmax_tok, m->ring, m->ring_len);
@@ -478,7 +527,7 @@ void enqueue_prefill_chunk(wick_cuda_model* m, int n, int start_pos, bool flash,
             for (const G& g : list) launch_gemm(st, *g.w, m->q8s, m->q8q, n, g.out);
         }
     };
-    if (embed) launch_embed(st, m->embd, m->tokens_dev, nullptr, m->hidden, n);
+    if (embed) embed_rows(m, m->tokens_dev, nullptr, n);
     const float* pending = nullptr;
     for (size_t li = 0; li < m->layers.size(); li++) {
         Layer& L = m->layers[li];
@@ -509,11 +558,7 @@ void enqueue_prefill_chunk(wick_cuda_model* m, int n, int start_pos, bool flash,
         // last token only (lfm2.rs:2190-2212)
         size_t lastrow = (size_t)(n - 1) * hs;
         launch_add_rmsnorm_quant(st, m->hidden + lastrow, pending + lastrow, m->output_norm, eps, 1, hs, m->q8s, m->q8q, m->normed_last);
-        if (want_logits) {
-            GemvJob lg{};
-            lg.count = 1; lg.w[0] = m->embd; lg.y[0] = m->logits;
-            launch_gemv(st, lg, m->q8s, m->q8q);
-        }
+        if (want_logits) logits_matvec(m);
     }
 }
 
@@ -644,7 +689,12 @@ int32_t build_model(wick_cuda_model* m, const GgufImage& g, uint32_t context_siz
         ~StagingGuard() { cudaFree(p); }
     } guard{staging};
 
-    W_TRY(upload_weight(m, g, "token_embd.weight", c.vocab_size, hs, staging, &m->embd));
+    {
+        const GgufTensor* te = g.tensor("token_embd.weight");
+        if (te && te->type == DT_Q6_K) W_TRY(upload_q6k(m, g, "token_embd.weight", c.vocab_size, hs, staging, &m->embd6));
+        else W_TRY(upload_weight(m, g, "token_embd.weight", c.vocab_size, hs, staging, &m->embd));
+        m->embd_q6k = te && te->type == DT_Q6_K;
+    }
     W_TRY(upload_f32(m, g, "token_embd_norm.weight", hs, &m->output_norm));  // the OUTPUT norm, lfm2.rs:188
     const int dc = (int)c.conv_kernel_size - 1;
     for (uint32_t i = 0; i < c.n_layers; i++) {
