@@ -24,7 +24,7 @@ def test_q6k_embedding_model_bit_exact(wick, orc, model_dir, spec, qtype):
     from wick_b200 import gguf_synth as gs
     path = gs.cached_model(spec, qtype, 0, cache_dir=model_dir, embd_qtype="q6_k")
     cm, om = wick.CudaLfm2Model(path, 512), orc.OracleModel(path, 512)
-    assert cm.decode_path() == "graph"             # the persistent kernel does not stream Q6_K planes
+    assert cm.decode_path() == "persistent"        # layers in the persistent kernel, Q6_K logits as a kernel of its own
     st = wick.InferenceState()
     vocab = cm.config().vocab_size
     # single steps: embedding row lookup + logits mat-vec every step

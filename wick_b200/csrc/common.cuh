@@ -56,6 +56,19 @@ struct DevQ6K {
     size_t bytes() const { return (size_t)m * (k / 2 + k / 4 + k / 16 + k / 256 * 2); }
 };
 
+// Element e of a row: quant.rs:393-410.  Within a super-block, pass n = (e % 256) / 128, r = e % 128,
+// j = r / 32 selects (ql half, nibble, qh bit pair), l = r % 32; scale index 8n + l/16 + 2j.
+__device__ __forceinline__ float q6k_elem(const DevQ6K& w, size_t row, int e) {
+    const int k = w.k, bi = e >> 8, n = (e >> 7) & 1, r = e & 127, j = r >> 5, l = r & 31;
+    const uint8_t* ql = w.ql + row * (size_t)(k / 2) + (size_t)bi * 128 + 64 * n + l + ((j & 1) ? 32 : 0);
+    const uint8_t h = w.qh[row * (size_t)(k / 4) + (size_t)bi * 64 + 32 * n + l];
+    const int nib = j < 2 ? (*ql & 0x0F) : (*ql >> 4);
+    const int q = (nib | (((h >> (2 * j)) & 3) << 4)) - 32;
+    const float d = __half2float(w.d[row * (size_t)(k / QK_K) + bi]);
+    const float s = (float)w.sc[row * (size_t)(k / 16) + (size_t)bi * 16 + 8 * n + (l >> 4) + 2 * j];
+    return __fmul_rn(__fmul_rn(d, s), (float)q);
+}
+
 // Word offsets inside a group (see DevWeight).
 __host__ __device__ __forceinline__ int q4_word(int b, int r, int l) { return b * 16 + r * 4 + l; }
 __host__ __device__ __forceinline__ int q8_word(int b, int half, int r, int l) {

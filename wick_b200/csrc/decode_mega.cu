@@ -357,7 +357,7 @@ __device__ void prologue_norm(Ctx& c, const MegaPhase& ph, uint32_t token, const
         v[j] = 0.0f;
         if (b < nb) {
             if (ph.embed) {
-                v[j] = embed_elem(P.embd, token, e);
+                v[j] = P.embd_q6k ? q6k_elem(P.embd6, token, e) : embed_elem(P.embd, token, e);
                 if (e >= e0 && e < e1) P.hidden[e] = v[j];
             } else {
                 v[j] = __ldcg(P.hidden + e);
@@ -906,7 +906,7 @@ __device__ void consumer(const MegaParams& P, const Smem& S, int cta, int ncta) 
                     off += gm;
                 }
             }
-            if (pi == P.n_phases - 1 && P.greedy) {
+            if (pi == P.n_phases - 1 && P.greedy && !P.skip_logits) {
                 // cpu_argmax (sampler.rs:8-19): CTA-level max, then one atomic per CTA
 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) {
@@ -927,7 +927,7 @@ __device__ void consumer(const MegaParams& P, const Smem& S, int cta, int ncta) 
         }
     }
     // last step's result and the control block
-    if (cta == 0) {
+    if (cta == 0 && !P.skip_logits) {
         const int n = P.n_tokens;
         grid_wait(c, (P.bar_base + (unsigned long long)n * P.n_phases) * (unsigned long long)ncta);
         if (c.ct == 0 && !*S.abort) {

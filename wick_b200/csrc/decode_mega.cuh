@@ -67,6 +67,10 @@ struct MegaParams {
     int hs, is, n_heads, head_dim, vocab, conv_ks, max_seq;
     float eps;
     DevWeight embd;
+    // token_embd stored as Q6_K: phase 0 reads its rows from embd6, and the step ends after the last layer
+    // (skip_logits): output norm, logits, argmax and the control-block update run as separate kernels
+    int embd_q6k, skip_logits;
+    DevQ6K embd6;
     float *hidden, *proj, *qbuf, *kbuf, *vbuf, *attn_out, *gate, *up, *logits;
     const float *rope_cos, *rope_sin;
     DecodeCtl* ctl;

@@ -260,7 +260,6 @@ int32_t build_mega(wick_cuda_model* m) {
     int coop = 0;
     CU_TRY(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, m->device));
     if (!coop) return WICK_CUDA_OK;
-    if (m->embd_q6k) return WICK_CUDA_OK;  // the persistent kernel streams Q4_0 / Q8_0 planes only: decode runs as the captured graph
     const wick_cuda_config& c = m->cfg;
     const int hs = c.hidden_size, is = c.intermediate_size;
     std::vector<MegaPhase> ph;
@@ -321,10 +320,12 @@ int32_t build_mega(wick_cuda_model* m) {
         d.mat[0] = mat(L.down, m->hidden, MEP_ADD);
         ph.push_back(d);
     }
-    MegaPhase v{};
-    v.kind = MPH_NORM; v.k = hs; v.layer = -1; v.conv_commit = -1; v.norm_w = m->output_norm; v.n_mat = 1;
-    v.mat[0] = mat(m->embd, m->logits, MEP_LOGITS);
-    ph.push_back(v);
+    if (!m->embd_q6k) {
+        MegaPhase v{};
+        v.kind = MPH_NORM; v.k = hs; v.layer = -1; v.conv_commit = -1; v.norm_w = m->output_norm; v.n_mat = 1;
+        v.mat[0] = mat(m->embd, m->logits, MEP_LOGITS);
+        ph.push_back(v);
+    }  // a Q6_K vocabulary matrix is not streamed by the persistent kernel: see run_mega
     if (!ok || c.conv_kernel_size < 2 || c.conv_kernel_size > 4 || m->head_dim > 256 || m->head_dim % 16 || std::max(hs, is) > MEGA_CONSUMER_WARPS * 16 * 32) return WICK_CUDA_OK;
 
     MegaParams& P = m->mega;
@@ -333,6 +334,9 @@ int32_t build_mega(wick_cuda_model* m) {
     P.hs = hs; P.is = is; P.n_heads = c.n_heads; P.head_dim = m->head_dim; P.vocab = c.vocab_size;
     P.conv_ks = c.conv_kernel_size; P.max_seq = c.max_seq_len; P.eps = c.rms_norm_eps;
     P.embd = m->embd;
+    P.embd_q6k = m->embd_q6k ? 1 : 0;
+    P.skip_logits = m->embd_q6k ? 1 : 0;
+    P.embd6 = m->embd6;
     P.hidden = m->hidden; P.proj = m->proj; P.qbuf = m->qbuf; P.kbuf = m->kbuf; P.vbuf = m->vbuf;
     P.attn_out = m->attn_out; P.gate = m->gate; P.up = m->up; P.logits = m->logits;
     P.rope_cos = m->rope_cos; P.rope_sin = m->rope_sin;
@@ -371,14 +375,40 @@ int32_t build_mega(wick_cuda_model* m) {
 }
 
 // Runs n decode steps with the persistent kernel; ctl holds token / pos / step on entry.
+void logits_matvec(wick_cuda_model* m);
+
 int32_t run_mega(wick_cuda_model* m, int n_tokens, bool greedy) {
     MegaParams P = m->mega;
-    P.n_tokens = n_tokens;
     P.greedy = greedy ? 1 : 0;
-    P.bar_base = m->bar_base;
-    CU_TRY(launch_decode_mega(m->stream, P, m->mega_ctas));
-    m->launches += 1;
-    m->bar_base += (unsigned long long)n_tokens * P.n_phases;
+    if (!P.skip_logits) {
+        P.n_tokens = n_tokens;
+        P.bar_base = m->bar_base;
+        CU_TRY(launch_decode_mega(m->stream, P, m->mega_ctas));
+        m->launches += 1;
+        m->bar_base += (unsigned long long)n_tokens * P.n_phases;
+    } else {
+        // Q6_K vocabulary matrix: the persistent kernel runs the layers of ONE step; the output norm, the
+        // Q6_K logits mat-vec, the argmax and the control-block update follow as kernels on the same stream
+        // (token and position stay on the device, so the host does not wait between steps)
+        const unsigned long long before = g_kernel_launches;
+        P.n_tokens = 1;
+        for (int t = 0; t < n_tokens; t++) {
+            P.bar_base = m->bar_base;
+            CU_TRY(launch_decode_mega(m->stream, P, m->mega_ctas));
+            m->bar_base += (unsigned long long)P.n_phases;
+            launch_add_rmsnorm_quant(m->stream, m->hidden, nullptr, m->output_norm, m->cfg.rms_norm_eps, 1, m->cfg.hidden_size, m->q8s,
+                                     m->q8q, nullptr);
+            logits_matvec(m);
+            if (greedy) {
+                launch_argmax(m->stream, m->logits, m->cfg.vocab_size, &m->ctl->argmax, m->argmax_tok);
+                launch_decode_advance(m->stream, m->ctl, m->argmax_tok, m->ring, m->ring_len);
+            } else {
+                launch_decode_advance(m->stream, m->ctl, &m->ctl->token, nullptr, 0);  // keeps the token, pos += 1
+            }
+        }
+        m->launches += g_kernel_launches - before;
+        CU_TRY(cudaGetLastError());
+    }
     CU_TRY(cudaMemcpyAsync(m->h_ctl, m->ctl, sizeof(DecodeCtl), cudaMemcpyDeviceToHost, m->stream));
     return WICK_CUDA_OK;
 }
