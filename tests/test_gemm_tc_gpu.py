@@ -82,7 +82,7 @@ def test_gemm_tc_matmul_sweep(ops, orc, dtype, n):
 @pytest.mark.parametrize("dtype", ["q4_0", "q8_0"])
 @pytest.mark.parametrize("m,k,n", [
     (128, 128, 16), (128, 512, 64), (256, 1152, 17), (384, 2048, 128), (200, 256, 37), (130, 384, 129), (64, 128, 1),
-    (6912, 2048, 8), (6912, 2048, 128), (2048, 6912, 130),
+    (6912, 2048, 8), (6912, 2048, 128), (6912, 2048, 2002), (2048, 6912, 130),
 ])
 def test_gemm_tc_exact_is_bit_exact(ops, orc, dtype, m, k, n):
     """The default prefill GEMM: tensor-core lane partials + the reference's eight chains.  Bit-equal to
