@@ -39,7 +39,11 @@ namespace {
 constexpr int TC_BM = 128;          // weight rows per tile == TMEM lanes
 constexpr int TC_KSTAGE = 128;      // int8 elements (bytes) per row per stage == one 128B swizzle atom
 constexpr int TC_KB_PER_STAGE = TC_KSTAGE / QK;  // 4 quantisation blocks per stage
-constexpr int TC_STAGES = 4;
+// Shared-memory stages: as many as fit (27.6 KB each for 64-column tiles, 36.9 KB for 128).  A stage is
+// only refilled after the epilogue has finished with its scales, and the refill has to be back from L2 before
+// the MMA issuer needs it; with four stages that left about one microsecond, less than a loaded L2 round trip.
+template <int BN>
+__host__ __device__ constexpr int tc_stages() { return BN == 64 ? 8 : 6; }
 constexpr int TC_COL_GROUPS = 4;    // epilogue warps per TMEM lane quarter; each takes BN/4 columns
 constexpr int TC_EPI_WARPS = 4 * TC_COL_GROUPS;
 constexpr int TC_THREADS = 32 * (4 + TC_EPI_WARPS);
@@ -55,9 +59,9 @@ struct alignas(1024) TcStage {
 
 template <int BN>
 struct TcSmem {
-    TcStage<BN> stage[TC_STAGES];
-    unsigned long long full[TC_STAGES];       // TMA bytes landed + scales written
-    unsigned long long empty[TC_STAGES];      // MMAs of the stage retired + epilogue done with its scales
+    TcStage<BN> stage[tc_stages<BN>()];
+    unsigned long long full[tc_stages<BN>()];   // TMA bytes landed + scales written
+    unsigned long long empty[tc_stages<BN>()];  // MMAs of the stage retired + epilogue done with its scales
     unsigned long long tmem_full[512 / BN];   // block sums of one k-block are in the buffer
     unsigned long long tmem_empty[512 / BN];  // all epilogue warps have read the buffer
     uint32_t tmem_base;
@@ -88,10 +92,13 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 }
 
 // Bounded wait.  Returns false once the limit is hit or another role has already given up.
-template <int BN>
+// SLEEP_NS > 0 is for the producer, MMA and scale-loader roles: they run stages ahead of the epilogue, and a
+// tight poll loop in those warps would take issue slots from the epilogue warps that bound the kernel.
+template <int BN, unsigned SLEEP_NS = 0>
 __device__ __forceinline__ bool mbar_wait(TcSmem<BN>* sm, uint32_t bar, uint32_t parity, uint32_t* err, uint32_t code) {
     for (uint32_t i = 0; i < TC_SPIN_LIMIT; i++) {
         if (mbar_try_wait(bar, parity)) return true;
+        if (SLEEP_NS) __nanosleep(SLEEP_NS);
         if ((i & 1023u) == 1023u && sm->abort) return false;
     }
     sm->abort = 1;
@@ -208,6 +215,7 @@ k_gemm_tc(const __grid_constant__ TcJob job, const __grid_constant__ CUtensorMap
     extern __shared__ uint8_t tc_smem_raw[];
     TcSmem<BN>* sm = reinterpret_cast<TcSmem<BN>*>((reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
     constexpr int NBUF = 512 / BN;
+    constexpr int TC_STAGES = tc_stages<BN>();
     constexpr int COLS = BN / TC_COL_GROUPS;  // columns per epilogue thread
     // EXACT: a column is (token, NEON lane group); the activation rows arrive masked to one lane group
     // each (tc_mask_expand), so a tile covers BN/4 tokens and the MMA yields the four lane partials
@@ -254,7 +262,7 @@ k_gemm_tc(const __grid_constant__ TcJob job, const __grid_constant__ CUtensorMap
                 for (int ks = 0; ks < k_stages; ks++, g++) {
                     const int s = g % TC_STAGES;
                     const uint32_t u = g / TC_STAGES;
-                    ok = mbar_wait(sm, smem_u32(&sm->empty[s]), (u & 1) ^ 1, err, 1);
+                    ok = mbar_wait<BN, 256>(sm, smem_u32(&sm->empty[s]), (u & 1) ^ 1, err, 1);
                     if (!ok) break;
                     const uint32_t bar = smem_u32(&sm->full[s]);
                     mbar_arrive_expect_tx(bar, (TC_BM + BN) * TC_KSTAGE);
@@ -273,7 +281,7 @@ k_gemm_tc(const __grid_constant__ TcJob job, const __grid_constant__ CUtensorMap
                 for (int ks = 0; ks < k_stages && ok; ks++, g++) {
                     const int s = g % TC_STAGES;
                     const uint32_t u = g / TC_STAGES;
-                    ok = mbar_wait(sm, smem_u32(&sm->full[s]), u & 1, err, 2);
+                    ok = mbar_wait<BN, 128>(sm, smem_u32(&sm->full[s]), u & 1, err, 2);
                     if (!ok) break;
                     tc_fence_after();
                     const unsigned long long da = umma_desc_sw128(smem_u32(sm->stage[s].a));
@@ -285,7 +293,7 @@ k_gemm_tc(const __grid_constant__ TcJob job, const __grid_constant__ CUtensorMap
                         if (!EXACT || (kk & 1) == 0) {
                             // EXACT hands buffers over in (even block, odd block) pairs: barrier index = pair
                             const uint32_t bi = EXACT ? buf >> 1 : buf, ub = EXACT ? (j >> 1) / (NBUF / 2) : j / NBUF;
-                            ok = mbar_wait(sm, smem_u32(&sm->tmem_empty[bi]), (ub & 1) ^ 1, err, 3);
+                            ok = mbar_wait<BN, 64>(sm, smem_u32(&sm->tmem_empty[bi]), (ub & 1) ^ 1, err, 3);
                             if (!ok) break;
                             tc_fence_after();
                         }
@@ -309,7 +317,7 @@ k_gemm_tc(const __grid_constant__ TcJob job, const __grid_constant__ CUtensorMap
             for (int ks = 0; ks < k_stages; ks++, g++) {
                 const int s = g % TC_STAGES;
                 const uint32_t u = g / TC_STAGES;
-                ok = mbar_wait(sm, smem_u32(&sm->empty[s]), (u & 1) ^ 1, err, 4);
+                ok = mbar_wait<BN, 256>(sm, smem_u32(&sm->empty[s]), (u & 1) ^ 1, err, 4);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 TcStage<BN>& st = sm->stage[s];
