@@ -395,21 +395,7 @@ __device__ void prologue_norm(Ctx& c, const MegaPhase& ph, uint32_t token, const
     STAMP(c, 5);
 }
 
-// Conv weights of the thread's first four blocks (static data, fetched BEFORE the dependency wait); w[j*4 + kk].
-__device__ __forceinline__ void load_conv_w(const Ctx& c, const MegaPhase& ph, float (&w)[MAXJ]) {
-    static_assert(MAXJ >= 16, "holds 4 blocks x 4 taps");
-    const MegaLayer& L = c.S.layers[ph.layer];
-    const int hs = c.P.hs, ks = c.P.conv_ks, nb = hs / QK;
-#pragma unroll
-    for (int j = 0; j < 4; j++) {
-        const int b = c.cw + j * NC;
-        const int chs = (b < nb ? b : 0) * QK + c.lane;
-#pragma unroll
-        for (int kk = 0; kk < 4; kk++) w[j * 4 + kk] = kk < ks ? __ldg(L.conv_w + chs * ks + kk) : 0.0f;
-    }
-}
-
-__device__ void prologue_conv(Ctx& c, const MegaPhase& ph, const float (&w0)[MAXJ]) {
+__device__ void prologue_conv(Ctx& c, const MegaPhase& ph) {
     const MegaParams& P = c.P;
     const MegaLayer& L = c.S.layers[ph.layer];
     const int hs = P.hs, ks = P.conv_ks, dc = ks - 1, nb = hs / QK;
@@ -426,8 +412,7 @@ __device__ void prologue_conv(Ctx& c, const MegaPhase& ph, const float (&w0)[MAX
 #pragma unroll
             for (int kk = 0; kk < MAXKS - 1; kk++) st[j][kk] = kk < dc ? __ldcg(L.conv_state + (size_t)kk * hs + chs) : 0.0f;
 #pragma unroll
-            for (int kk = 0; kk < MAXKS; kk++)
-                cw[j][kk] = j0 == 0 ? w0[j * 4 + kk] : (kk < ks ? __ldg(L.conv_w + chs * ks + kk) : 0.0f);
+            for (int kk = 0; kk < MAXKS; kk++) cw[j][kk] = kk < ks ? __ldg(L.conv_w + chs * ks + kk) : 0.0f;
         }
         float o[4];
 #pragma unroll
@@ -566,32 +551,7 @@ __device__ void phase_attention(Ctx& c, const MegaPhase& ph, int pos) {
         const int h = it / nq, d0 = (it % nq) * 16;
         const int kvh = h / group, off = kvh * hd;
         STAMP(c, 0);
-        // The cached K rows and V rows do not depend on this step's q: their loads are issued first, so that
-        // their latency overlaps the q / k normalisation instead of following it.
-        constexpr int KU = 4;
-        constexpr int KPR = NCT / 8;                   // keys per round of the consumer threads
-        const int ch = c.ct & 7, kslot = c.ct >> 3;
-        const int nd8 = hd >> 3;
-        float kv[KU][8];
-        auto load_keys = [&](int tb) {                  // branch-free (out-of-range keys read row 0 and are dropped)
-#pragma unroll
-            for (int u = 0; u < KU; u++) {
-                const int t = tb + u * KPR + kslot;
-                const float* kp = L.k_cache + (size_t)(t < pos ? t : 0) * kv_dim + off + ch;
-#pragma unroll
-                for (int j = 0; j < 8; j++) kv[u][j] = __ldcg(kp + (j < nd8 ? j : 0) * 8);
-            }
-        };
-        if (pos > 0) load_keys(0);
-        const bool v_early = seq <= chunk && seq * 4 <= NCT;   // the whole V slice is one gather of one float4 per thread
-        float4 vpre = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (v_early && c.ct < seq * 4) {
-            const int t = c.ct >> 2, part = c.ct & 3;
-            const float* src = t < pos ? L.v_cache + (size_t)t * kv_dim + off + d0 + part * 4 : P.vbuf + off + d0 + part * 4;
-            vpre = __ldcg(reinterpret_cast<const float4*>(src));
-        }
         consumer_sync();
-        if (v_early && c.ct < seq * 4) reinterpret_cast<float4*>(Vs)[c.ct] = vpre;
         if (c.cw == 0) head_norm_rope(P.qbuf + h * hd, L.q_norm, P.eps, cosr, sinr, hd, qs, c.lane);
         if (c.cw == 1) {
             head_norm_rope(P.kbuf + off, L.k_norm, P.eps, cosr, sinr, hd, ks, c.lane);
@@ -611,11 +571,23 @@ __device__ void phase_attention(Ctx& c, const MegaPhase& ph, int pos) {
         // each, and every thread issues the loads of KU keys before any arithmetic.
         float mx = __int_as_float(0xFF800000);
         {
+            constexpr int KU = 4;
+            constexpr int KPR = NCT / 8;                   // keys per round of the consumer threads
+            const int ch = c.ct & 7, kslot = c.ct >> 3;
+            const int nd8 = hd >> 3;
             float qreg[8];
 #pragma unroll
             for (int j = 0; j < 8; j++) qreg[j] = j < nd8 ? qs[ch + j * 8] : 0.0f;
+            // cached keys t < pos: branch-free loads (out-of-range keys read row 0 and are dropped)
             for (int tb = 0; tb < pos; tb += KPR * KU) {
-                if (tb > 0) load_keys(tb);
+                float kv[KU][8];
+#pragma unroll
+                for (int u = 0; u < KU; u++) {
+                    const int t = tb + u * KPR + kslot;
+                    const float* kp = L.k_cache + (size_t)(t < pos ? t : 0) * kv_dim + off + ch;
+#pragma unroll
+                    for (int j = 0; j < 8; j++) kv[u][j] = __ldcg(kp + (j < nd8 ? j : 0) * 8);
+                }
 #pragma unroll
                 for (int u = 0; u < KU; u++) {
                     const int t = tb + u * KPR + kslot;
@@ -675,7 +647,7 @@ __device__ void phase_attention(Ctx& c, const MegaPhase& ph, int pos) {
         for (int t0 = 0; t0 < seq; t0 += chunk) {
             const int rows = chunk < seq - t0 ? chunk : seq - t0;
             consumer_sync();  // scores normalised / previous chunk consumed
-            for (int idx = c.ct; idx < rows * 4 && !v_early; idx += NCT) {
+            for (int idx = c.ct; idx < rows * 4; idx += NCT) {
                 const int t = t0 + (idx >> 2), part = idx & 3;
                 const float* src = t < pos ? L.v_cache + (size_t)t * kv_dim + off + d0 + part * 4 : P.vbuf + off + d0 + part * 4;
                 reinterpret_cast<float4*>(Vs)[idx] = __ldcg(reinterpret_cast<const float4*>(src));
@@ -795,7 +767,6 @@ __device__ void consumer(const MegaParams& P, const Smem& S, int cta, int ncta) 
             const MegaPhase& ph = S.ph[pi];
             float nw[MAXJ];
             if (ph.kind == MPH_NORM) load_norm_w(c, ph, nw);
-            if (ph.kind == MPH_CONV) load_conv_w(c, ph, nw);
             if (t > 0 || pi > 0) grid_wait(c, (P.bar_base + (unsigned long long)t * P.n_phases + pi) * (unsigned long long)ncta);
             const bool prof = P.prof && cta == 0 && c.ct == 0 && t == P.n_tokens - 1;
             c.stamp = (prof && pi == P.prof_phase) ? P.prof + (size_t)P.n_phases * 4 : nullptr;
@@ -808,7 +779,7 @@ __device__ void consumer(const MegaParams& P, const Smem& S, int cta, int ncta) 
             if (pi == 1 && cta == 0 && c.ct == 0) P.argmax_acc[(t + 1) & 1] = 0;  // free for the next step
             switch (ph.kind) {
                 case MPH_NORM: prologue_norm(c, ph, token, nw); break;
-                case MPH_CONV: prologue_conv(c, ph, nw); break;
+                case MPH_CONV: prologue_conv(c, ph); break;
                 case MPH_SILU: prologue_silu(c, ph); break;
                 case MPH_QUANT: prologue_quant(c, ph); break;
                 default: phase_attention(c, ph, pos); break;
