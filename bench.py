@@ -221,7 +221,7 @@ def workload_config(args, spec):
                     f"then tg{DECODE_TOKENS} greedy decode (timed)",
         "weights": "random init N(0,0.02) seed 0, quantised per 32-element block; synthetic stand-in for the public checkpoint",
         "l2": f"inputs larger than L2: {spec.decode_bytes_per_token(args.qtype) / 1e6:.0f} MB of weights are streamed per token (L2 126 MB)",
-        "context": 4096,
+        "context": args.context,
     }
 
 
@@ -241,6 +241,7 @@ def main():
     ap.add_argument("--only", default="decode", choices=["decode", "prefill"],
                     help="profiling aid: 'prefill' times forward_prefill_chunked of --prompt-tokens instead of the headline decode")
     ap.add_argument("--prefill-mode", default="exact", choices=["exact", "tensor", "exact-cuda-cores"])
+    ap.add_argument("--context", type=int, default=4096, help="context size the model is created with (prompt + decode tokens must fit)")
     ap.add_argument("--ubatch", type=int, default=512, help="prefill chunk of --only prefill (0 = one call); wick's default is 512")
     args = ap.parse_args()
     PROMPT_TOKENS, DECODE_TOKENS = args.prompt_tokens, args.decode_tokens
@@ -274,7 +275,7 @@ def main():
 
     path, spec = model_file(args, rank, world)
     barrier()
-    m = CudaLfm2Model(path, 4096, device=local_rank)
+    m = CudaLfm2Model(path, args.context, device=local_rank)
     st = InferenceState()
     # one independent sequence per rank (round-robin over `world` sequences), no data-path collective
     seq_index = sharding.shard_sequences(world, world, rank)[0]

@@ -85,7 +85,9 @@ __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;"
 
 // floats of the attention staging area: normalised scores of up to max_seq keys plus at least
 // 64 gathered V rows of 16 columns
-__host__ __device__ __forceinline__ int xf_floats(const MegaParams& P) { return P.max_seq + 4 + 64 * 16; }
+// (xf_extra: whatever shared memory is left once the ring is sized; at long contexts the V rows are gathered in
+// chunks of (staging floats) / 16 rows, one memory round trip per chunk, so a larger staging area is fewer trips)
+__host__ __device__ __forceinline__ int xf_floats(const MegaParams& P) { return P.max_seq + 4 + 64 * 16 + P.xf_extra; }
 
 struct Smem {
     uint8_t* ring;
@@ -647,15 +649,57 @@ __device__ void phase_attention(Ctx& c, const MegaPhase& ph, int pos) {
         for (int t0 = 0; t0 < seq; t0 += chunk) {
             const int rows = chunk < seq - t0 ? chunk : seq - t0;
             consumer_sync();  // scores normalised / previous chunk consumed
-            for (int idx = c.ct; idx < rows * 4; idx += NCT) {
-                const int t = t0 + (idx >> 2), part = idx & 3;
-                const float* src = t < pos ? L.v_cache + (size_t)t * kv_dim + off + d0 + part * 4 : P.vbuf + off + d0 + part * 4;
-                reinterpret_cast<float4*>(Vs)[idx] = __ldcg(reinterpret_cast<const float4*>(src));
+            // gather with four independent loads in flight per thread (a load -> store pair per iteration
+            // would pay one memory latency per iteration)
+            for (int idx0 = c.ct; idx0 < rows * 4; idx0 += NCT * 4) {
+                float4 g[4];
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    const int idx = idx0 + u * NCT;
+                    const int t = t0 + ((idx < rows * 4 ? idx : idx0) >> 2), part = idx & 3;
+                    const float* src = t < pos ? L.v_cache + (size_t)t * kv_dim + off + d0 + part * 4 : P.vbuf + off + d0 + part * 4;
+                    g[u] = __ldcg(reinterpret_cast<const float4*>(src));
+                }
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    const int idx = idx0 + u * NCT;
+                    if (idx < rows * 4) reinterpret_cast<float4*>(Vs)[idx] = g[u];
+                }
             }
             consumer_sync();
             if (c.ct < 16) {
-#pragma unroll 8
-                for (int tl = 0; tl < rows; tl++) acc = __fmaf_rn(sc[t0 + tl], Vs[tl * 16 + c.ct], acc);
+                // The chain is serial (one fused multiply-add per key, ascending t), but its operands are not:
+                // they are staged 16 steps at a time in registers, the next batch being loaded before the
+                // current batch's dependent FMAs, so the chain runs at FMA latency instead of shared-memory latency.
+                const float* scp = sc + t0;
+                const float* vp = Vs + c.ct;
+                auto load16 = [&](int tl, float (&sv)[16], float (&vv)[16]) {
+#pragma unroll
+                    for (int i = 0; i < 16; i++) {
+                        sv[i] = scp[tl + i];
+                        vv[i] = vp[(tl + i) * 16];
+                    }
+                };
+                int tl = 0;
+                if (rows >= 16) {
+                    float sa[16], va[16], sb[16], vb[16];
+                    load16(0, sa, va);
+                    for (;;) {
+                        bool more = tl + 32 <= rows;
+                        if (more) load16(tl + 16, sb, vb);
+#pragma unroll
+                        for (int i = 0; i < 16; i++) acc = __fmaf_rn(sa[i], va[i], acc);
+                        tl += 16;
+                        if (!more) break;
+                        more = tl + 32 <= rows;
+                        if (more) load16(tl + 16, sa, va);
+#pragma unroll
+                        for (int i = 0; i < 16; i++) acc = __fmaf_rn(sb[i], vb[i], acc);
+                        tl += 16;
+                        if (!more) break;
+                    }
+                }
+                for (; tl < rows; tl++) acc = __fmaf_rn(scp[tl], vp[tl * 16], acc);
             }
         }
         STAMP(c, 6);

@@ -344,6 +344,7 @@ int32_t build_mega(wick_cuda_model* m) {
     P.kmax = std::max(hs, is);
     P.slot_bytes = (int)std::max<size_t>(16384, (max_group + 1023) / 1024 * 1024);
     P.n_slots = 0;
+    P.xf_extra = 0;
     int max_smem = 0;
     CU_TRY(cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, m->device));
     size_t fixed = mega_smem_bytes(P);
@@ -369,6 +370,10 @@ int32_t build_mega(wick_cuda_model* m) {
     P.layers = m->d_mlayers;
     P.bar_counter = m->d_sync;
     P.argmax_acc = m->d_sync + 1;
+    {   // hand the shared memory the ring leaves unused to the attention staging area
+        const size_t used = mega_smem_bytes(P);
+        if ((size_t)max_smem > used + 1024) P.xf_extra = (int)(((size_t)max_smem - used - 1024) / 4) & ~15;
+    }
     m->mega_ctas = mega_max_ctas(P);
     m->mega_ok = m->mega_ctas > 0;
     return WICK_CUDA_OK;
