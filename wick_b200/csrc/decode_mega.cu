@@ -649,57 +649,15 @@ __device__ void phase_attention(Ctx& c, const MegaPhase& ph, int pos) {
         for (int t0 = 0; t0 < seq; t0 += chunk) {
             const int rows = chunk < seq - t0 ? chunk : seq - t0;
             consumer_sync();  // scores normalised / previous chunk consumed
-            // gather with four independent loads in flight per thread (a load -> store pair per iteration
-            // would pay one memory latency per iteration)
-            for (int idx0 = c.ct; idx0 < rows * 4; idx0 += NCT * 4) {
-                float4 g[4];
-#pragma unroll
-                for (int u = 0; u < 4; u++) {
-                    const int idx = idx0 + u * NCT;
-                    const int t = t0 + ((idx < rows * 4 ? idx : idx0) >> 2), part = idx & 3;
-                    const float* src = t < pos ? L.v_cache + (size_t)t * kv_dim + off + d0 + part * 4 : P.vbuf + off + d0 + part * 4;
-                    g[u] = __ldcg(reinterpret_cast<const float4*>(src));
-                }
-#pragma unroll
-                for (int u = 0; u < 4; u++) {
-                    const int idx = idx0 + u * NCT;
-                    if (idx < rows * 4) reinterpret_cast<float4*>(Vs)[idx] = g[u];
-                }
+            for (int idx = c.ct; idx < rows * 4; idx += NCT) {
+                const int t = t0 + (idx >> 2), part = idx & 3;
+                const float* src = t < pos ? L.v_cache + (size_t)t * kv_dim + off + d0 + part * 4 : P.vbuf + off + d0 + part * 4;
+                reinterpret_cast<float4*>(Vs)[idx] = __ldcg(reinterpret_cast<const float4*>(src));
             }
             consumer_sync();
             if (c.ct < 16) {
-                // The chain is serial (one fused multiply-add per key, ascending t), but its operands are not:
-                // they are staged 16 steps at a time in registers, the next batch being loaded before the
-                // current batch's dependent FMAs, so the chain runs at FMA latency instead of shared-memory latency.
-                const float* scp = sc + t0;
-                const float* vp = Vs + c.ct;
-                auto load16 = [&](int tl, float (&sv)[16], float (&vv)[16]) {
-#pragma unroll
-                    for (int i = 0; i < 16; i++) {
-                        sv[i] = scp[tl + i];
-                        vv[i] = vp[(tl + i) * 16];
-                    }
-                };
-                int tl = 0;
-                if (rows >= 16) {
-                    float sa[16], va[16], sb[16], vb[16];
-                    load16(0, sa, va);
-                    for (;;) {
-                        bool more = tl + 32 <= rows;
-                        if (more) load16(tl + 16, sb, vb);
-#pragma unroll
-                        for (int i = 0; i < 16; i++) acc = __fmaf_rn(sa[i], va[i], acc);
-                        tl += 16;
-                        if (!more) break;
-                        more = tl + 32 <= rows;
-                        if (more) load16(tl + 16, sa, va);
-#pragma unroll
-                        for (int i = 0; i < 16; i++) acc = __fmaf_rn(sb[i], vb[i], acc);
-                        tl += 16;
-                        if (!more) break;
-                    }
-                }
-                for (; tl < rows; tl++) acc = __fmaf_rn(scp[tl], vp[tl * 16], acc);
+#pragma unroll 8
+                for (int tl = 0; tl < rows; tl++) acc = __fmaf_rn(sc[t0 + tl], Vs[tl * 16 + c.ct], acc);
             }
         }
         STAMP(c, 6);
@@ -796,6 +754,13 @@ __device__ __forceinline__ float group_chain_sum(const uint32_t* __restrict__ qs
     return acc;
 }
 
+// DTK: the quantisation type every streamed matrix of the model has (DT_Q4_0 or DT_Q8_0), or 0 when they differ
+// and the type is looked up per matrix.  Specialising removes the other type's product / chain code from the
+// kernel: the kernel walks ~70 short phases per token, and its speed turned out to depend on its code size.
+template <int DTK>
+__device__ __forceinline__ bool is_q4(int dtype) { return DTK ? DTK == DT_Q4_0 : dtype == DT_Q4_0; }
+
+template <int DTK>
 __device__ void consumer(const MegaParams& P, const Smem& S, int cta, int ncta) {
     Ctx c{P, S, cta, ncta, (int)threadIdx.x - 32, ((int)threadIdx.x - 32) >> 5, (int)threadIdx.x & 31, nullptr};
     int slot = 0;
@@ -866,7 +831,7 @@ __device__ void consumer(const MegaParams& P, const Smem& S, int cta, int ncta) 
                         const __half* dbase = reinterpret_cast<const __half*>(bases[half] + (size_t)ng * qgb);
                         for (int gi = 0; gi < ng; gi++) {
                             uint32_t* qs = reinterpret_cast<uint32_t*>(bases[half] + (size_t)gi * qgb);
-                            if (w.dtype == DT_Q4_0) stage_products<DT_Q4_0>(qs, dbase + (size_t)gi * nb * 4, nb, tt, xq32, S.xs16);
+                            if (is_q4<DTK>(w.dtype)) stage_products<DT_Q4_0>(qs, dbase + (size_t)gi * nb * 4, nb, tt, xq32, S.xs16);
                             else stage_products<DT_Q8_0>(qs, dbase + (size_t)gi * nb * 4, nb, tt, xq32, S.xs);
                         }
                     }
@@ -874,8 +839,8 @@ __device__ void consumer(const MegaParams& P, const Smem& S, int cta, int ncta) 
                     for (int gi = tw; gi < ng; gi += TEAM_WARPS) {
                         const uint32_t* qa = reinterpret_cast<const uint32_t*>(bases[0] + (size_t)gi * qgb);
                         const uint32_t* qb = reinterpret_cast<const uint32_t*>(bases[1] + (size_t)gi * qgb);
-                        float ga = wg.dtype == DT_Q4_0 ? group_chain_sum<DT_Q4_0>(qa, nb, c.lane) : group_chain_sum<DT_Q8_0>(qa, nb, c.lane);
-                        float ua = wu.dtype == DT_Q4_0 ? group_chain_sum<DT_Q4_0>(qb, nb, c.lane) : group_chain_sum<DT_Q8_0>(qb, nb, c.lane);
+                        float ga = is_q4<DTK>(wg.dtype) ? group_chain_sum<DT_Q4_0>(qa, nb, c.lane) : group_chain_sum<DT_Q8_0>(qa, nb, c.lane);
+                        float ua = is_q4<DTK>(wu.dtype) ? group_chain_sum<DT_Q4_0>(qb, nb, c.lane) : group_chain_sum<DT_Q8_0>(qb, nb, c.lane);
                         ga = reduce_row8(ga);
                         ua = reduce_row8(ua);
                         const int row = (g0 + gi) * 4 + ((c.lane >> 2) & 3);
@@ -917,14 +882,14 @@ __device__ void consumer(const MegaParams& P, const Smem& S, int cta, int ncta) 
                         const __half* dbase = reinterpret_cast<const __half*>(base + (size_t)ng * qgb);
                         for (int gi = 0; gi < ng; gi++) {
                             uint32_t* qs = reinterpret_cast<uint32_t*>(base + (size_t)gi * qgb);
-                            if (w.dtype == DT_Q4_0) stage_products<DT_Q4_0>(qs, dbase + (size_t)gi * nb * 4, nb, tt, xq32, S.xs16);
+                            if (is_q4<DTK>(w.dtype)) stage_products<DT_Q4_0>(qs, dbase + (size_t)gi * nb * 4, nb, tt, xq32, S.xs16);
                             else stage_products<DT_Q8_0>(qs, dbase + (size_t)gi * nb * 4, nb, tt, xq32, S.xs);
                         }
                         team_sync(team);
                         if (c.stamp && nst < 4) c.stamp[nst * 4 + 2] = globaltimer_ns();
                         for (int gi = tw; gi < ng; gi += TEAM_WARPS) {
                             const uint32_t* qs = reinterpret_cast<const uint32_t*>(base + (size_t)gi * qgb);
-                            float acc = w.dtype == DT_Q4_0 ? group_chain_sum<DT_Q4_0>(qs, nb, c.lane) : group_chain_sum<DT_Q8_0>(qs, nb, c.lane);
+                            float acc = is_q4<DTK>(w.dtype) ? group_chain_sum<DT_Q4_0>(qs, nb, c.lane) : group_chain_sum<DT_Q8_0>(qs, nb, c.lane);
                             acc = reduce_row8(acc);
                             const int row = (g0 + gi) * 4 + ((c.lane >> 2) & 3);
                             if ((c.lane & 19) == 0 && row < w.m) {
@@ -988,6 +953,7 @@ __device__ void consumer(const MegaParams& P, const Smem& S, int cta, int ncta) 
     }
 }
 
+template <int DTK>
 __global__ void __launch_bounds__(MEGA_THREADS, 1) k_decode_mega(const MegaParams P) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     Smem S = carve(smem_raw, P);
@@ -1023,7 +989,7 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) k_decode_mega(const MegaParam
             }
         }
     } else {
-        consumer(P, S, blockIdx.x, gridDim.x);
+        consumer<DTK>(P, S, blockIdx.x, gridDim.x);
     }
     __syncthreads();
 }
@@ -1043,16 +1009,26 @@ size_t mega_smem_bytes(const MegaParams& P) {
     return o;
 }
 
+namespace {
+const void* mega_kernel(const MegaParams& P) {
+    switch (P.uniform_dtype) {
+        case DT_Q4_0: return (const void*)k_decode_mega<DT_Q4_0>;
+        case DT_Q8_0: return (const void*)k_decode_mega<DT_Q8_0>;
+        default: return (const void*)k_decode_mega<0>;
+    }
+}
+}  // namespace
+
 int mega_max_ctas(const MegaParams& P) {
     int dev = 0, sms = 0, per_sm = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     size_t smem = mega_smem_bytes(P);
-    if (cudaFuncSetAttribute(k_decode_mega, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+    if (cudaFuncSetAttribute(mega_kernel(P), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
         cudaGetLastError();
         return 0;
     }
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_decode_mega, MEGA_THREADS, smem) != cudaSuccess) {
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, mega_kernel(P), MEGA_THREADS, smem) != cudaSuccess) {
         cudaGetLastError();
         return 0;
     }
@@ -1062,11 +1038,11 @@ int mega_max_ctas(const MegaParams& P) {
 cudaError_t launch_decode_mega(cudaStream_t st, const MegaParams& P, int n_ctas) {
     size_t smem = mega_smem_bytes(P);
     // the attribute is per function, not per model: models of different size share the kernel
-    cudaError_t e = cudaFuncSetAttribute(k_decode_mega, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(mega_kernel(P), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     void* args[] = {(void*)&P};
     g_kernel_launches++;
-    return cudaLaunchCooperativeKernel((const void*)k_decode_mega, dim3(n_ctas), dim3(MEGA_THREADS), args, smem, st);
+    return cudaLaunchCooperativeKernel(mega_kernel(P), dim3(n_ctas), dim3(MEGA_THREADS), args, smem, st);
 }
 
 }  // namespace wick

@@ -81,6 +81,7 @@ struct MegaParams {
     unsigned long long* argmax_acc;    // [2], alternating by token
     int slot_bytes, n_slots;           // bulk-copy ring geometry
     int kmax;                          // max input length over phases (shared-memory sizing)
+    int uniform_dtype;                 // DT_Q4_0 / DT_Q8_0 when every streamed matrix has that type, else 0
     int xf_extra;                      // extra floats of attention staging (the shared memory left over by the ring)
     // optional per-phase timestamps (globaltimer ns) of CTA 0 for the last step of a launch:
     // [phase][0] barrier passed, [1] prologue done, [2] mat-vec done, [3] arrived

@@ -345,6 +345,17 @@ int32_t build_mega(wick_cuda_model* m) {
     P.slot_bytes = (int)std::max<size_t>(16384, (max_group + 1023) / 1024 * 1024);
     P.n_slots = 0;
     P.xf_extra = 0;
+    P.uniform_dtype = 0;
+    {
+        int dt = -1;
+        bool same = true;
+        for (const MegaPhase& q : ph)
+            for (int i = 0; i < q.n_mat; i++) {
+                if (dt < 0) dt = q.mat[i].w.dtype;
+                same = same && q.mat[i].w.dtype == dt;
+            }
+        if (same && (dt == DT_Q4_0 || dt == DT_Q8_0)) P.uniform_dtype = dt;
+    }
     int max_smem = 0;
     CU_TRY(cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, m->device));
     size_t fixed = mega_smem_bytes(P);
