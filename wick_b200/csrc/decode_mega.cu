@@ -649,16 +649,46 @@ __device__ void phase_attention(Ctx& c, const MegaPhase& ph, int pos) {
         for (int t0 = 0; t0 < seq; t0 += chunk) {
             const int rows = chunk < seq - t0 ? chunk : seq - t0;
             consumer_sync();  // scores normalised / previous chunk consumed
-            for (int idx = c.ct; idx < rows * 4; idx += NCT) {
-                const int t = t0 + (idx >> 2), part = idx & 3;
-                const float* src = t < pos ? L.v_cache + (size_t)t * kv_dim + off + d0 + part * 4 : P.vbuf + off + d0 + part * 4;
-                reinterpret_cast<float4*>(Vs)[idx] = __ldcg(reinterpret_cast<const float4*>(src));
+            if (t0 == 0) STAMP(c, 8);
+            // gather: four independent 16-byte loads in flight per thread (a load -> store pair per iteration
+            // pays one memory latency per iteration)
+            for (int idx0 = c.ct; idx0 < rows * 4; idx0 += NCT * 4) {
+                float4 g0, g1, g2, g3;
+                const int n4 = rows * 4;
+                const int i0 = idx0, i1 = idx0 + NCT, i2 = idx0 + 2 * NCT, i3 = idx0 + 3 * NCT;
+#define WICK_VSRC(i) ((t0 + ((i) >> 2)) < pos ? L.v_cache + (size_t)(t0 + ((i) >> 2)) * kv_dim + off + d0 + ((i)&3) * 4 \
+                                              : P.vbuf + off + d0 + ((i)&3) * 4)
+                g0 = __ldcg(reinterpret_cast<const float4*>(WICK_VSRC(i0)));
+                g1 = __ldcg(reinterpret_cast<const float4*>(WICK_VSRC(i1 < n4 ? i1 : i0)));
+                g2 = __ldcg(reinterpret_cast<const float4*>(WICK_VSRC(i2 < n4 ? i2 : i0)));
+                g3 = __ldcg(reinterpret_cast<const float4*>(WICK_VSRC(i3 < n4 ? i3 : i0)));
+#undef WICK_VSRC
+                float4* V4 = reinterpret_cast<float4*>(Vs);
+                V4[i0] = g0;
+                if (i1 < n4) V4[i1] = g1;
+                if (i2 < n4) V4[i2] = g2;
+                if (i3 < n4) V4[i3] = g3;
             }
             consumer_sync();
+            if (t0 == 0) STAMP(c, 9);
             if (c.ct < 16) {
-#pragma unroll 8
-                for (int tl = 0; tl < rows; tl++) acc = __fmaf_rn(sc[t0 + tl], Vs[tl * 16 + c.ct], acc);
+                // the chain is serial, its operands are not: 16 steps' operands are loaded before their FMAs
+                const float* scp = sc + t0;
+                const float* vp = Vs + c.ct;
+                int tl = 0;
+                for (; tl + 16 <= rows; tl += 16) {
+                    float sv[16], vv[16];
+#pragma unroll
+                    for (int i = 0; i < 16; i++) {
+                        sv[i] = scp[tl + i];
+                        vv[i] = vp[(tl + i) * 16];
+                    }
+#pragma unroll
+                    for (int i = 0; i < 16; i++) acc = __fmaf_rn(sv[i], vv[i], acc);
+                }
+                for (; tl < rows; tl++) acc = __fmaf_rn(scp[tl], vp[tl * 16], acc);
             }
+            if (t0 == 0) STAMP(c, 10);
         }
         STAMP(c, 6);
         if (c.ct < 16) P.attn_out[h * hd + d0 + c.ct] = acc;
