@@ -277,3 +277,39 @@ def test_bounded_waits_report_timeout(wick, model_dir):
     st = wick.InferenceState()
     assert np.array_equal(m.forward_prefill(toks, 0, st), want)
     assert m.forward_greedy([3], 8, st) == t1
+
+
+def test_split_scores_long_context_decode(wick, orc, model_dir, monkeypatch):
+    """From 768 cached tokens on, decode computes the cached keys' scores in a phase of its own (keys split over
+    all CTAs).  Same bits as the in-phase loop (switched back on by WICK_CUDA_NO_SPLIT_SCORES) and as the oracle,
+    across the switch-over point and for the device-resident loop."""
+    from wick_b200 import gguf_synth as gs
+    path = _model_path(model_dir, "tiny-wide", "q4_0")
+    toks = gs.random_prompt(760, gs.SPECS["tiny-wide"].vocab, seed=12)
+    a = wick.CudaLfm2Model(path, 2048)
+    sa = wick.InferenceState()
+    la = a.forward_prefill(toks, 0, sa)
+    om = orc.OracleModel(path, 2048)
+    lo = om.forward_prefill(toks, 0)
+    assert_logits_equal(la, lo, "prefill")
+    tok = orc.argmax(lo)
+    for i in range(20):                      # positions 760..779: the list switches at 768
+        x, y = a.forward([tok], sa.seq_len, sa), om.forward(tok)
+        assert_logits_equal(x, y, f"step {i}")
+        tok = orc.argmax(y)
+    dev = a.generate_greedy(tok, 40, sa)
+    assert list(dev) == list(om.generate_greedy(tok, 40))
+    monkeypatch.setenv("WICK_CUDA_NO_SPLIT_SCORES", "1")
+    b = wick.CudaLfm2Model(path, 2048)
+    sb = wick.InferenceState()
+    more = gs.random_prompt(900, gs.SPECS["tiny-wide"].vocab, seed=13)
+    lb = b.forward_prefill(more, 0, sb)
+    monkeypatch.delenv("WICK_CUDA_NO_SPLIT_SCORES")
+    la2 = a.forward_prefill(more, 0, sa)
+    assert_logits_equal(la2, lb, "prefill again")
+    first = int(np.argmax(lb))
+    monkeypatch.setenv("WICK_CUDA_NO_SPLIT_SCORES", "1")
+    gb = b.generate_greedy(first, 32, sb)
+    monkeypatch.delenv("WICK_CUDA_NO_SPLIT_SCORES")
+    ga = a.generate_greedy(first, 32, sa)
+    assert list(ga) == list(gb)

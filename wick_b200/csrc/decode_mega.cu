@@ -181,7 +181,7 @@ __device__ unsigned long long producer(const MegaParams& P, const Smem& S, int c
     for (int t = 0; t < P.n_tokens; t++) {
         for (int pi = 0; pi < P.n_phases; pi++) {
             const MegaPhase& ph = S.ph[pi];
-            if (ph.kind == MPH_ATTN) continue;
+            if (ph.kind == MPH_ATTN || ph.kind == MPH_SCORES) continue;
             Plan pl = plan_phase(ph, cta, ncta, P.slot_bytes);
             // stage list: per matrix its chunks in order; a paired phase alternates the two matrices chunk by chunk
             const int n_seq = ph.pair ? 1 : ph.n_mat, n_alt = ph.pair ? 2 : 1;
@@ -525,11 +525,71 @@ __device__ void head_norm_rope(const float* src_g, const float* w, float eps, co
     __syncwarp();
 }
 
+// Long contexts: the q.k scores of the cached keys, for the phase_attention that follows.  In phase_attention
+// every (head, slice) item recomputes its head's scores, which is cheap while the context is short; at thousands
+// of keys it dominates the step (each CTA can only keep a few hundred small loads in flight).  Here the work
+// items are (head, block of KEYS_PER_ITEM keys), dealt to ALL CTAs, and each score is computed once, with the
+// arithmetic of the in-phase loop (attn_scores, cpu.rs:1404-1458), and stored to P.scores_g.
+__device__ void phase_scores(Ctx& c, const MegaPhase& ph, int pos) {
+    const MegaParams& P = c.P;
+    const MegaLayer& L = c.S.layers[ph.layer];
+    const int hd = P.head_dim, n_heads = P.n_heads, n_kv = L.n_kv, kv_dim = n_kv * hd, group = n_heads / n_kv;
+    const float scale = __fdiv_rn(1.0f, sqrtf((float)hd));
+    const float* cosr = P.rope_cos + (size_t)pos * (hd / 2);
+    const float* sinr = P.rope_sin + (size_t)pos * (hd / 2);
+    float* qs = c.S.head;
+    constexpr int KU = 4;
+    constexpr int KPR = NCT / 8;
+    constexpr int KEYS_PER_ITEM = KPR * KU;
+    const int nblk = (pos + KEYS_PER_ITEM - 1) / KEYS_PER_ITEM;
+    const int items = n_heads * nblk;
+    const int it0 = share(c.cta, items, c.ncta), it1 = share(c.cta + 1, items, c.ncta);
+    const int ch = c.ct & 7, kslot = c.ct >> 3;
+    const int nd8 = hd >> 3;
+    int cur_h = -1;
+    float qreg[8];
+    for (int it = it0; it < it1; it++) {
+        const int h = it / nblk, tb = (it - h * nblk) * KEYS_PER_ITEM;
+        const int off = (h / group) * hd;
+        if (h != cur_h) {
+            consumer_sync();  // everyone is done with the previous head's q
+            if (c.cw == 0) head_norm_rope(P.qbuf + h * hd, L.q_norm, P.eps, cosr, sinr, hd, qs, c.lane);
+            consumer_sync();
+#pragma unroll
+            for (int j = 0; j < 8; j++) qreg[j] = j < nd8 ? qs[ch + j * 8] : 0.0f;
+            cur_h = h;
+        }
+        float kv[KU][8];
+#pragma unroll
+        for (int u = 0; u < KU; u++) {
+            const int t = tb + u * KPR + kslot;
+            const float* kp = L.k_cache + (size_t)(t < pos ? t : 0) * kv_dim + off + ch;
+#pragma unroll
+            for (int j = 0; j < 8; j++) kv[u][j] = __ldcg(kp + (j < nd8 ? j : 0) * 8);
+        }
+#pragma unroll
+        for (int u = 0; u < KU; u++) {
+            const int t = tb + u * KPR + kslot;
+            float a = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 8; j++)
+                if (j < nd8) a = __fmaf_rn(qreg[j], kv[u][j], a);
+            for (int j = 8; j < nd8; j++)  // heads wider than 64
+                a = __fmaf_rn(qs[ch + j * 8], __ldcg(L.k_cache + (size_t)(t < pos ? t : 0) * kv_dim + off + ch + j * 8), a);
+            a = __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, 4));
+            a = __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, 1));
+            a = __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, 2));
+            if (t < pos && ch == 0) P.scores_g[(size_t)h * P.max_seq + t] = __fmul_rn(a, scale);
+        }
+    }
+}
+
 // forward_attn_block between the QKV and output projections (lfm2.rs:783-1007).  A work item is
 // (query head, 16-wide slice of the head's output dims); items are spread over the CTAs.  Every
 // item recomputes its head's scores and softmax (cheap), then the slice's weighted V sum: the
 // needed V columns are first gathered into shared memory by all threads (one memory latency per
 // chunk), and 16 threads run the fused chains in ascending t, the reference's order.
+template <bool LONG>
 __device__ void phase_attention(Ctx& c, const MegaPhase& ph, int pos) {
     const MegaParams& P = c.P;
     const MegaLayer& L = c.S.layers[ph.layer];
@@ -580,8 +640,16 @@ __device__ void phase_attention(Ctx& c, const MegaPhase& ph, int pos) {
             float qreg[8];
 #pragma unroll
             for (int j = 0; j < 8; j++) qreg[j] = j < nd8 ? qs[ch + j * 8] : 0.0f;
+            // long contexts: the cached keys' scores were computed once by the MPH_SCORES phase
+            if (LONG) {
+                for (int t = c.ct; t < pos; t += NCT) {
+                    const float sv = __ldcg(P.scores_g + (size_t)h * P.max_seq + t);
+                    sc[t] = sv;
+                    mx = fmaxf(mx, sv);
+                }
+            }
             // cached keys t < pos: branch-free loads (out-of-range keys read row 0 and are dropped)
-            for (int tb = 0; tb < pos; tb += KPR * KU) {
+            for (int tb = 0; tb < pos && !LONG; tb += KPR * KU) {
                 float kv[KU][8];
 #pragma unroll
                 for (int u = 0; u < KU; u++) {
@@ -790,7 +858,9 @@ __device__ __forceinline__ float group_chain_sum(const uint32_t* __restrict__ qs
 template <int DTK>
 __device__ __forceinline__ bool is_q4(int dtype) { return DTK ? DTK == DT_Q4_0 : dtype == DT_Q4_0; }
 
-template <int DTK>
+// LONG: the launch uses the long-context phase list (MPH_SCORES phases present).  A separate instantiation, so
+// that the short-context kernel does not carry that code (see the note on code size above).
+template <int DTK, bool LONG>
 __device__ void consumer(const MegaParams& P, const Smem& S, int cta, int ncta) {
     Ctx c{P, S, cta, ncta, (int)threadIdx.x - 32, ((int)threadIdx.x - 32) >> 5, (int)threadIdx.x & 31, nullptr};
     int slot = 0;
@@ -821,10 +891,13 @@ __device__ void consumer(const MegaParams& P, const Smem& S, int cta, int ncta) 
                 case MPH_CONV: prologue_conv(c, ph); break;
                 case MPH_SILU: prologue_silu(c, ph); break;
                 case MPH_QUANT: prologue_quant(c, ph); break;
-                default: phase_attention(c, ph, pos); break;
+                case MPH_SCORES:
+                    if (LONG) phase_scores(c, ph, pos);
+                    break;
+                default: phase_attention<LONG>(c, ph, pos); break;
             }
             if (prof) P.prof[pi * 4 + 1] = globaltimer_ns();
-            if (ph.kind != MPH_ATTN && ph.pair) {
+            if (ph.kind != MPH_ATTN && ph.kind != MPH_SCORES && ph.pair) {
                 // gate / up as alternating stages: stage pair j goes to team j % NTEAMS, which keeps both
                 // slots until it has the two sums of each row and can apply SwiGLU (n_slots is a multiple of
                 // 2 * NTEAMS, so within the phase a slot always returns to the same team)
@@ -883,7 +956,7 @@ __device__ void consumer(const MegaParams& P, const Smem& S, int cta, int ncta) 
                         mbar_arrive(&S.empty[slot_b]);
                     }
                 }
-            } else if (ph.kind != MPH_ATTN) {
+            } else if (ph.kind != MPH_ATTN && ph.kind != MPH_SCORES) {
                 Plan pl = plan_phase(ph, cta, ncta, P.slot_bytes);
                 int off = 0, nst = 0;
                 for (int mi = 0; mi < ph.n_mat; mi++) {
@@ -983,7 +1056,7 @@ __device__ void consumer(const MegaParams& P, const Smem& S, int cta, int ncta) 
     }
 }
 
-template <int DTK>
+template <int DTK, bool LONG>
 __global__ void __launch_bounds__(MEGA_THREADS, 1) k_decode_mega(const MegaParams P) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     Smem S = carve(smem_raw, P);
@@ -1019,7 +1092,7 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) k_decode_mega(const MegaParam
             }
         }
     } else {
-        consumer<DTK>(P, S, blockIdx.x, gridDim.x);
+        consumer<DTK, LONG>(P, S, blockIdx.x, gridDim.x);
     }
     __syncthreads();
 }
@@ -1041,10 +1114,17 @@ size_t mega_smem_bytes(const MegaParams& P) {
 
 namespace {
 const void* mega_kernel(const MegaParams& P) {
+    if (P.long_ctx) {
+        switch (P.uniform_dtype) {
+            case DT_Q4_0: return (const void*)k_decode_mega<DT_Q4_0, true>;
+            case DT_Q8_0: return (const void*)k_decode_mega<DT_Q8_0, true>;
+            default: return (const void*)k_decode_mega<0, true>;
+        }
+    }
     switch (P.uniform_dtype) {
-        case DT_Q4_0: return (const void*)k_decode_mega<DT_Q4_0>;
-        case DT_Q8_0: return (const void*)k_decode_mega<DT_Q8_0>;
-        default: return (const void*)k_decode_mega<0>;
+        case DT_Q4_0: return (const void*)k_decode_mega<DT_Q4_0, false>;
+        case DT_Q8_0: return (const void*)k_decode_mega<DT_Q8_0, false>;
+        default: return (const void*)k_decode_mega<0, false>;
     }
 }
 }  // namespace

@@ -18,6 +18,8 @@ enum MegaPhaseKind : int {
     MPH_ATTN = 2,   // no matmul: QK-norm, RoPE, KV append, single-query attention per head
     MPH_QUANT = 3,  // input = a vector produced by the previous phase (attn_out, or the fused SwiGLU output)
     MPH_SILU = 4,   // input = silu(gate) * up, recomputed by every CTA (when the fused form is unavailable)
+    MPH_SCORES = 5, // long contexts only, before MPH_ATTN of the same layer: q.k of the cached keys, the keys of every
+                    // head split over ALL CTAs, raw scaled scores to global memory (no mat-vec)
 };
 
 enum MegaEpilogue : int {
@@ -81,6 +83,8 @@ struct MegaParams {
     unsigned long long* argmax_acc;    // [2], alternating by token
     int slot_bytes, n_slots;           // bulk-copy ring geometry
     int kmax;                          // max input length over phases (shared-memory sizing)
+    int long_ctx;                      // 1: the phase list has MPH_SCORES phases and MPH_ATTN reads the scores they wrote
+    float* scores_g;                   // [n_heads][max_seq] scaled scores of the cached keys (long_ctx)
     int uniform_dtype;                 // DT_Q4_0 / DT_Q8_0 when every streamed matrix has that type, else 0
     int xf_extra;                      // extra floats of attention staging (the shared memory left over by the ring)
     // optional per-phase timestamps (globaltimer ns) of CTA 0 for the last step of a launch:

@@ -3,6 +3,7 @@
 // MetalLfm2Model plays in wick (wick/src/model/metal_lfm2.rs:170-277, :280-610):
 // one sequence lives in the model; weights, KV cache, conv state and scratch are
 // device resident; a decode step is one submission (here: one CUDA graph launch).
+#include <algorithm>
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
@@ -108,6 +109,10 @@ struct wick_cuda_model {
     int mega_ctas = 0;
     MegaParams mega{};
     MegaPhase* d_phases = nullptr;
+    MegaPhase* d_phases_long = nullptr;  // the same list with an MPH_SCORES phase before every MPH_ATTN (long contexts)
+    int n_phases_long = 0;
+    float* scores_g = nullptr;
+    bool last_launch_long = false, long_ok = false;
     MegaLayer* d_mlayers = nullptr;
     unsigned long long* d_sync = nullptr;  // [0] barrier counter, [1..2] argmax accumulators
     unsigned long long* d_prof = nullptr;  // [n_phases][4] timestamps of the last step
@@ -358,7 +363,9 @@ int32_t build_mega(wick_cuda_model* m) {
     }
     int max_smem = 0;
     CU_TRY(cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, m->device));
-    size_t fixed = mega_smem_bytes(P);
+    const int n_phases_short = P.n_phases;
+    P.n_phases = (int)ph.size() + (int)std::count_if(ph.begin(), ph.end(), [](const MegaPhase& q) { return q.kind == MPH_ATTN; });
+    size_t fixed = mega_smem_bytes(P);  // sized for the longer of the two phase lists
     if (fixed + MEGA_TEAMS * ((size_t)P.slot_bytes + 16) + 64 * 4 > (size_t)max_smem) return WICK_CUDA_OK;
     P.n_slots = (int)(((size_t)max_smem - fixed - 64 * 4) / ((size_t)P.slot_bytes + 16));
     if (P.n_slots > 30) P.n_slots = 30;
@@ -367,11 +374,25 @@ int32_t build_mega(wick_cuda_model* m) {
         for (auto& q : ph) if (q.pair) { q.pair = 0; q.mat[0].epi = q.mat[1].epi = MEP_STORE; }
     for (size_t i = 0; i + 1 < ph.size(); i++)
         if (ph[i].kind == MPH_NORM && ph[i].n_mat == 2 && !ph[i].pair && ph[i + 1].kind == MPH_QUANT && ph[i + 1].src == m->gate) ph[i + 1].kind = MPH_SILU;
+    // long-context variant of the list: the cached keys' scores are computed by a phase of their own, spread over all CTAs
+    std::vector<MegaPhase> ph_long;
+    for (const MegaPhase& q : ph) {
+        if (q.kind == MPH_ATTN) {
+            MegaPhase sc = q;
+            sc.kind = MPH_SCORES;
+            ph_long.push_back(sc);
+        }
+        ph_long.push_back(q);
+    }
+    m->n_phases_long = (int)ph_long.size();
+    W_TRY(dev_alloc(m, &m->d_phases_long, ph_long.size()));
+    W_TRY(dev_alloc(m, &m->scores_g, (size_t)c.n_heads * c.max_seq_len));
+    CU_TRY(cudaMemcpy(m->d_phases_long, ph_long.data(), ph_long.size() * sizeof(MegaPhase), cudaMemcpyHostToDevice));
     W_TRY(dev_alloc(m, &m->d_phases, ph.size()));
     W_TRY(dev_alloc(m, &m->d_mlayers, ml.size()));
     W_TRY(dev_alloc(m, &m->d_sync, 4));
-    W_TRY(dev_alloc(m, &m->d_prof, ph.size() * 4 + 16));
-    CU_TRY(cudaMemset(m->d_prof, 0, (ph.size() * 4 + 16) * 8));
+    W_TRY(dev_alloc(m, &m->d_prof, ph_long.size() * 4 + 16));
+    CU_TRY(cudaMemset(m->d_prof, 0, (ph_long.size() * 4 + 16) * 8));
     P.prof = m->d_prof;
     P.prof_phase = getenv("WICK_CUDA_PROF_PHASE") ? atoi(getenv("WICK_CUDA_PROF_PHASE")) : -1;
     CU_TRY(cudaMemcpy(m->d_phases, ph.data(), ph.size() * sizeof(MegaPhase), cudaMemcpyHostToDevice));
@@ -382,10 +403,20 @@ int32_t build_mega(wick_cuda_model* m) {
     P.bar_counter = m->d_sync;
     P.argmax_acc = m->d_sync + 1;
     {   // hand the shared memory the ring leaves unused to the attention staging area
-        const size_t used = mega_smem_bytes(P);
+        const size_t used = mega_smem_bytes(P);  // still with the long list's phase count
         if ((size_t)max_smem > used + 1024) P.xf_extra = (int)(((size_t)max_smem - used - 1024) / 4) & ~15;
     }
+    P.n_phases = n_phases_short;
+    P.long_ctx = 0;
+    P.scores_g = m->scores_g;
     m->mega_ctas = mega_max_ctas(P);
+    {   // the long-context instantiation must be co-resident on the same grid, or it is not used
+        MegaParams PL = P;
+        PL.long_ctx = 1;
+        PL.n_phases = m->n_phases_long;
+        PL.phases = m->d_phases_long;
+        m->long_ok = mega_max_ctas(PL) >= m->mega_ctas;
+    }
     m->mega_ok = m->mega_ctas > 0;
     return WICK_CUDA_OK;
 }
@@ -393,9 +424,19 @@ int32_t build_mega(wick_cuda_model* m) {
 // Runs n decode steps with the persistent kernel; ctl holds token / pos / step on entry.
 void logits_matvec(wick_cuda_model* m);
 
+// Contexts from this length on decode with the split-scores phase list (one extra grid barrier per attention layer,
+// ~2.5 us, against a scores loop that grows by ~12 ns per cached key and CTA).
+static const uint32_t MEGA_LONG_CTX = 768;
+
 int32_t run_mega(wick_cuda_model* m, int n_tokens, bool greedy) {
     MegaParams P = m->mega;
     P.greedy = greedy ? 1 : 0;
+    m->last_launch_long = m->long_ok && m->seq_len >= MEGA_LONG_CTX && getenv("WICK_CUDA_NO_SPLIT_SCORES") == nullptr;
+    if (m->last_launch_long) {
+        P.phases = m->d_phases_long;
+        P.n_phases = m->n_phases_long;
+        P.long_ctx = 1;
+    }
     if (!P.skip_logits) {
         P.n_tokens = n_tokens;
         P.bar_base = m->bar_base;
@@ -1262,15 +1303,16 @@ int32_t wick_cuda_decode_profile(wick_cuda_model* m, uint64_t* ns_out, int32_t* 
     W_TRY(check_model(m));
     if (!m->mega_ok) return fail(WICK_CUDA_ERR_BAD_ARG, "this model decodes through captured graphs");
     if (!n_phases) return fail(WICK_CUDA_ERR_BAD_ARG, "n_phases is NULL");
-    *n_phases = (uint32_t)m->mega.n_phases;
-    if (!ns_out || !kinds_out || capacity < (uint32_t)m->mega.n_phases) return WICK_CUDA_OK;
+    const int np = m->last_launch_long ? m->n_phases_long : m->mega.n_phases;
+    *n_phases = (uint32_t)np;
+    if (!ns_out || !kinds_out || capacity < (uint32_t)np) return WICK_CUDA_OK;
     CU_TRY(cudaSetDevice(m->device));
     CU_TRY(cudaStreamSynchronize(m->stream));
-    CU_TRY(cudaMemcpy(ns_out, m->d_prof, (size_t)m->mega.n_phases * 32, cudaMemcpyDeviceToHost));
-    if (capacity >= (uint32_t)m->mega.n_phases + 4)  // optional: the 16 internal stamps of WICK_CUDA_PROF_PHASE
-        CU_TRY(cudaMemcpy(ns_out + (size_t)m->mega.n_phases * 4, m->d_prof + (size_t)m->mega.n_phases * 4, 128, cudaMemcpyDeviceToHost));
-    std::vector<MegaPhase> ph(m->mega.n_phases);
-    CU_TRY(cudaMemcpy(ph.data(), m->d_phases, ph.size() * sizeof(MegaPhase), cudaMemcpyDeviceToHost));
+    CU_TRY(cudaMemcpy(ns_out, m->d_prof, (size_t)np * 32, cudaMemcpyDeviceToHost));
+    if (capacity >= (uint32_t)np + 4)  // optional: the 16 internal stamps of WICK_CUDA_PROF_PHASE
+        CU_TRY(cudaMemcpy(ns_out + (size_t)np * 4, m->d_prof + (size_t)np * 4, 128, cudaMemcpyDeviceToHost));
+    std::vector<MegaPhase> ph(np);
+    CU_TRY(cudaMemcpy(ph.data(), m->last_launch_long ? m->d_phases_long : m->d_phases, ph.size() * sizeof(MegaPhase), cudaMemcpyDeviceToHost));
     for (size_t i = 0; i < ph.size(); i++) kinds_out[i] = ph[i].kind;
     return WICK_CUDA_OK;
 }
