@@ -988,6 +988,16 @@ __device__ void consumer(const MegaParams& P, const Smem& S, int cta, int ncta) 
                             if (is_q4<DTK>(w.dtype)) stage_products<DT_Q4_0>(qs, dbase + (size_t)gi * nb * 4, nb, tt, xq32, S.xs16);
                             else stage_products<DT_Q8_0>(qs, dbase + (size_t)gi * nb * 4, nb, tt, xq32, S.xs);
                         }
+                        // residual-add epilogue: the old value of the row is fetched now, so that its latency runs
+                        // under the chain step instead of after it (a warp owns at most two groups of a slot)
+                        float resid[2] = {0.0f, 0.0f};
+                        if (M.epi == MEP_ADD && (c.lane & 19) == 0) {
+#pragma unroll
+                            for (int q = 0; q < 2; q++) {
+                                const int gi = tw + q * TEAM_WARPS, row = (g0 + gi) * 4 + ((c.lane >> 2) & 3);
+                                if (gi < ng && row < w.m) resid[q] = __ldcg(M.y + row);
+                            }
+                        }
                         team_sync(team);
                         if (c.stamp && nst < 4) c.stamp[nst * 4 + 2] = globaltimer_ns();
                         for (int gi = tw; gi < ng; gi += TEAM_WARPS) {
@@ -997,7 +1007,7 @@ __device__ void consumer(const MegaParams& P, const Smem& S, int cta, int ncta) 
                             const int row = (g0 + gi) * 4 + ((c.lane >> 2) & 3);
                             if ((c.lane & 19) == 0 && row < w.m) {
                                 if (M.epi == MEP_ADD) {
-                                    M.y[row] = __fadd_rn(__ldcg(M.y + row), acc);
+                                    M.y[row] = __fadd_rn(gi == tw ? resid[0] : resid[1], acc);
                                 } else if (M.epi == MEP_STORE) {
                                     M.y[row] = acc;
                                 } else {
