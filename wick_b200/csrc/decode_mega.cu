@@ -785,7 +785,7 @@ __device__ __forceinline__ void team_sync(int team) {
 // One thread takes one (block, row) of the group per step: its four lane-words are 16 contiguous
 // bytes (as are the matching input words), so weights, inputs and products move as 128-bit
 // shared-memory accesses and the scale product is formed once per four terms.
-template <int DT, int U = 2>
+template <int DT, int U = (DT == DT_Q4_0 ? 3 : 2)>
 __device__ __forceinline__ void stage_products(uint32_t* __restrict__ qs, const __half* __restrict__ ds, int nb, int tt,
                                                const int* __restrict__ xq32, const float* __restrict__ xsc) {
     const int ni = nb * 4;  // (block, row) items of the group
