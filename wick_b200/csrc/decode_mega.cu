@@ -32,7 +32,8 @@ constexpr int NCT = NC * 32;
 constexpr int TEAM_WARPS = MEGA_TEAM_WARPS;  // consumer warps work on ring slots in teams
 constexpr int NTEAMS = MEGA_TEAMS;
 constexpr int TEAM_THREADS = TEAM_WARPS * 32;
-constexpr unsigned SPIN_LIMIT = 1u << 22;  // x ~0.25-1 us of back-off per iteration
+constexpr unsigned SPIN_LIMIT = 1u << 22;  // x ~0.25-2 us per iteration
+constexpr unsigned WAIT_NS = 2000;         // hardware suspend limit of one mbarrier test
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -53,6 +54,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
         : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// The same test with a time limit: the thread is suspended in hardware until the phase completes or `ns` have
+// passed, so a waiting warp issues almost nothing and wakes as soon as the barrier flips.
+__device__ __forceinline__ bool mbar_try_wait_for(uint64_t* bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
         : "memory");
     return ok != 0;
 }
@@ -195,14 +209,13 @@ __device__ unsigned long long producer(const MegaParams& P, const Smem& S, int c
                         const uint32_t qgb = (uint32_t)w.q_group_bytes(), dgb = (uint32_t)w.d_group_bytes();
                         int ng = pl.rg < b - g0 ? pl.rg : b - g0;
                         unsigned spins = 0;
-                        while (!mbar_try_wait(&S.empty[slot], par ^ 1)) {
+                        while (!mbar_try_wait_for(&S.empty[slot], par ^ 1, WAIT_NS)) {
                             if (*S.abort) return cnt;
                             if (++spins > SPIN_LIMIT) {
                                 atomicOr(&P.ctl->error, 2u);
                                 *S.abort = 1;
                                 return cnt;
                             }
-                            __nanosleep(64);
                         }
                         uint8_t* dst = S.ring + (size_t)slot * P.slot_bytes;
                         mbar_expect_tx(&S.full[slot], ng * (qgb + dgb));
@@ -922,13 +935,12 @@ __device__ void consumer(const MegaParams& P, const Smem& S, int cta, int ncta) 
                     uint8_t* bases[2] = {S.ring + (size_t)slot_a * P.slot_bytes, S.ring + (size_t)slot_b * P.slot_bytes};
                     for (int half = 0; half < 2; half++) {
                         unsigned spins = 0;
-                        while (!*S.abort && !mbar_try_wait(&S.full[half ? slot_b : slot_a], half ? par_b : par_a)) {
+                        while (!*S.abort && !mbar_try_wait_for(&S.full[half ? slot_b : slot_a], half ? par_b : par_a, WAIT_NS)) {
                             if (++spins > SPIN_LIMIT) {
                                 atomicOr(&P.ctl->error, 4u);
                                 *S.abort = 1;
                                 break;
                             }
-                            if (spins > 32) __nanosleep(32);
                         }
                         const DevWeight& w = half ? wu : wg;
                         const __half* dbase = reinterpret_cast<const __half*>(bases[half] + (size_t)ng * qgb);
@@ -972,13 +984,12 @@ __device__ void consumer(const MegaParams& P, const Smem& S, int cta, int ncta) 
                         int ng = pl.rg < b - g0 ? pl.rg : b - g0;
                         if (c.stamp && nst < 4) c.stamp[nst * 4 + 0] = globaltimer_ns();
                         unsigned spins = 0;
-                        while (!*S.abort && !mbar_try_wait(&S.full[slot], par)) {
+                        while (!*S.abort && !mbar_try_wait_for(&S.full[slot], par, WAIT_NS)) {
                             if (++spins > SPIN_LIMIT) {
                                 atomicOr(&P.ctl->error, 4u);
                                 *S.abort = 1;
                                 break;
                             }
-                            if (spins > 32) __nanosleep(32);
                         }
                         if (c.stamp && nst < 4) c.stamp[nst * 4 + 1] = globaltimer_ns();
                         uint8_t* base = S.ring + (size_t)slot * P.slot_bytes;
