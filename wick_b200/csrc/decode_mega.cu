@@ -90,6 +90,14 @@ __device__ __forceinline__ unsigned long long ld_acquire_u64(const unsigned long
     asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
     return v;
 }
+__device__ __forceinline__ unsigned long long ld_relaxed_u64(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_relaxed_u64(unsigned long long* p, unsigned long long v) {
+    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
 __device__ __forceinline__ unsigned long long globaltimer_ns() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
@@ -260,10 +268,12 @@ __device__ void grid_wait(Ctx& c, unsigned long long target) {
     consumer_sync();
 }
 
-__device__ void grid_arrive(Ctx& c) {
+// `count` = 1 + the arrivals of the flag_out phases passed since the last one (those phases hand their rows over
+// through flagged words and skip the barrier), so the counter stays one arrival per phase and CTA.
+__device__ void grid_arrive(Ctx& c, unsigned count) {
     consumer_sync();
     if (c.ct == 0)  // release: orders the CTA's writes (made visible to this thread by the barrier) before the count
-        asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(c.P.bar_counter), "l"(1ull) : "memory");
+        asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(c.P.bar_counter), "l"((unsigned long long)count) : "memory");
 }
 
 // Phase inputs are produced block-wise: consumer warp cw owns the 32-element blocks
@@ -349,33 +359,69 @@ __device__ __forceinline__ void load_norm_w(const Ctx& c, const MegaPhase& ph, f
     }
 }
 
-__device__ void prologue_norm(Ctx& c, const MegaPhase& ph, uint32_t token, const float (&w)[MAXJ]) {
+// Identifier a flag_out phase stamps on the rows it writes: unique among the values a word of the flagged copy
+// can still hold (its previous writer ran at most a few phases earlier) and never 0, the cleared state.
+__device__ __forceinline__ uint32_t phase_id(const MegaParams& P, int t, int pi) {
+    return (uint32_t)(P.bar_base + (unsigned long long)t * P.n_phases + pi) | 0x80000000u;
+}
+
+__device__ void prologue_norm(Ctx& c, const MegaPhase& ph, uint32_t token, const float (&w)[MAXJ], uint32_t id_in) {
     const MegaParams& P = c.P;
     const int k = ph.k, nb = k / QK;
-    if (ph.conv_commit >= 0) {
-        // advance the conv rolling buffer of the layer whose gating ran one phase ago; every CTA
-        // finished reading the old buffer before the barrier that was just passed
-        const MegaLayer& L = c.S.layers[ph.conv_commit];
-        const int dc = P.conv_ks - 1, hs = P.hs;
-        int c0 = share(c.cta, hs, c.ncta), c1 = share(c.cta + 1, hs, c.ncta);
-        for (int ch = c0 + c.ct; ch < c1; ch += NCT) {
-            for (int kk = 0; kk + 1 < dc; kk++) L.conv_state[(size_t)kk * hs + ch] = __ldcg(L.conv_state + (size_t)(kk + 1) * hs + ch);
-            if (dc > 0) L.conv_state[(size_t)(dc - 1) * hs + ch] = conv_bx(P.proj, hs, ch);
-        }
+    // Conv state of the layer whose gating ran one phase ago (lfm2.rs:691-695).  The values are fetched now; the
+    // rolling buffer is overwritten further down, once every CTA is known to have finished reading the old one.
+    const MegaLayer* CL = ph.conv_commit >= 0 ? &c.S.layers[ph.conv_commit] : nullptr;
+    const int dc = P.conv_ks - 1, hs = P.hs;
+    const int cc0 = CL ? share(c.cta, hs, c.ncta) : 0, cc1 = CL ? share(c.cta + 1, hs, c.ncta) : 0;
+    float cst[3] = {0.0f, 0.0f, 0.0f};  // conv_ks <= 4
+    if (cc0 + c.ct < cc1) {
+        const int ch = cc0 + c.ct;
+#pragma unroll
+        for (int kk = 0; kk < 2; kk++)
+            if (kk + 1 < dc) cst[kk] = __ldcg(CL->conv_state + (size_t)(kk + 1) * hs + ch);
+        cst[2] = conv_bx(P.proj, hs, ch);
     }
     STAMP(c, 0);
     float v[MAXJ];
     const int e0 = ph.embed ? share(c.cta, k, c.ncta) : 0, e1 = ph.embed ? share(c.cta + 1, k, c.ncta) : 0;
+    if (ph.flag_in) {
+        // The previous phase wrote every row as (its id, value) in one 64-bit word: a word that carries the id holds
+        // the new value, so the row is consumed element by element as it arrives and no grid barrier is needed.
+        // Seeing all words also proves that every team of every CTA has finished the previous mat-vec.
 #pragma unroll
-    for (int j = 0; j < MAXJ; j++) {
-        const int b = c.cw + j * NC, e = b * QK + c.lane;
-        v[j] = 0.0f;
-        if (b < nb) {
-            if (ph.embed) {
-                v[j] = P.embd_q6k ? q6k_elem(P.embd6, token, e) : embed_elem(P.embd, token, e);
-                if (e >= e0 && e < e1) P.hidden[e] = v[j];
-            } else {
-                v[j] = __ldcg(P.hidden + e);
+        for (int j = 0; j < MAXJ; j++) v[j] = 0.0f;
+        uint32_t pending = 0;
+#pragma unroll
+        for (int j = 0; j < FASTJ; j++) pending |= (c.cw + j * NC < nb) ? 1u << j : 0u;
+        unsigned spins = 0;
+        while (pending && !*c.S.abort) {
+            unsigned long long x[FASTJ];
+#pragma unroll
+            for (int j = 0; j < FASTJ; j++)
+                if (pending >> j & 1) x[j] = ld_relaxed_u64(P.hidden_flagged + (c.cw + j * NC) * QK + c.lane);
+#pragma unroll
+            for (int j = 0; j < FASTJ; j++)
+                if ((pending >> j & 1) && (uint32_t)(x[j] >> 32) == id_in) {
+                    v[j] = __uint_as_float((uint32_t)x[j]);
+                    pending &= ~(1u << j);
+                }
+            if (pending && ++spins > SPIN_LIMIT) {
+                atomicOr(&P.ctl->error, 8u);
+                *c.S.abort = 1;
+            }
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < MAXJ; j++) {
+            const int b = c.cw + j * NC, e = b * QK + c.lane;
+            v[j] = 0.0f;
+            if (b < nb) {
+                if (ph.embed) {
+                    v[j] = P.embd_q6k ? q6k_elem(P.embd6, token, e) : embed_elem(P.embd, token, e);
+                    if (e >= e0 && e < e1) P.hidden[e] = v[j];
+                } else {
+                    v[j] = __ldcg(P.hidden + e);
+                }
             }
         }
     }
@@ -391,6 +437,22 @@ __device__ void prologue_norm(Ctx& c, const MegaPhase& ph, uint32_t token, const
     if (c.lane == 0) c.S.red[c.cw] = s;
     consumer_sync();
     STAMP(c, 2);
+    if (CL) {
+        // every CTA has passed the gating prologue that read the old buffer: either a grid barrier lies in between,
+        // or (flag_in) all rows of the mat-vec that followed that prologue have been seen by this CTA
+        for (int ch = cc0 + c.ct; ch < cc1; ch += NCT) {
+            if (ch != cc0 + c.ct) {  // rows beyond the first of this thread (hidden sizes above 480 x CTAs)
+#pragma unroll
+                for (int kk = 0; kk < 2; kk++)
+                    if (kk + 1 < dc) cst[kk] = __ldcg(CL->conv_state + (size_t)(kk + 1) * hs + ch);
+                cst[2] = conv_bx(P.proj, hs, ch);
+            }
+#pragma unroll
+            for (int kk = 0; kk < 2; kk++)
+                if (kk + 1 < dc) CL->conv_state[(size_t)kk * hs + ch] = cst[kk];
+            if (dc > 0) CL->conv_state[(size_t)(dc - 1) * hs + ch] = cst[2];
+        }
+    }
     double tot = 0.0;
     for (int i = 0; i < NC; i++) tot += c.S.red[i];
     const float inv = (float)(1.0 / sqrt(tot / (double)k + (double)P.eps));
@@ -881,15 +943,17 @@ __device__ void consumer(const MegaParams& P, const Smem& S, int cta, int ncta) 
     const int team = c.cw / TEAM_WARPS, tw = c.cw % TEAM_WARPS, tt = tw * 32 + c.lane;
     const uint32_t pos0 = __ldcg(&P.ctl->pos), step0 = __ldcg(&P.ctl->step);
     uint32_t token = __ldcg(&P.ctl->token);
+    unsigned owed = 0;  // arrivals of flag_out phases not yet added to the barrier counter
     const int* xq32 = reinterpret_cast<const int*>(S.xq);
     for (int t = 0; t < P.n_tokens; t++) {
         const int pos = (int)pos0 + t;
         unsigned long long best = 0;
         for (int pi = 0; pi < P.n_phases; pi++) {
             const MegaPhase& ph = S.ph[pi];
+            const uint32_t id_out = phase_id(P, t, pi);
             float nw[MAXJ];
             if (ph.kind == MPH_NORM) load_norm_w(c, ph, nw);
-            if (t > 0 || pi > 0) grid_wait(c, (P.bar_base + (unsigned long long)t * P.n_phases + pi) * (unsigned long long)ncta);
+            if ((t > 0 || pi > 0) && !ph.flag_in) grid_wait(c, (P.bar_base + (unsigned long long)t * P.n_phases + pi) * (unsigned long long)ncta);
             const bool prof = P.prof && cta == 0 && c.ct == 0 && t == P.n_tokens - 1;
             c.stamp = (prof && pi == P.prof_phase) ? P.prof + (size_t)P.n_phases * 4 : nullptr;
             if (prof) P.prof[pi * 4 + 0] = globaltimer_ns();
@@ -900,7 +964,7 @@ __device__ void consumer(const MegaParams& P, const Smem& S, int cta, int ncta) 
             }
             if (pi == 1 && cta == 0 && c.ct == 0) P.argmax_acc[(t + 1) & 1] = 0;  // free for the next step
             switch (ph.kind) {
-                case MPH_NORM: prologue_norm(c, ph, token, nw); break;
+                case MPH_NORM: prologue_norm(c, ph, token, nw, phase_id(P, t, pi - 1)); break;
                 case MPH_CONV: prologue_conv(c, ph); break;
                 case MPH_SILU: prologue_silu(c, ph); break;
                 case MPH_QUANT: prologue_quant(c, ph); break;
@@ -1018,7 +1082,9 @@ __device__ void consumer(const MegaParams& P, const Smem& S, int cta, int ncta) 
                             const int row = (g0 + gi) * 4 + ((c.lane >> 2) & 3);
                             if ((c.lane & 19) == 0 && row < w.m) {
                                 if (M.epi == MEP_ADD) {
-                                    M.y[row] = __fadd_rn(gi == tw ? resid[0] : resid[1], acc);
+                                    const float hv = __fadd_rn(gi == tw ? resid[0] : resid[1], acc);
+                                    M.y[row] = hv;
+                                    if (ph.flag_out) st_relaxed_u64(P.hidden_flagged + row, (unsigned long long)id_out << 32 | __float_as_uint(hv));
                                 } else if (M.epi == MEP_STORE) {
                                     M.y[row] = acc;
                                 } else {
@@ -1055,7 +1121,12 @@ __device__ void consumer(const MegaParams& P, const Smem& S, int cta, int ncta) 
                 }
             }
             if (prof) P.prof[pi * 4 + 2] = globaltimer_ns();
-            grid_arrive(c);
+            if (ph.flag_out) {
+                owed++;
+            } else {
+                grid_arrive(c, 1 + owed);
+                owed = 0;
+            }
             if (prof) P.prof[pi * 4 + 3] = globaltimer_ns();
         }
     }

@@ -44,6 +44,10 @@ struct MegaPhase {
     int conv_commit;    // MPH_NORM: layer whose conv state is advanced in this prologue, or -1
     int pair;           // 1: mat[0] / mat[1] are gate / up of equal shape, streamed as alternating stages and
                         //    combined row by row in the epilogue (MEP_SWIGLU)
+    int flag_in;        // MPH_NORM: the hidden row is taken from the flagged copy the previous phase wrote, element by
+                        //    element as it arrives; no grid barrier in front of this phase
+    int flag_out;       // MEP_ADD phase in front of a flag_in phase: rows are also written as (phase id, value) words
+                        //    and the phase does not arrive at the grid barrier (the arrival is made up at the next one)
     const float* src;   // MPH_QUANT: the vector to quantise
     const float* norm_w;
     MegaMat mat[3];
@@ -78,6 +82,7 @@ struct MegaParams {
     DecodeCtl* ctl;
     uint32_t* ring;
     int ring_len;
+    unsigned long long* hidden_flagged;  // [hs] (phase id << 32 | f32 bits) copy of the hidden row (flag_in / flag_out)
     unsigned long long* bar_counter;   // monotonically increasing arrival counter
     unsigned long long bar_base;       // barriers completed before this launch
     unsigned long long* argmax_acc;    // [2], alternating by token
@@ -92,6 +97,9 @@ struct MegaParams {
     unsigned long long* prof;          // [n_phases * 4 + 16]
     int prof_phase;                    // phase that also records up to 16 internal stamps after the table
 };
+
+// Longest hidden row a flag_in phase handles (15 consumer warps x 5 blocks x 32 elements).
+constexpr int MEGA_FLAGGED_MAX_K = 2400;
 
 size_t mega_smem_bytes(const MegaParams& P);
 // Launches the persistent kernel (cooperative: one CTA per SM, all co-resident).

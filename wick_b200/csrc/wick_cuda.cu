@@ -115,6 +115,7 @@ struct wick_cuda_model {
     bool last_launch_long = false, long_ok = false;
     MegaLayer* d_mlayers = nullptr;
     unsigned long long* d_sync = nullptr;  // [0] barrier counter, [1..2] argmax accumulators
+    unsigned long long* hidden_flagged = nullptr;  // [hs] flagged copy of the hidden row (persistent decode kernel)
     unsigned long long* d_prof = nullptr;  // [n_phases][4] timestamps of the last step
     unsigned long long bar_base = 0;
     DecodeCtl* h_ctl = nullptr;            // pinned copy of the control block
@@ -374,6 +375,12 @@ int32_t build_mega(wick_cuda_model* m) {
         for (auto& q : ph) if (q.pair) { q.pair = 0; q.mat[0].epi = q.mat[1].epi = MEP_STORE; }
     for (size_t i = 0; i + 1 < ph.size(); i++)
         if (ph[i].kind == MPH_NORM && ph[i].n_mat == 2 && !ph[i].pair && ph[i + 1].kind == MPH_QUANT && ph[i + 1].src == m->gate) ph[i + 1].kind = MPH_SILU;
+    // A residual-add phase followed by an RMSNorm phase hands the hidden row over through flagged words instead of
+    // a grid barrier (WICK_CUDA_NO_FLAGGED_HIDDEN keeps the barrier, for A/B measurements).
+    if (hs <= MEGA_FLAGGED_MAX_K && getenv("WICK_CUDA_NO_FLAGGED_HIDDEN") == nullptr)
+        for (size_t i = 0; i + 1 < ph.size(); i++)
+            if (ph[i].n_mat == 1 && ph[i].mat[0].epi == MEP_ADD && ph[i].mat[0].y == m->hidden && ph[i + 1].kind == MPH_NORM && !ph[i + 1].embed && ph[i + 1].k == hs)
+                ph[i].flag_out = ph[i + 1].flag_in = 1;
     // long-context variant of the list: the cached keys' scores are computed by a phase of their own, spread over all CTAs
     std::vector<MegaPhase> ph_long;
     for (const MegaPhase& q : ph) {
@@ -391,6 +398,8 @@ int32_t build_mega(wick_cuda_model* m) {
     W_TRY(dev_alloc(m, &m->d_phases, ph.size()));
     W_TRY(dev_alloc(m, &m->d_mlayers, ml.size()));
     W_TRY(dev_alloc(m, &m->d_sync, 4));
+    W_TRY(dev_alloc(m, &m->hidden_flagged, (size_t)hs));
+    CU_TRY(cudaMemset(m->hidden_flagged, 0, (size_t)hs * 8));
     W_TRY(dev_alloc(m, &m->d_prof, ph_long.size() * 4 + 16));
     CU_TRY(cudaMemset(m->d_prof, 0, (ph_long.size() * 4 + 16) * 8));
     P.prof = m->d_prof;
@@ -401,6 +410,7 @@ int32_t build_mega(wick_cuda_model* m) {
     P.phases = m->d_phases;
     P.layers = m->d_mlayers;
     P.bar_counter = m->d_sync;
+    P.hidden_flagged = m->hidden_flagged;
     P.argmax_acc = m->d_sync + 1;
     {   // hand the shared memory the ring leaves unused to the attention staging area
         const size_t used = mega_smem_bytes(P);  // still with the long list's phase count
@@ -475,6 +485,7 @@ int32_t check_mega_status(wick_cuda_model* m) {
         uint32_t e = m->h_ctl->error;
         // the barrier counter is no longer in step with bar_base: resynchronise and clear
         cudaMemsetAsync(m->d_sync, 0, 32, m->stream);
+        cudaMemsetAsync(m->hidden_flagged, 0, (size_t)m->cfg.hidden_size * 8, m->stream);  // phase ids restart with bar_base
         cudaMemsetAsync(&m->ctl->error, 0, 4, m->stream);
         cudaStreamSynchronize(m->stream);
         m->bar_base = 0;
