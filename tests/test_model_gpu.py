@@ -313,3 +313,33 @@ def test_split_scores_long_context_decode(wick, orc, model_dir, monkeypatch):
     monkeypatch.delenv("WICK_CUDA_NO_SPLIT_SCORES")
     ga = a.generate_greedy(first, 32, sa)
     assert list(ga) == list(gb)
+
+
+@pytest.mark.parametrize("spec,qtype", [("tiny", "q4_0"), ("tiny-wide", "q8_0")])
+def test_flagged_hidden_handover_matches_barrier_path(wick, orc, model_dir, monkeypatch, spec, qtype):
+    """RMSNorm phases take the hidden row from flagged 64-bit words instead of waiting at a grid barrier.  A model
+    created with WICK_CUDA_NO_FLAGGED_HIDDEN keeps the barriers: both must give the oracle's bits, step by step and
+    in the device-resident loop (many steps per launch, so phase ids run on across steps and launches)."""
+    from wick_b200 import gguf_synth as gs
+    path = _model_path(model_dir, spec, qtype)
+    toks = gs.random_prompt(24, gs.SPECS[spec].vocab, seed=31)
+    a = wick.CudaLfm2Model(path, 512)
+    monkeypatch.setenv("WICK_CUDA_NO_FLAGGED_HIDDEN", "1")
+    b = wick.CudaLfm2Model(path, 512)
+    monkeypatch.delenv("WICK_CUDA_NO_FLAGGED_HIDDEN")
+    om = orc.OracleModel(path, 512)
+    sa, sb = wick.InferenceState(), wick.InferenceState()
+    la, lb, lo = a.forward_prefill(toks, 0, sa), b.forward_prefill(toks, 0, sb), om.forward_prefill(toks, 0)
+    assert_logits_equal(la, lo, "prefill")
+    assert_logits_equal(lb, lo, "prefill (barriers)")
+    tok = orc.argmax(lo)
+    for i in range(6):
+        y = om.forward(tok)
+        assert_logits_equal(a.forward([tok], sa.seq_len, sa), y, f"step {i}")
+        assert_logits_equal(b.forward([tok], sb.seq_len, sb), y, f"step {i} (barriers)")
+        tok = orc.argmax(y)
+    want = list(om.generate_greedy(tok, 100))
+    assert list(a.generate_greedy(tok, 100, sa)) == want
+    assert list(b.generate_greedy(tok, 100, sb)) == want
+    # the persistent kernel is what ran (a fallback to the per-kernel graph would not exercise the hand-over)
+    assert a.decode_path() == "persistent" and b.decode_path() == "persistent"
