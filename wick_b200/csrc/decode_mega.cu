@@ -294,22 +294,15 @@ __device__ __forceinline__ void quantize_blocks(Ctx& c, const float (&v)[J], int
     constexpr int JP = J <= 4 ? 4 : (J <= 8 ? 8 : 16);
     constexpr int LOG = JP == 4 ? 2 : (JP == 8 ? 3 : 4);
     constexpr int SH = 5 - LOG;  // lanes per block after the halving rounds: 1 << SH
-    float a[JP];
+    // Block maxima: |v| >= 0, so the IEEE bit patterns order like unsigned integers and one warp-wide integer
+    // max per block (independent of one another) replaces the dependent shuffle rounds.  max is exact, so the order
+    // does not matter.  Lane L then performs the two IEEE divisions of block L >> SH only.
+    float a[1] = {0.0f};
 #pragma unroll
-    for (int j = 0; j < JP; j++) a[j] = j < J ? fabsf(v[j]) : 0.0f;
-#pragma unroll
-    for (int r = 0; r < LOG; r++) {
-        const int n = JP >> r, sft = 16 >> r;
-        const bool up = (c.lane & sft) != 0;
-#pragma unroll
-        for (int i = 0; i < n / 2; i++) {
-            const float keep = up ? a[i + n / 2] : a[i];
-            const float send = up ? a[i] : a[i + n / 2];
-            a[i] = fmaxf(keep, __shfl_xor_sync(0xffffffffu, send, sft));
-        }
+    for (int j = 0; j < J; j++) {
+        const float mx = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(fabsf(v[j]))));
+        a[0] = (c.lane >> SH) == j ? mx : a[0];
     }
-#pragma unroll
-    for (int sft = (16 >> LOG); sft > 0; sft >>= 1) a[0] = fmaxf(a[0], __shfl_xor_sync(0xffffffffu, a[0], sft));
     // this lane's block
     const int jm = c.lane >> SH;
     const float d = __fdiv_rn(a[0], 127.0f);
@@ -455,7 +448,9 @@ __device__ void prologue_norm(Ctx& c, const MegaPhase& ph, uint32_t token, const
     }
     double tot = 0.0;
     for (int i = 0; i < NC; i++) tot += c.S.red[i];
-    const float inv = (float)(1.0 / sqrt(tot / (double)k + (double)P.eps));
+    // (for a power-of-two length the division is an exact scaling, as is the multiplication by its reciprocal)
+    const double mean = (k & (k - 1)) == 0 ? tot * (1.0 / (double)k) : tot / (double)k;
+    const float inv = (float)(1.0 / sqrt(mean + (double)P.eps));
     STAMP(c, 3);
 #pragma unroll
     for (int j = 0; j < MAXJ; j++) v[j] = __fmul_rn(__fmul_rn(v[j], inv), w[j]);
