@@ -684,6 +684,15 @@ __device__ void phase_attention(Ctx& c, const MegaPhase& ph, int pos) {
         const int kvh = h / group, off = kvh * hd;
         STAMP(c, 0);
         consumer_sync();
+        {   // The V columns of the first chunk do not depend on the scores: they are fetched now with asynchronous
+            // global -> shared copies (no registers held) and land while the scores and the softmax are computed.
+            const int rows = chunk < seq ? chunk : seq;
+            for (int i = c.ct; i < rows * 4; i += NCT) {
+                const float* src = (i >> 2) < pos ? L.v_cache + (size_t)(i >> 2) * kv_dim + off + d0 + (i & 3) * 4 : P.vbuf + off + d0 + (i & 3) * 4;
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(Vs + i * 4)), "l"(src) : "memory");
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        }
         if (c.cw == 0) head_norm_rope(P.qbuf + h * hd, L.q_norm, P.eps, cosr, sinr, hd, qs, c.lane);
         if (c.cw == 1) {
             head_norm_rope(P.kbuf + off, L.k_norm, P.eps, cosr, sinr, hd, ks, c.lane);
@@ -788,9 +797,10 @@ __device__ void phase_attention(Ctx& c, const MegaPhase& ph, int pos) {
             const int rows = chunk < seq - t0 ? chunk : seq - t0;
             consumer_sync();  // scores normalised / previous chunk consumed
             if (t0 == 0) STAMP(c, 8);
-            // gather: four independent 16-byte loads in flight per thread (a load -> store pair per iteration
+            if (t0 == 0) asm volatile("cp.async.wait_group 0;" ::: "memory");  // this thread's copies of the first chunk
+            // later chunks: four independent 16-byte loads in flight per thread (a load -> store pair per iteration
             // pays one memory latency per iteration)
-            for (int idx0 = c.ct; idx0 < rows * 4; idx0 += NCT * 4) {
+            for (int idx0 = c.ct; idx0 < rows * 4 && t0 > 0; idx0 += NCT * 4) {
                 float4 g0, g1, g2, g3;
                 const int n4 = rows * 4;
                 const int i0 = idx0, i1 = idx0 + NCT, i2 = idx0 + 2 * NCT, i3 = idx0 + 3 * NCT;
