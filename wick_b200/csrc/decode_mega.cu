@@ -472,10 +472,12 @@ __device__ void prologue_conv(Ctx& c, const MegaPhase& ph) {
     const MegaLayer& L = c.S.layers[ph.layer];
     const int hs = P.hs, ks = P.conv_ks, dc = ks - 1, nb = hs / QK;
     constexpr int MAXKS = 4;  // kernel sizes up to 4 (LFM2 uses 3); larger ones take the per-kernel path
-    for (int j0 = 0; j0 * NC < nb; j0 += 4) {
-        float st[4][MAXKS - 1], pb[4], pc[4], px[4], cw[4][MAXKS];
+    // five blocks per warp and pass: hidden sizes up to 2400 are done in one pass (one memory round trip)
+    constexpr int CJ = FASTJ;
+    for (int j0 = 0; j0 * NC < nb; j0 += CJ) {
+        float st[CJ][MAXKS - 1], pb[CJ], pc[CJ], px[CJ], cw[CJ][MAXKS];
 #pragma unroll
-        for (int j = 0; j < 4; j++) {  // every load of the four blocks first
+        for (int j = 0; j < CJ; j++) {  // every load of the blocks first
             const int b = c.cw + (j0 + j) * NC;
             const int chs = (b < nb ? b : 0) * QK + c.lane;
             pb[j] = __ldcg(P.proj + chs);
@@ -486,9 +488,9 @@ __device__ void prologue_conv(Ctx& c, const MegaPhase& ph) {
 #pragma unroll
             for (int kk = 0; kk < MAXKS; kk++) cw[j][kk] = kk < ks ? __ldg(L.conv_w + chs * ks + kk) : 0.0f;
         }
-        float o[4];
+        float o[CJ];
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
+        for (int j = 0; j < CJ; j++) {
             float sum = 0.0f;
 #pragma unroll
             for (int kk = 0; kk < MAXKS - 1; kk++)
@@ -500,7 +502,7 @@ __device__ void prologue_conv(Ctx& c, const MegaPhase& ph) {
             sum = __fadd_rn(sum, __fmul_rn(bx, wl));
             o[j] = __fmul_rn(pc[j], sum);
         }
-        quantize_blocks<4>(c, o, j0, nb);
+        quantize_blocks<CJ>(c, o, j0, nb);
     }
     consumer_sync();
 }
@@ -577,6 +579,43 @@ __device__ __forceinline__ float qk_dot_row(const float* q, const float* kv, int
 __device__ void head_norm_rope(const float* src_g, const float* w, float eps, const float* cosr, const float* sinr, int hd,
                                float* dst, int lane) {
     const int half = hd / 2;
+    if (half <= 64) {
+        // heads up to 128 wide: every operand (values, norm weights, rotation table) is requested before the first
+        // use, so the whole step costs one memory round trip; the arithmetic and its order are those of the loop below
+        float a[2], b[2], wa[2], wb[2], cs[2], sn[2];
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+            const int i = lane + 32 * r, ii = i < half ? i : 0;
+            a[r] = __ldcg(src_g + ii);
+            b[r] = __ldcg(src_g + ii + half);
+            wa[r] = __ldg(w + ii);
+            wb[r] = __ldg(w + ii + half);
+            cs[r] = __ldg(cosr + ii);
+            sn[r] = __ldg(sinr + ii);
+        }
+        double ss = 0.0;
+#pragma unroll
+        for (int r = 0; r < 2; r++)
+            if (lane + 32 * r < half) {
+                ss += (double)a[r] * (double)a[r];
+                ss += (double)b[r] * (double)b[r];
+            }
+        ss = warp_sum_f64(ss);
+        const double mean = (hd & (hd - 1)) == 0 ? ss * (1.0 / (double)hd) : ss / (double)hd;  // exact scaling either way
+        const float inv = (float)(1.0 / sqrt(mean + (double)eps));
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+            const int i = lane + 32 * r;
+            if (i < half) {
+                const float x0 = __fmul_rn(__fmul_rn(a[r], inv), wa[r]);
+                const float x1 = __fmul_rn(__fmul_rn(b[r], inv), wb[r]);
+                dst[i] = __fsub_rn(__fmul_rn(x0, cs[r]), __fmul_rn(x1, sn[r]));
+                dst[i + half] = __fadd_rn(__fmul_rn(x0, sn[r]), __fmul_rn(x1, cs[r]));
+            }
+        }
+        __syncwarp();
+        return;
+    }
     double ss = 0.0;
     for (int i = lane; i < half; i += 32) {
         double a = (double)__ldcg(src_g + i), b = (double)__ldcg(src_g + i + half);
