@@ -305,8 +305,15 @@ __device__ __forceinline__ void quantize_blocks(Ctx& c, const float (&v)[J], int
     }
     // this lane's block
     const int jm = c.lane >> SH;
-    const float d = __fdiv_rn(a[0], 127.0f);
-    const float id = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+    // d = amax / 127 and id = 1 / d, both correctly rounded (simd.rs:255-323) but without the generic division
+    // routine: with r = RN(1/127), q0 = RN(a * r) and rem = RN(fma(-q0, 127, a)), fma(rem, r, q0) equals RN(a / 127)
+    // for EVERY finite a >= 0 (checked exhaustively over all 2^31 - 2^23 bit patterns on the host, subnormals
+    // included); the reciprocal intrinsic is the correctly rounded 1 / d by definition.
+    constexpr float R127 = 1.0f / 127.0f;
+    const float q0 = __fmul_rn(a[0], R127);
+    float d = __fmaf_rn(__fmaf_rn(-q0, 127.0f, a[0]), R127, q0);
+    if (!(a[0] < __int_as_float(0x7f800000))) d = __fdiv_rn(a[0], 127.0f);  // infinity / NaN: the plain division
+    const float id = d != 0.0f ? __frcp_rn(d) : 0.0f;
     {
         const int b = c.cw + (j0 + jm) * NC;
         if ((c.lane & ((1 << SH) - 1)) == 0 && jm < J && b < nb) {
@@ -356,6 +363,19 @@ __device__ __forceinline__ void load_norm_w(const Ctx& c, const MegaPhase& ph, f
 // can still hold (its previous writer ran at most a few phases earlier) and never 0, the cleared state.
 __device__ __forceinline__ uint32_t phase_id(const MegaParams& P, int t, int pi) {
     return (uint32_t)(P.bar_base + (unsigned long long)t * P.n_phases + pi) | 0x80000000u;
+}
+
+// Sum of the NC per-warp partial sums as a balanced tree (depth 4 instead of 15 dependent f64 additions).
+__device__ __forceinline__ double sum_warp_partials(const double* red) {
+    static_assert(NC <= 16, "tree of 16 leaves");
+    double t[16];
+#pragma unroll
+    for (int i = 0; i < 16; i++) t[i] = i < NC ? red[i] : 0.0;
+#pragma unroll
+    for (int w = 8; w >= 1; w >>= 1)
+#pragma unroll
+        for (int i = 0; i < w; i++) t[i] += t[i + w];
+    return t[0];
 }
 
 __device__ void prologue_norm(Ctx& c, const MegaPhase& ph, uint32_t token, const float (&w)[MAXJ], uint32_t id_in) {
@@ -446,8 +466,7 @@ __device__ void prologue_norm(Ctx& c, const MegaPhase& ph, uint32_t token, const
             if (dc > 0) CL->conv_state[(size_t)(dc - 1) * hs + ch] = cst[2];
         }
     }
-    double tot = 0.0;
-    for (int i = 0; i < NC; i++) tot += c.S.red[i];
+    const double tot = sum_warp_partials(c.S.red);
     // (for a power-of-two length the division is an exact scaling, as is the multiplication by its reciprocal)
     const double mean = (k & (k - 1)) == 0 ? tot * (1.0 / (double)k) : tot / (double)k;
     const float inv = (float)(1.0 / sqrt(mean + (double)P.eps));
@@ -825,8 +844,7 @@ __device__ void phase_attention(Ctx& c, const MegaPhase& ph, int pos) {
         sum = warp_sum_f64(sum);
         if (c.lane == 0) c.S.red[c.cw] = sum;
         consumer_sync();
-        double tot = 0.0;
-        for (int i = 0; i < NC; i++) tot += c.S.red[i];
+        const double tot = sum_warp_partials(c.S.red);
         const float inv = (float)(1.0 / tot);
         for (int t = c.ct; t < seq; t += NCT) sc[t] = __fmul_rn(sc[t], inv);
         STAMP(c, 5);
