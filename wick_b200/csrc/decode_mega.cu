@@ -439,11 +439,21 @@ __device__ void prologue_norm(Ctx& c, const MegaPhase& ph, uint32_t token, const
         }
     }
     // cpu::rmsnorm (cpu.rs:577-594); f64 partial sums combined in a fixed order
+    // (rows of up to FASTJ blocks per warp skip the other blocks' terms: they would add +0.0, which changes nothing,
+    // but the additions are dependent f64 operations on the critical path)
+    const bool short_row = nb <= FASTJ * NC;
     double s = 0.0;
 #pragma unroll
-    for (int j = 0; j < MAXJ; j++) {
+    for (int j = 0; j < FASTJ; j++) {
         double x = (double)v[j];
         s += x * x;  // absent blocks add +0.0
+    }
+    if (!short_row) {
+#pragma unroll
+        for (int j = FASTJ; j < MAXJ; j++) {
+            double x = (double)v[j];
+            s += x * x;
+        }
     }
     STAMP(c, 1);
     s = warp_sum_f64(s);
@@ -471,14 +481,14 @@ __device__ void prologue_norm(Ctx& c, const MegaPhase& ph, uint32_t token, const
     const double mean = (k & (k - 1)) == 0 ? tot * (1.0 / (double)k) : tot / (double)k;
     const float inv = (float)(1.0 / sqrt(mean + (double)P.eps));
     STAMP(c, 3);
-#pragma unroll
-    for (int j = 0; j < MAXJ; j++) v[j] = __fmul_rn(__fmul_rn(v[j], inv), w[j]);
-    if (nb <= FASTJ * NC) {
+    if (short_row) {
         float vf[FASTJ];  // (a cast to a sub-array would force v into local memory)
 #pragma unroll
-        for (int j = 0; j < FASTJ; j++) vf[j] = v[j];
+        for (int j = 0; j < FASTJ; j++) vf[j] = __fmul_rn(__fmul_rn(v[j], inv), w[j]);
         quantize_blocks<FASTJ>(c, vf, 0, nb);
     } else {
+#pragma unroll
+        for (int j = 0; j < MAXJ; j++) v[j] = __fmul_rn(__fmul_rn(v[j], inv), w[j]);
         quantize_blocks<MAXJ>(c, v, 0, nb);
     }
     STAMP(c, 4);
