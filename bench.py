@@ -43,7 +43,7 @@ FALLBACK_HBM_GBS = 6650.0
 
 # dram__bytes_read.sum + dram__bytes_write.sum per decoded token from an ncu capture of the decode
 # kernels (profiles/), keyed by (model, qtype); None until captured.
-NCU_TRAFFIC_BYTES_PER_TOKEN = {("lfm2.5-1.6b", "q4_0"): 589.0e6}
+NCU_TRAFFIC_BYTES_PER_TOKEN = {("lfm2.5-1.6b", "q4_0"): 588.7e6}
 
 
 def measured_peak():
