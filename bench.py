@@ -13,7 +13,7 @@ then 128 greedy decode tokens are generated (tg128, positions 128..255) and time
           one wick_cuda_forward_greedy per token: the token id goes host->device from
           pinned memory and the chosen id comes back device->host every step; host wall clock.
   roofline  algorithmic weight bytes per token / device time per token, against the measured
-          HBM copy bandwidth of this pool's B200s.
+          HBM copy bandwidth (MEASURED_PEAKS.json, else a fallback constant).
 
 `--impl reference` times the CPU oracle (the restatement of wick's own CPU path; wick is Rust and
 cannot be built here) on the host cores for the same workload, on a bounded sample.
@@ -42,7 +42,7 @@ DECODE_TOKENS = 128
 FALLBACK_HBM_GBS = 6650.0
 
 # dram__bytes_read.sum + dram__bytes_write.sum per decoded token from an ncu capture of the decode
-# kernels (profiles/), keyed by (model, qtype); None until captured.
+# kernels, keyed by (model, qtype); None until captured.
 NCU_TRAFFIC_BYTES_PER_TOKEN = {("lfm2.5-1.6b", "q4_0"): 588.7e6}
 
 

@@ -271,14 +271,17 @@ int32_t wick_cuda_argmax(const float* logits_dev, uint32_t count, uint32_t* out_
 
 /* ---- allocation-free variant ------------------------------------------------
  * No counterpart in wick: this entry point exists for callers of this library that are not allowed
- * to allocate (a host callback, a real-time thread, a process that has given its whole memory pool
- * away).  Same result as wick_cuda_argmax(), but the scratch it needs lives in a fixed 32 KB array
- * inside the library (held by every GPU that loads it, until the process exits) and no allocation
- * routine is called.  At most WICK_CUDA_ARGMAX_NOALLOC_MAX logits; more is WICK_CUDA_ERR_BAD_ARG
- * (message from wick_cuda_argmax_noalloc_last_error()).  The first call on each device looks up the
- * array's device address, so make that first call outside any stream capture.  All calls share the
- * one array: two calls whose kernels can overlap on the GPU (different streams) race; calls on one
- * stream are safe, and nothing needs to be cleared between calls. */
+ * to allocate (a real-time audio or serving thread, a process that has given its whole device memory
+ * pool away).  Same result as wick_cuda_argmax(), but the scratch it needs lives in a fixed 32 KB array
+ * inside the library (held by every GPU that loads it, until the process exits); no CUDA allocation
+ * routine is called and the host heap is not used either (error messages are formatted into a fixed
+ * per-thread buffer).  At most WICK_CUDA_ARGMAX_NOALLOC_MAX logits; more is WICK_CUDA_ERR_BAD_ARG
+ * (message from wick_cuda_argmax_noalloc_last_error()).  Every call takes a short process-wide mutex;
+ * the FIRST call on each device additionally looks up the array's device address, which may load the
+ * library's module onto that device: make that first call a warm-up, outside real-time sections and
+ * outside any stream capture.  It must not be called from a cudaLaunchHostFunc callback (no CUDA API
+ * call may).  All calls share the one array: two calls whose kernels can overlap on the GPU (different
+ * streams) race; calls on one stream are safe, and nothing needs to be cleared between calls. */
 #define WICK_CUDA_ARGMAX_NOALLOC_MAX (4096 * 1024)
 int32_t wick_cuda_argmax_noalloc(const float* logits_dev, uint32_t count, uint32_t* out_dev, void* stream);
 const char* wick_cuda_argmax_noalloc_last_error(void);

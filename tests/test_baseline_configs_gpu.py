@@ -94,6 +94,86 @@ def test_config2_1p6b_q4_0_prefill_and_decode(wick, orc, model_dir):
     assert list(cm.generate_greedy(first, 64, st)) == list(om.generate_greedy(first, 64))
 
 
+def test_config1_350m_q8_0_full_size_vs_oracle(wick, orc, model_dir):
+    """350M-class Q8_0 at the stated size against the oracle itself: a 4096-token prompt in 512-token chunks
+    (tiled-attention chunks at start_pos 0, 512, ..., 3584) gives bit-equal logits, and the 512 greedy tokens
+    that follow (decode against 4096..4607 cached keys, the split-scores phase list) are identical."""
+    from wick_b200 import gguf_synth as gs
+    path = _path(model_dir, "lfm2-350m", "q8_0")
+    cm, om = wick.CudaLfm2Model(path, 4608), orc.OracleModel(path, 4608)
+    st = wick.InferenceState()
+    toks = gs.random_prompt(4096, cm.config().vocab_size, seed=3)
+    _, lg = cm.forward_prefill_chunked(toks, 0, st, 512)
+    lo = om.forward_prefill_chunked(toks, 0, 512)
+    assert float(np.abs(lg - lo).max()) <= 1e-2
+    assert np.array_equal(bits(lg), bits(lo))
+    first = orc.argmax(lo)
+    got, want = cm.generate_greedy(first, 512, st), om.generate_greedy(first, 512)
+    assert list(got[:64]) == list(want[:64])
+    assert list(got) == list(want)
+    assert st.seq_len == 4096 + 512
+
+
+@pytest.mark.parametrize("n_prompt", [1024, 4096])
+def test_config2_1p6b_q4_0_long_prefill_vs_oracle(wick, orc, model_dir, n_prompt):
+    """1.6B-class Q4_0 prefill at 1024 and 4096 tokens (512-token chunks, as a wick Session submits them):
+    logits bit-equal to the oracle, then 16 greedy tokens at that context identical."""
+    from wick_b200 import gguf_synth as gs
+    path = _path(model_dir, "lfm2.5-1.6b", "q4_0")
+    cm, om = wick.CudaLfm2Model(path, 4352), orc.OracleModel(path, 4352)
+    st = wick.InferenceState()
+    toks = gs.random_prompt(n_prompt, cm.config().vocab_size, seed=4)
+    _, lg = cm.forward_prefill_chunked(toks, 0, st, 512)
+    lo = om.forward_prefill_chunked(toks, 0, 512)
+    assert float(np.abs(lg - lo).max()) <= 1e-2
+    assert np.array_equal(bits(lg), bits(lo))
+    first = orc.argmax(lo)
+    assert list(cm.generate_greedy(first, 16, st)) == list(om.generate_greedy(first, 16))
+
+
+def test_config2_1p6b_q4_0_tg512_vs_oracle(wick, orc, model_dir):
+    """1.6B-class Q4_0 decode tg512 primed with a 128-token prompt: all 512 greedy tokens equal the oracle's."""
+    from wick_b200 import gguf_synth as gs
+    path = _path(model_dir, "lfm2.5-1.6b", "q4_0")
+    cm, om = wick.CudaLfm2Model(path, 4096), orc.OracleModel(path, 4096)
+    st = wick.InferenceState()
+    toks = gs.random_prompt(128, cm.config().vocab_size, seed=1)
+    lg, lo = cm.forward_prefill(toks, 0, st), om.forward_prefill(toks, 0)
+    assert np.array_equal(bits(lg), bits(lo))
+    first = orc.argmax(lo)
+    got, want = cm.generate_greedy(first, 512, st), om.generate_greedy(first, 512)
+    assert list(got[:64]) == list(want[:64])
+    assert list(got) == list(want)
+
+
+@pytest.mark.parametrize("qtype", ["q4_0", "q8_0"])
+def test_config3_matmul_sweep_n4096_full_shape(wick, orc, cuda_lib, qtype):
+    """The isolated matmul sweep at its largest point, m = 6912, k = 2048, n = 4096, through the default
+    (tensor-core, bit-exact) GEMM: every output equals the CUDA-core integer GEMM, eight sampled tokens equal
+    the oracle's mat-vec bit for bit (contract: relative 1e-5), and their int32 block sums are equal."""
+    from wick_b200 import gguf_synth as gs, ops
+    m, k, n = 6912, 2048, 4096
+    rng = np.random.default_rng(33)
+    wf = rng.standard_normal((m, k), dtype=F32) * F32(0.02)
+    raw = (gs.quantize_q4_0(wf) if qtype == "q4_0" else gs.quantize_q8_0(wf)).reshape(-1)
+    dt = orc.QTYPE_ID[qtype]
+    x = rng.standard_normal((n, k), dtype=F32)
+    w = ops.QuantWeight(dt, raw, m, k)
+    bs, bq = ops.quantize_f32_to_q8_0(torch.from_numpy(x).cuda())
+    out = ops.gemm_q8_tc_exact(w, bs, bq)
+    assert torch.equal(out.view(torch.int32), ops.gemm_q8(w, bs, bq).view(torch.int32))
+    bs_h, bq_h = bs.cpu().numpy(), bq.cpu().numpy()
+    so, qo = orc.quantize_q8_0(x[:4])
+    assert np.array_equal(bq_h[:4], qo) and np.array_equal(bits(bs_h[:4]), bits(so))
+    for j in (0, 1, 511, 512, 1777, 2048, 3333, 4095):
+        ref = orc.gemv(dt, raw, bs_h[j], bq_h[j], m, k)
+        got = out[j].cpu().numpy()
+        assert float(np.abs(got - ref).max()) <= 1e-5 * float(np.abs(ref).max())
+        assert np.array_equal(bits(got), bits(ref)), f"token {j}"
+        S = ops.block_sums(w, bq[j]).cpu().numpy()
+        assert np.array_equal(S, orc.block_sums(dt, raw, bq_h[j], m, k)[0]), f"block sums of token {j}"
+
+
 def test_config4_many_sequences_one_model(wick, orc, model_dir):
     """Sequence-sharded serving: a rank decodes its sequences one after another on one model instance;
     every sequence equals the oracle's run of the same sequence, whatever ran before it."""

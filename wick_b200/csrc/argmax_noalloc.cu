@@ -1,14 +1,19 @@
 // Argmax over device logits for callers that must not allocate.
 //
 // wick_cuda_argmax() borrows a few bytes of scratch from the stream-ordered allocator on
-// every call.  Some callers cannot do that: code running inside a host callback or a real-time
-// audio / serving thread where the CUDA allocator (and the locks and possible device
-// synchronisation behind it) is off limits, or a process whose memory pool has been handed over
-// completely to another component.  For them this file keeps the scratch in a fixed array that
-// is part of the library image: it exists once per GPU that loads the library, for as long as
-// the process lives, and no allocation call of any kind is made here.
+// every call.  Some callers cannot do that: a real-time audio / serving thread where the CUDA
+// allocator (and the locks and possible device synchronisation behind it) is off limits, or a
+// process whose device memory pool has been handed over completely to another component.  For
+// them this file keeps the scratch in a fixed array that is part of the library image: it exists
+// once per GPU that loads the library, for as long as the process lives, and neither a CUDA
+// allocation routine nor the host heap is used here (error messages go into a fixed per-thread
+// buffer).  What the entry point still does on its FIRST call per device: it takes a process-wide
+// mutex and asks the runtime for the array's device address, which may load the module onto that
+// device.  Make that call once per device as a warm-up, outside real-time sections and outside
+// stream capture; later calls on that device only read the cached address under the same mutex.
+// (It cannot be called from inside a cudaLaunchHostFunc callback: no CUDA API call can.)
+#include <cstdio>
 #include <mutex>
-#include <string>
 
 #include "../../include/wick_cuda.h"
 #include "common.cuh"
@@ -71,27 +76,31 @@ constexpr int NA_MAX_DEVICES = 64;
 std::mutex g_na_mutex;
 unsigned long long* g_na_ptr[NA_MAX_DEVICES] = {};
 
-thread_local std::string g_na_error;
+thread_local char g_na_error[192] = "";
+
+int32_t na_fail(int32_t code, const char* what, const char* detail) {
+    snprintf(g_na_error, sizeof(g_na_error), "argmax_noalloc: %s%s%s", what, detail ? ": " : "", detail ? detail : "");
+    return code;
+}
 
 }  // namespace
 
-extern "C" const char* wick_cuda_argmax_noalloc_last_error(void) { return g_na_error.c_str(); }
+extern "C" const char* wick_cuda_argmax_noalloc_last_error(void) { return g_na_error; }
 
 extern "C" int32_t wick_cuda_argmax_noalloc(const float* logits_dev, uint32_t count, uint32_t* out_dev, void* stream) {
-    if (!logits_dev || !out_dev || count == 0) {
-        g_na_error = "argmax_noalloc: NULL argument or empty input";
-        return WICK_CUDA_ERR_BAD_ARG;
-    }
+    if (!logits_dev || !out_dev || count == 0) return na_fail(WICK_CUDA_ERR_BAD_ARG, "NULL argument or empty input", nullptr);
     if (count > (uint32_t)WICK_CUDA_ARGMAX_NOALLOC_MAX) {
-        g_na_error = "argmax_noalloc: " + std::to_string(count) + " logits exceed the fixed scratch (maximum " +
-                     std::to_string(WICK_CUDA_ARGMAX_NOALLOC_MAX) + "); use wick_cuda_argmax";
+        snprintf(g_na_error, sizeof(g_na_error), "argmax_noalloc: %u logits exceed the fixed scratch (maximum %d); use wick_cuda_argmax",
+                 count, (int)WICK_CUDA_ARGMAX_NOALLOC_MAX);
         return WICK_CUDA_ERR_BAD_ARG;
     }
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
-    if (e != cudaSuccess || dev < 0 || dev >= NA_MAX_DEVICES) {
-        g_na_error = std::string("argmax_noalloc: cudaGetDevice: ") + cudaGetErrorString(e);
-        return WICK_CUDA_ERR_CUDA;
+    if (e != cudaSuccess) return na_fail(WICK_CUDA_ERR_CUDA, "cudaGetDevice", cudaGetErrorString(e));
+    if (dev < 0 || dev >= NA_MAX_DEVICES) {
+        snprintf(g_na_error, sizeof(g_na_error), "argmax_noalloc: device ordinal %d is beyond the %d devices this entry point keeps an address for",
+                 dev, NA_MAX_DEVICES);
+        return WICK_CUDA_ERR_BAD_ARG;
     }
     unsigned long long* scratch;
     {
@@ -99,10 +108,7 @@ extern "C" int32_t wick_cuda_argmax_noalloc(const float* logits_dev, uint32_t co
         if (!g_na_ptr[dev]) {  // first call on this device: resolve the symbol's device address
             void* p = nullptr;
             e = cudaGetSymbolAddress(&p, g_noalloc_partials);
-            if (e != cudaSuccess || !p) {
-                g_na_error = std::string("argmax_noalloc: cudaGetSymbolAddress: ") + cudaGetErrorString(e);
-                return WICK_CUDA_ERR_CUDA;
-            }
+            if (e != cudaSuccess || !p) return na_fail(WICK_CUDA_ERR_CUDA, "cudaGetSymbolAddress", cudaGetErrorString(e));
             g_na_ptr[dev] = (unsigned long long*)p;
         }
         scratch = g_na_ptr[dev];
@@ -113,9 +119,6 @@ extern "C" int32_t wick_cuda_argmax_noalloc(const float* logits_dev, uint32_t co
     k_argmax_na_pass1<<<nblk, 256, 0, st>>>(logits_dev, (int)count, scratch);
     k_argmax_na_pass2<<<1, 256, 0, st>>>(scratch, nblk, out_dev);
     e = cudaGetLastError();
-    if (e != cudaSuccess) {
-        g_na_error = std::string("argmax_noalloc: launch: ") + cudaGetErrorString(e);
-        return WICK_CUDA_ERR_CUDA;
-    }
+    if (e != cudaSuccess) return na_fail(WICK_CUDA_ERR_CUDA, "launch", cudaGetErrorString(e));
     return WICK_CUDA_OK;
 }

@@ -112,15 +112,31 @@ __global__ void __launch_bounds__(NAIVE_THREADS) k_attention_naive(const float* 
     }
 }
 
-void configure_naive_attention_smem(size_t bytes) {
-    cudaFuncSetAttribute(k_attention_naive, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+// The opt-in limit is a property of the kernel on a device, shared by every model and operator call: it is only
+// ever raised (a second model with a shorter context, or an operator call with a shorter sequence, must not
+// lower the limit under a model that still launches with its own, larger size).
+static cudaError_t raise_naive_attention_smem(size_t bytes) {
+    constexpr int MAX_DEV = 64;
+    static size_t granted[MAX_DEV] = {};  // written under the callers' own serialisation (one handle = one thread at a time);
+                                          // a lost update only repeats an idempotent cudaFuncSetAttribute
+    if (bytes <= 48 * 1024) return cudaSuccess;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev >= 0 && dev < MAX_DEV && granted[dev] >= bytes) return cudaSuccess;
+    e = cudaFuncSetAttribute(k_attention_naive, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e == cudaSuccess && dev >= 0 && dev < MAX_DEV) granted[dev] = bytes;
+    return e;
 }
+
+void configure_naive_attention_smem(size_t bytes) { raise_naive_attention_smem(bytes); }
 
 void launch_attention_naive(cudaStream_t st, const float* q, const float* k_cache, const float* v_cache, float* out,
                             int n, int start_pos, const DecodeCtl* ctl, int n_heads, int n_kv_heads, int head_dim,
                             int max_seq) {
     dim3 grid(n_heads, n);
     size_t smem = (size_t)(head_dim + max_seq) * sizeof(float);
+    raise_naive_attention_smem(smem);  // no-op once granted; a failure surfaces as the launch error
     g_kernel_launches++;
     k_attention_naive<<<grid, NAIVE_THREADS, smem, st>>>(q, k_cache, v_cache, out, start_pos, ctl, n_heads, n_kv_heads,
                                                         head_dim);
