@@ -269,6 +269,37 @@ int32_t wick_cuda_shortconv(const float* proj_dev, const float* conv_w_dev, floa
 /* cpu_argmax (sampler.rs:8-19) of `count` logits -> *out_dev. */
 int32_t wick_cuda_argmax(const float* logits_dev, uint32_t count, uint32_t* out_dev, void* stream);
 
+/* ---- many sequences on one model (extension) --------------------------------
+ * wick's Model trait keeps ONE sequence per model instance, serialised behind `infer_lock`
+ * (wick/src/model/mod.rs:56-71; the GPU backends keep that sequence's state inside the model,
+ * metal_lfm2.rs:2146-2147), so these entry points are not reachable from the trait: they are for a
+ * serving loop that decodes many independent sequences from one copy of the weights.  A slot holds one
+ * more sequence's state (K / V caches, rolling conv buffers, length); the model's own sequence, the one
+ * every entry point above uses, is not a slot and is left untouched.
+ *
+ * wick_cuda_decode_batch advances `bs` different slots by one token each in ONE pass over the weights:
+ * row j feeds tokens_host[j] to slot seq_ids_host[j] at that slot's own position and returns its greedy
+ * choice (cpu_argmax, sampler.rs:8-19) in next_tokens_host[j].  The mat-vecs of the step run as the batched
+ * integer GEMMs of the prefill path, which are bit-identical to the mat-vec per row (simd.rs:1440-1623), so every
+ * row's result equals the same sequence decoded alone through wick_cuda_forward_greedy.  A slot may appear at
+ * most once per batch (BAD_ARG); CONTEXT_FULL when a slot has no room left.
+ * wick_cuda_decode_batch_steps keeps n_steps such steps on the device (row j's token of step s comes back in
+ * out_tokens_host[s * bs + j]); wick_cuda_decode_batch_logits is the one-step form of wick_cuda_forward:
+ * logits_host[j * vocab ..] instead of the argmax.  wick_cuda_seq_prefill is wick_cuda_forward_prefill on a
+ * slot (same chunk rule, start_pos == 0 starts the slot's sequence anew). */
+int32_t wick_cuda_seq_create(wick_cuda_model* m, uint32_t* seq_id);
+int32_t wick_cuda_seq_destroy(wick_cuda_model* m, uint32_t seq_id);
+int32_t wick_cuda_seq_length(const wick_cuda_model* m, uint32_t seq_id, uint32_t* out);
+int32_t wick_cuda_seq_prefill(wick_cuda_model* m, uint32_t seq_id, const uint32_t* tokens_host, uint32_t n,
+                              uint32_t start_pos, float* logits_host);
+int32_t wick_cuda_decode_batch(wick_cuda_model* m, const uint32_t* tokens_host, const uint32_t* seq_ids_host,
+                               uint32_t bs, uint32_t* next_tokens_host);
+int32_t wick_cuda_decode_batch_steps(wick_cuda_model* m, const uint32_t* first_tokens_host,
+                                     const uint32_t* seq_ids_host, uint32_t bs, uint32_t n_steps,
+                                     uint32_t* out_tokens_host);
+int32_t wick_cuda_decode_batch_logits(wick_cuda_model* m, const uint32_t* tokens_host, const uint32_t* seq_ids_host,
+                                      uint32_t bs, float* logits_host);
+
 /* ---- allocation-free variant ------------------------------------------------
  * No counterpart in wick: this entry point exists for callers of this library that are not allowed
  * to allocate (a real-time audio or serving thread, a process that has given its whole device memory

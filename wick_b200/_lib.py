@@ -69,6 +69,13 @@ SIGNATURES = {
     "wick_cuda_decode_path": [_vp, C.POINTER(_i32)],
     "wick_cuda_read_kv": [_vp, _u32, _vp, _vp],
     "wick_cuda_read_conv_state": [_vp, _u32, _vp],
+    "wick_cuda_seq_create": [_vp, C.POINTER(_u32)],
+    "wick_cuda_seq_destroy": [_vp, _u32],
+    "wick_cuda_seq_length": [_vp, _u32, C.POINTER(_u32)],
+    "wick_cuda_seq_prefill": [_vp, _u32, _vp, _u32, _u32, _vp],
+    "wick_cuda_decode_batch": [_vp, _vp, _vp, _u32, _vp],
+    "wick_cuda_decode_batch_steps": [_vp, _vp, _vp, _u32, _u32, _vp],
+    "wick_cuda_decode_batch_logits": [_vp, _vp, _vp, _u32, _vp],
     "wick_cuda_weight_create": [_i32, _vp, _u32, _u32, C.POINTER(_vp)],
     "wick_cuda_quantize_q8_0": [_vp, _u32, _u32, _vp, _vp, _vp],
     "wick_cuda_gemv_q8": [_vp, _vp, _vp, _vp, _vp],

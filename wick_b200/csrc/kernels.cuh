@@ -91,6 +91,18 @@ void launch_gemv(cudaStream_t st, const GemvJob& job, const float* xs, const int
 void launch_gemm(cudaStream_t st, const DevWeight& w, const float* bs, const int8_t* bq, int n, float* out);
 void launch_block_sums(cudaStream_t st, const DevWeight& w, const int8_t* xq, int32_t* S);
 
+// Multi-sequence decode step (kernels_batch.cu): row j of n is the next token of its own sequence, with its own
+// position and state.  `states`, `k_caches`, `v_caches` are device arrays of n per-row pointers.
+void launch_shortconv_rows(cudaStream_t st, const float* proj, const float* conv_w, float* const* states, int n, int hs, int ks,
+                           float* q8s, int8_t* q8q);
+void launch_qknorm_rope_kv_rows(cudaStream_t st, float* q, const float* k, const float* v, const float* q_norm, const float* k_norm,
+                                float eps, const float* rope_cos, const float* rope_sin, float* const* k_caches, float* const* v_caches,
+                                const uint32_t* positions, int n, int n_heads, int n_kv_heads, int head_dim);
+cudaError_t launch_attention_rows(cudaStream_t st, const float* q, float* const* k_caches, float* const* v_caches, const uint32_t* positions,
+                                  float* out, int n, int n_heads, int n_kv_heads, int head_dim, int max_seq);
+void launch_argmax_rows(cudaStream_t st, const float* logits, int n, int count, uint32_t* out);
+void launch_rows_advance(cudaStream_t st, uint32_t* tokens, const uint32_t* next, uint32_t* positions, uint32_t* out_table, int n, int step);
+
 // cpu_argmax (sampler.rs:8-19).  Uses ctl->argmax as scratch when ctl != NULL, else `scratch`.
 void launch_argmax(cudaStream_t st, const float* logits, int count, unsigned long long* scratch, uint32_t* out);
 // End of a decode step on the device: token <- argmax, pos += 1, ring[step++] = token.

@@ -122,6 +122,20 @@ struct wick_cuda_model {
     uint32_t seq_len = 0;
     uint64_t bytes = 0;
     std::vector<void*> allocs;
+    // extra sequence slots for wick_cuda_decode_batch (the model's own sequence is not one of them)
+    struct SeqSlot {
+        bool live = false;
+        uint32_t seq_len = 0;
+        std::vector<float*> k_cache, v_cache, conv_state;  // per layer (NULL where the layer has none)
+    };
+    std::vector<SeqSlot> seqs;
+    int batch_cap = 0;                  // rows the batch buffers below hold
+    float* logits_rows = nullptr;       // [batch_cap][vocab]
+    uint32_t *rows_tok = nullptr, *rows_next = nullptr, *rows_pos = nullptr, *rows_out = nullptr;  // device; rows_out [steps][rows]
+    size_t rows_out_cap = 0;
+    float** rows_ptrs = nullptr;        // device [n_layers][2][batch_cap] per-row state pointers
+    uint8_t* h_rows = nullptr;          // pinned staging for tokens, positions, pointers and results
+    size_t h_rows_bytes = 0;
 
     ~wick_cuda_model() {
         cudaSetDevice(device);
@@ -134,6 +148,7 @@ struct wick_cuda_model {
         if (h_u32) cudaFreeHost(h_u32);
         if (h_logits) cudaFreeHost(h_logits);
         if (h_ctl) cudaFreeHost(h_ctl);
+        if (h_rows) cudaFreeHost(h_rows);
         if (stream) cudaStreamDestroy(stream);
     }
 };
@@ -584,6 +599,40 @@ int32_t capture_graph(wick_cuda_model* m, bool greedy, cudaGraphExec_t* out, uin
     return WICK_CUDA_OK;
 }
 
+// Integer GEMMs of n quantised rows (m->q8q / m->q8s) with up to three matrices that read the same input, as one
+// launch on the tensor cores when the chunk is wide enough to fill an MMA tile, else the exact CUDA-core kernel.
+struct GemmTarget {
+    const DevWeight* w;
+    const TcWeight* t;
+    float* out;
+};
+void run_gemms(wick_cuda_model* m, int n, std::initializer_list<GemmTarget> list) {
+    cudaStream_t st = m->stream;
+    const int hs = m->cfg.hidden_size;
+    const bool tc = m->tc_ok && n >= 16 && m->prefill_mode != WICK_CUDA_PREFILL_EXACT_CUDA_CORES;
+    const bool tc_exact = tc && m->prefill_mode == WICK_CUDA_PREFILL_EXACT;
+    if (tc) {
+        const TcWeight* tw[3];
+        float* outs[3];
+        int c = 0;
+        for (const GemmTarget& g : list) {
+            tw[c] = g.t;
+            outs[c++] = g.out;
+        }
+        const bool is_hs = tw[0]->k == hs;
+        cudaError_t e;
+        if (tc_exact) {
+            launch_tc_mask_expand(st, m->q8q, n, tw[0]->k, m->q8m);
+            e = launch_gemm_tc_exact(st, tw, outs, c, is_hs ? m->map_xm_hs : m->map_xm_is, m->q8s, n, m->tc_err);
+        } else {
+            e = launch_gemm_tc(st, tw, outs, c, is_hs ? m->map_x_hs : m->map_x_is, m->q8s, n, nullptr, m->tc_err);
+        }
+        (void)e;  // surfaced by the cudaGetLastError() check after the chunk
+    } else {
+        for (const GemmTarget& g : list) launch_gemm(st, *g.w, m->q8s, m->q8q, n, g.out);
+    }
+}
+
 // One internal prefill chunk of n <= max_chunk tokens already in m->tokens_dev
 // (prefill_layers_and_logits, lfm2.rs:1139-2213, aarch64 non-BLAS branch).
 // `embed`: fill hidden from the token ids (false: the caller has copied input embeddings into m->hidden).
@@ -594,37 +643,7 @@ void enqueue_prefill_chunk(wick_cuda_model* m, int n, int start_pos, bool flash,
     cudaStream_t st = m->stream;
     const int hs = m->cfg.hidden_size, is = m->cfg.intermediate_size, hd = m->head_dim;
     const float eps = m->cfg.rms_norm_eps;
-    // tensor-core path for chunks wide enough to fill an MMA tile; the exact kernel otherwise.
-    // Up to three matrices that read the same quantised input go out as one launch.
-    const bool tc = m->tc_ok && n >= 16 && m->prefill_mode != WICK_CUDA_PREFILL_EXACT_CUDA_CORES;
-    const bool tc_exact = tc && m->prefill_mode == WICK_CUDA_PREFILL_EXACT;
-    struct G {
-        const DevWeight* w;
-        const TcWeight* t;
-        float* out;
-    };
-    auto gemms = [&](std::initializer_list<G> list) {
-        if (tc) {
-            const TcWeight* tw[3];
-            float* outs[3];
-            int c = 0;
-            for (const G& g : list) {
-                tw[c] = g.t;
-                outs[c++] = g.out;
-            }
-            const bool is_hs = tw[0]->k == hs;
-            cudaError_t e;
-            if (tc_exact) {
-                launch_tc_mask_expand(st, m->q8q, n, tw[0]->k, m->q8m);
-                e = launch_gemm_tc_exact(st, tw, outs, c, is_hs ? m->map_xm_hs : m->map_xm_is, m->q8s, n, m->tc_err);
-            } else {
-                e = launch_gemm_tc(st, tw, outs, c, is_hs ? m->map_x_hs : m->map_x_is, m->q8s, n, nullptr, m->tc_err);
-            }
-            (void)e;  // surfaced by the cudaGetLastError() check after the chunk
-        } else {
-            for (const G& g : list) launch_gemm(st, *g.w, m->q8s, m->q8q, n, g.out);
-        }
-    };
+    auto gemms = [&](std::initializer_list<GemmTarget> list) { run_gemms(m, n, list); };
     if (embed) embed_rows(m, m->tokens_dev, nullptr, n);
     const float* pending = nullptr;
     for (size_t li = 0; li < m->layers.size(); li++) {
@@ -874,6 +893,186 @@ int32_t build_model(wick_cuda_model* m, const GgufImage& g, uint32_t context_siz
 
 int32_t check_model(const wick_cuda_model* m) {
     if (!m) return fail(WICK_CUDA_ERR_BAD_ARG, "model handle is NULL");
+    return WICK_CUDA_OK;
+}
+
+// ── sequence slots and the multi-sequence decode step ──────────────────────
+// wick keeps one sequence per model (wick/src/model/mod.rs:56-71).  A slot is one more sequence's state (K / V caches,
+// rolling conv buffers, length) on the same weights; wick_cuda_decode_batch advances many slots in one pass over the
+// weights.  The model's own sequence (the one the Model-trait entry points use) is not a slot.
+int32_t check_seq(const wick_cuda_model* m, uint32_t id) {
+    if (id >= m->seqs.size() || !m->seqs[id].live) return fail(WICK_CUDA_ERR_BAD_ARG, "no such sequence slot: " + std::to_string(id));
+    return WICK_CUDA_OK;
+}
+
+// Runs `fn` with the slot's state bound in place of the model's own sequence (the prefill drivers address the
+// state through the layer table), then puts the model's own sequence back, device position included.
+template <class F>
+int32_t with_slot(wick_cuda_model* m, uint32_t id, F&& fn) {
+    wick_cuda_model::SeqSlot& sl = m->seqs[id];
+    auto swap_state = [&]() {
+        for (size_t li = 0; li < m->layers.size(); li++) {
+            Layer& L = m->layers[li];
+            if (L.is_attn) {
+                std::swap(L.k_cache, sl.k_cache[li]);
+                std::swap(L.v_cache, sl.v_cache[li]);
+            } else {
+                std::swap(L.conv_state, sl.conv_state[li]);
+            }
+        }
+        std::swap(m->seq_len, sl.seq_len);
+    };
+    swap_state();
+    const int32_t r = fn();
+    swap_state();
+    m->h_u32[0] = m->seq_len;
+    cudaError_t e = cudaMemcpyAsync(&m->ctl->pos, m->h_u32, 4, cudaMemcpyHostToDevice, m->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(m->stream);
+    if (r != WICK_CUDA_OK) return r;
+    if (e != cudaSuccess) return fail(WICK_CUDA_ERR_CUDA, std::string("restoring the model's own sequence: ") + cudaGetErrorString(e));
+    return WICK_CUDA_OK;
+}
+
+constexpr uint32_t MAX_BATCH_ROWS = 1024;
+
+int32_t ensure_batch_buffers(wick_cuda_model* m, uint32_t rows, uint32_t steps) {
+    const size_t nl = m->layers.size();
+    if ((int)rows > m->batch_cap) {
+        const int cap = (int)std::min<uint32_t>(std::max<uint32_t>((rows + 63) / 64 * 64, 64), (uint32_t)std::max(m->max_chunk, 1));
+        if ((int)rows > cap) return fail(WICK_CUDA_ERR_BAD_ARG, "batch larger than the model's scratch (" + std::to_string(cap) + " rows)");
+        W_TRY(dev_alloc(m, &m->logits_rows, (size_t)cap * m->cfg.vocab_size));
+        W_TRY(dev_alloc(m, &m->rows_tok, (size_t)cap));
+        W_TRY(dev_alloc(m, &m->rows_next, (size_t)cap));
+        W_TRY(dev_alloc(m, &m->rows_pos, (size_t)cap));
+        W_TRY(dev_alloc(m, &m->rows_ptrs, nl * 2 * cap));
+        m->batch_cap = cap;
+        m->rows_out_cap = 0;
+    }
+    const size_t out_need = (size_t)steps * rows;
+    if (out_need > m->rows_out_cap) {
+        W_TRY(dev_alloc(m, &m->rows_out, out_need));
+        m->rows_out_cap = out_need;
+    }
+    const size_t host_need = (size_t)m->batch_cap * (8 + nl * 16) + out_need * 4 + 64;
+    if (host_need > m->h_rows_bytes) {
+        if (m->h_rows) cudaFreeHost(m->h_rows);
+        m->h_rows = nullptr;
+        m->h_rows_bytes = 0;
+        CU_TRY(cudaMallocHost((void**)&m->h_rows, host_need));
+        m->h_rows_bytes = host_need;
+    }
+    return WICK_CUDA_OK;
+}
+
+// One decode step for n rows: tokens in m->rows_tok, positions in m->rows_pos, per-row state pointers in m->rows_ptrs
+// (run_layers, lfm2.rs:1020-1124, for every row; the mat-vecs as batched GEMMs, bit-identical to the mat-vec per row,
+// simd.rs:1440-1623).  Leaves the logits of every row in m->logits_rows.
+int32_t enqueue_decode_rows(wick_cuda_model* m, int n) {
+    cudaStream_t st = m->stream;
+    const int hs = m->cfg.hidden_size, is = m->cfg.intermediate_size, hd = m->head_dim, cap = m->batch_cap;
+    const float eps = m->cfg.rms_norm_eps;
+    auto gemms = [&](std::initializer_list<GemmTarget> list) { run_gemms(m, n, list); };
+    embed_rows(m, m->rows_tok, nullptr, n);
+    const float* pending = nullptr;
+    for (size_t li = 0; li < m->layers.size(); li++) {
+        Layer& L = m->layers[li];
+        float** p0 = m->rows_ptrs + (li * 2) * cap;
+        float** p1 = m->rows_ptrs + (li * 2 + 1) * cap;
+        launch_add_rmsnorm_quant(st, m->hidden, pending, L.attn_norm, eps, n, hs, m->q8s, m->q8q, nullptr);
+        if (!L.is_attn) {
+            gemms({{&L.in_proj, &L.tc_in_proj, m->proj}});
+            launch_shortconv_rows(st, m->proj, L.conv_w, p0, n, hs, m->cfg.conv_kernel_size, m->q8s, m->q8q);
+            gemms({{&L.out_proj, &L.tc_out_proj, m->block_out}});
+        } else {
+            gemms({{&L.q, &L.tc_q, m->qbuf}, {&L.k, &L.tc_k, m->kbuf}, {&L.v, &L.tc_v, m->vbuf}});
+            launch_qknorm_rope_kv_rows(st, m->qbuf, m->kbuf, m->vbuf, L.q_norm, L.k_norm, eps, m->rope_cos, m->rope_sin, p0, p1, m->rows_pos, n,
+                                       m->cfg.n_heads, L.n_kv, hd);
+            CU_TRY(launch_attention_rows(st, m->qbuf, p0, p1, m->rows_pos, m->attn_out, n, m->cfg.n_heads, L.n_kv, hd, m->cfg.max_seq_len));
+            launch_quant_rows(st, m->attn_out, n, hs, m->q8s, m->q8q);
+            gemms({{&L.o, &L.tc_o, m->block_out}});
+        }
+        launch_add_rmsnorm_quant(st, m->hidden, m->block_out, L.ffn_norm, eps, n, hs, m->q8s, m->q8q, nullptr);
+        gemms({{&L.gate, &L.tc_gate, m->gate}, {&L.up, &L.tc_up, m->up}});
+        launch_silu_mul_quant(st, m->gate, m->up, n, is, m->q8s, m->q8q, nullptr);
+        gemms({{&L.down, &L.tc_down, m->ffn_out}});
+        pending = m->ffn_out;
+    }
+    launch_add_rmsnorm_quant(st, m->hidden, pending, m->output_norm, eps, n, hs, m->q8s, m->q8q, nullptr);
+    if (m->embd_q6k) {
+        for (int j = 0; j < n; j++)
+            launch_gemv_q6k(st, m->embd6, m->q8s + (size_t)j * (hs / QK), m->q8q + (size_t)j * hs, m->logits_rows + (size_t)j * m->cfg.vocab_size);
+    } else {
+        launch_gemm(st, m->embd, m->q8s, m->q8q, n, m->logits_rows);
+    }
+    return WICK_CUDA_OK;
+}
+
+// Shared driver of the batched entry points: n_steps greedy steps for the rows, or (logits_host != NULL) one step
+// that returns every row's logits instead of feeding the argmax back.
+int32_t decode_rows(wick_cuda_model* m, const uint32_t* tokens_host, const uint32_t* seq_ids_host, uint32_t bs, uint32_t n_steps,
+                    uint32_t* out_tokens_host, float* logits_host) {
+    W_TRY(check_model(m));
+    if (bs == 0 || n_steps == 0) return WICK_CUDA_OK;
+    if (!tokens_host || !seq_ids_host || (!out_tokens_host && !logits_host)) return fail(WICK_CUDA_ERR_BAD_ARG, "NULL argument");
+    if (bs > MAX_BATCH_ROWS) return fail(WICK_CUDA_ERR_BAD_ARG, "batch of " + std::to_string(bs) + " rows exceeds " + std::to_string(MAX_BATCH_ROWS));
+    std::vector<uint8_t> seen(m->seqs.size(), 0);
+    for (uint32_t j = 0; j < bs; j++) {
+        W_TRY(check_seq(m, seq_ids_host[j]));
+        if (seen[seq_ids_host[j]]) return fail(WICK_CUDA_ERR_BAD_ARG, "sequence " + std::to_string(seq_ids_host[j]) + " appears twice in one batch");
+        seen[seq_ids_host[j]] = 1;
+        if (tokens_host[j] >= m->cfg.vocab_size)
+            return fail(WICK_CUDA_ERR_BAD_ARG, "token_id " + std::to_string(tokens_host[j]) + " out of range (vocab_size=" + std::to_string(m->cfg.vocab_size) + ")");
+        if ((uint64_t)m->seqs[seq_ids_host[j]].seq_len + n_steps > m->cfg.max_seq_len)
+            return fail(WICK_CUDA_ERR_CONTEXT_FULL, "sequence " + std::to_string(seq_ids_host[j]) + ": seq_len + steps exceeds max_seq_len " +
+                                                        std::to_string(m->cfg.max_seq_len));
+    }
+    CU_TRY(cudaSetDevice(m->device));
+    W_TRY(ensure_batch_buffers(m, bs, n_steps));
+    const size_t nl = m->layers.size();
+    const int cap = m->batch_cap;
+    // staging: tokens, positions, then the per-layer pointer table
+    uint32_t* h_tok = (uint32_t*)m->h_rows;
+    uint32_t* h_pos = h_tok + cap;
+    float** h_ptr = (float**)(m->h_rows + (size_t)cap * 8);
+    uint32_t* h_out = (uint32_t*)(m->h_rows + (size_t)cap * (8 + nl * 16));
+    for (uint32_t j = 0; j < bs; j++) {
+        const wick_cuda_model::SeqSlot& sl = m->seqs[seq_ids_host[j]];
+        h_tok[j] = tokens_host[j];
+        h_pos[j] = sl.seq_len;
+        for (size_t li = 0; li < nl; li++) {
+            h_ptr[(li * 2) * cap + j] = m->layers[li].is_attn ? sl.k_cache[li] : sl.conv_state[li];
+            h_ptr[(li * 2 + 1) * cap + j] = m->layers[li].is_attn ? sl.v_cache[li] : nullptr;
+        }
+    }
+    CU_TRY(cudaEventRecord(m->ev0, m->stream));
+    CU_TRY(cudaMemcpyAsync(m->rows_tok, h_tok, (size_t)bs * 4, cudaMemcpyHostToDevice, m->stream));
+    CU_TRY(cudaMemcpyAsync(m->rows_pos, h_pos, (size_t)bs * 4, cudaMemcpyHostToDevice, m->stream));
+    CU_TRY(cudaMemcpyAsync(m->rows_ptrs, h_ptr, nl * 2 * cap * sizeof(float*), cudaMemcpyHostToDevice, m->stream));
+    const unsigned long long before = g_kernel_launches;
+    for (uint32_t s_i = 0; s_i < n_steps; s_i++) {
+        W_TRY(enqueue_decode_rows(m, (int)bs));
+        if (!logits_host) {
+            launch_argmax_rows(m->stream, m->logits_rows, (int)bs, (int)m->cfg.vocab_size, m->rows_next);
+            launch_rows_advance(m->stream, m->rows_tok, m->rows_next, m->rows_pos, m->rows_out, (int)bs, (int)s_i);
+        }
+    }
+    m->launches += g_kernel_launches - before;
+    CU_TRY(cudaGetLastError());
+    if (!logits_host) CU_TRY(cudaMemcpyAsync(h_out, m->rows_out, (size_t)n_steps * bs * 4, cudaMemcpyDeviceToHost, m->stream));
+    m->h_u32[2] = 0;
+    if (m->tc_err) CU_TRY(cudaMemcpyAsync(m->h_u32 + 2, m->tc_err, 4, cudaMemcpyDeviceToHost, m->stream));
+    CU_TRY(cudaEventRecord(m->ev1, m->stream));
+    CU_TRY(cudaStreamSynchronize(m->stream));
+    if (m->h_u32[2] != 0) {
+        const uint32_t code = m->h_u32[2];
+        cudaMemsetAsync(m->tc_err, 0, 4, m->stream);
+        return fail(WICK_CUDA_ERR_TIMEOUT, "tensor-core GEMM: a bounded wait expired (role code " + std::to_string(code) + ")");
+    }
+    if (logits_host)
+        CU_TRY(cudaMemcpy(logits_host, m->logits_rows, (size_t)bs * m->cfg.vocab_size * 4, cudaMemcpyDeviceToHost));
+    else
+        memcpy(out_tokens_host, h_out, (size_t)n_steps * bs * 4);
+    for (uint32_t j = 0; j < bs; j++) m->seqs[seq_ids_host[j]].seq_len += n_steps;
     return WICK_CUDA_OK;
 }
 
@@ -1362,6 +1561,87 @@ int32_t wick_cuda_read_conv_state(wick_cuda_model* m, uint32_t layer, float* out
     size_t b = (size_t)((int)m->cfg.conv_kernel_size - 1) * m->cfg.hidden_size * 4;
     if (b) CU_TRY(cudaMemcpy(out_host, m->layers[layer].conv_state, b, cudaMemcpyDeviceToHost));
     return WICK_CUDA_OK;
+}
+
+// ── sequence slots (extension; not reachable from wick's Model trait) ──────
+
+int32_t wick_cuda_seq_create(wick_cuda_model* m, uint32_t* seq_id) {
+    W_TRY(check_model(m));
+    if (!seq_id) return fail(WICK_CUDA_ERR_BAD_ARG, "seq_id is NULL");
+    CU_TRY(cudaSetDevice(m->device));
+    size_t id = 0;
+    while (id < m->seqs.size() && m->seqs[id].live) id++;
+    const int hs = m->cfg.hidden_size, dc = (int)m->cfg.conv_kernel_size - 1;
+    if (id == m->seqs.size()) {
+        if (m->seqs.size() >= 65536) return fail(WICK_CUDA_ERR_BAD_ARG, "too many sequence slots");
+        wick_cuda_model::SeqSlot sl;
+        const size_t nl = m->layers.size();
+        sl.k_cache.assign(nl, nullptr);
+        sl.v_cache.assign(nl, nullptr);
+        sl.conv_state.assign(nl, nullptr);
+        for (size_t li = 0; li < nl; li++) {
+            const Layer& L = m->layers[li];
+            if (L.is_attn) {
+                const size_t rows = (size_t)m->cfg.max_seq_len * L.n_kv * m->head_dim;
+                W_TRY(dev_alloc(m, &sl.k_cache[li], rows));
+                W_TRY(dev_alloc(m, &sl.v_cache[li], rows));
+            } else {
+                W_TRY(dev_alloc(m, &sl.conv_state[li], (size_t)std::max(dc, 1) * hs));
+            }
+        }
+        m->seqs.push_back(std::move(sl));
+    }
+    wick_cuda_model::SeqSlot& sl = m->seqs[id];  // a recycled slot keeps its buffers
+    for (size_t li = 0; li < m->layers.size(); li++)
+        if (!m->layers[li].is_attn && dc > 0) CU_TRY(cudaMemsetAsync(sl.conv_state[li], 0, (size_t)dc * hs * sizeof(float), m->stream));
+    CU_TRY(cudaStreamSynchronize(m->stream));
+    sl.live = true;
+    sl.seq_len = 0;
+    *seq_id = (uint32_t)id;
+    return WICK_CUDA_OK;
+}
+
+int32_t wick_cuda_seq_destroy(wick_cuda_model* m, uint32_t seq_id) {
+    W_TRY(check_model(m));
+    W_TRY(check_seq(m, seq_id));
+    m->seqs[seq_id].live = false;  // the buffers stay with the model and serve the next wick_cuda_seq_create
+    m->seqs[seq_id].seq_len = 0;
+    return WICK_CUDA_OK;
+}
+
+int32_t wick_cuda_seq_length(const wick_cuda_model* m, uint32_t seq_id, uint32_t* out) {
+    W_TRY(check_model(m));
+    W_TRY(check_seq(m, seq_id));
+    if (!out) return fail(WICK_CUDA_ERR_BAD_ARG, "out is NULL");
+    *out = m->seqs[seq_id].seq_len;
+    return WICK_CUDA_OK;
+}
+
+int32_t wick_cuda_seq_prefill(wick_cuda_model* m, uint32_t seq_id, const uint32_t* tokens_host, uint32_t n, uint32_t start_pos,
+                              float* logits_host) {
+    W_TRY(check_model(m));
+    W_TRY(check_seq(m, seq_id));
+    if (!tokens_host || !logits_host) return fail(WICK_CUDA_ERR_BAD_ARG, "NULL argument");
+    CU_TRY(cudaSetDevice(m->device));
+    return with_slot(m, seq_id, [&]() { return prefill_core(m, tokens_host, nullptr, n, start_pos, logits_host, nullptr); });
+}
+
+int32_t wick_cuda_decode_batch(wick_cuda_model* m, const uint32_t* tokens_host, const uint32_t* seq_ids_host, uint32_t bs,
+                               uint32_t* next_tokens_host) {
+    if (!next_tokens_host) return fail(WICK_CUDA_ERR_BAD_ARG, "next_tokens_host is NULL");
+    return decode_rows(m, tokens_host, seq_ids_host, bs, 1, next_tokens_host, nullptr);
+}
+
+int32_t wick_cuda_decode_batch_steps(wick_cuda_model* m, const uint32_t* first_tokens_host, const uint32_t* seq_ids_host, uint32_t bs,
+                                     uint32_t n_steps, uint32_t* out_tokens_host) {
+    if (!out_tokens_host) return fail(WICK_CUDA_ERR_BAD_ARG, "out_tokens_host is NULL");
+    return decode_rows(m, first_tokens_host, seq_ids_host, bs, n_steps, out_tokens_host, nullptr);
+}
+
+int32_t wick_cuda_decode_batch_logits(wick_cuda_model* m, const uint32_t* tokens_host, const uint32_t* seq_ids_host, uint32_t bs,
+                                      float* logits_host) {
+    if (!logits_host) return fail(WICK_CUDA_ERR_BAD_ARG, "logits_host is NULL");
+    return decode_rows(m, tokens_host, seq_ids_host, bs, 1, nullptr, logits_host);
 }
 
 // ── operators ──────────────────────────────────────────────────────────────

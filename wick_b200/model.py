@@ -311,6 +311,59 @@ class CudaLfm2Model:
         return s
 
 
+    # ---- many sequences on one model (extension; not part of trait Model) ------
+    def seq_create(self) -> int:
+        """A new sequence slot (own KV caches, conv buffers, length) on this model's weights."""
+        sid = C.c_uint32(0)
+        with self._lock:
+            check(self._lib.wick_cuda_seq_create(self._h, C.byref(sid)))
+        return sid.value
+
+    def seq_destroy(self, seq_id: int) -> None:
+        with self._lock:
+            check(self._lib.wick_cuda_seq_destroy(self._h, int(seq_id)))
+
+    def seq_length(self, seq_id: int) -> int:
+        n = C.c_uint32(0)
+        check(self._lib.wick_cuda_seq_length(self._h, int(seq_id), C.byref(n)))
+        return n.value
+
+    def seq_prefill(self, seq_id: int, tokens: Sequence[int], start_pos: int) -> np.ndarray:
+        """forward_prefill on a slot: logits of the last position."""
+        toks = np.ascontiguousarray(tokens, np.uint32)
+        logits = np.empty(self._config.vocab_size, np.float32)
+        with self._lock:
+            check(self._lib.wick_cuda_seq_prefill(self._h, int(seq_id), toks.ctypes.data, len(toks), int(start_pos), logits.ctypes.data))
+        return logits
+
+    def decode_batch(self, tokens: Sequence[int], seq_ids: Sequence[int]) -> np.ndarray:
+        """One greedy step for every listed slot in one pass over the weights: next token per row."""
+        toks, ids = np.ascontiguousarray(tokens, np.uint32), np.ascontiguousarray(seq_ids, np.uint32)
+        assert len(toks) == len(ids)
+        out = np.empty(len(toks), np.uint32)
+        with self._lock:
+            check(self._lib.wick_cuda_decode_batch(self._h, toks.ctypes.data, ids.ctypes.data, len(toks), out.ctypes.data))
+        return out
+
+    def decode_batch_steps(self, first_tokens: Sequence[int], seq_ids: Sequence[int], n_steps: int) -> np.ndarray:
+        """n_steps greedy steps for the listed slots, kept on the device: tokens [n_steps, rows]."""
+        toks, ids = np.ascontiguousarray(first_tokens, np.uint32), np.ascontiguousarray(seq_ids, np.uint32)
+        assert len(toks) == len(ids)
+        out = np.empty((int(n_steps), len(toks)), np.uint32)
+        with self._lock:
+            check(self._lib.wick_cuda_decode_batch_steps(self._h, toks.ctypes.data, ids.ctypes.data, len(toks), int(n_steps), out.ctypes.data))
+        return out
+
+    def decode_batch_logits(self, tokens: Sequence[int], seq_ids: Sequence[int]) -> np.ndarray:
+        """One step for every listed slot, returning logits [rows, vocab] (Model::forward for many sequences)."""
+        toks, ids = np.ascontiguousarray(tokens, np.uint32), np.ascontiguousarray(seq_ids, np.uint32)
+        assert len(toks) == len(ids)
+        out = np.empty((len(toks), self._config.vocab_size), np.float32)
+        with self._lock:
+            check(self._lib.wick_cuda_decode_batch_logits(self._h, toks.ctypes.data, ids.ctypes.data, len(toks), out.ctypes.data))
+        return out
+
+
 def load_model_cuda(path: str, context_size: int = 4096, device: int = 0) -> CudaLfm2Model:
     """Counterpart of load_model_metal (model/mod.rs:386-403)."""
     return CudaLfm2Model(path, context_size, device)
