@@ -39,6 +39,9 @@ import numpy as np  # noqa: E402
 
 PROMPT_TOKENS = 128
 DECODE_TOKENS = 128
+PREFILL_REPEATS = 5     # side measurements of prefill: p50 over this many repeats after one warm call
+# serving side line: independent sequences per GPU, each with its own prompt, decoded together in batched steps
+SERVE_SEQUENCES, SERVE_PROMPT, SERVE_DECODE = 64, 512, 256
 FALLBACK_HBM_GBS = 6650.0
 
 # dram__bytes_read.sum + dram__bytes_write.sum per decoded token from an ncu capture of the decode
@@ -215,6 +218,49 @@ def run_prefill_only(args, m, st, spec, gs):
     }))
 
 
+def serving_side_line(m, spec, args, gs, hbm_peak):
+    """Batched multi-sequence decode on one GPU: SERVE_SEQUENCES independent sequences, each prefilled with its own
+    SERVE_PROMPT-token uniform-random prompt, then SERVE_DECODE greedy steps in which every step reads the weights
+    once for all sequences (wick_cuda_decode_batch_steps).  Not the headline metric; reported with its own roofline
+    (weight bytes once per step over the device time of a step)."""
+    ids, firsts = [], []
+    t0 = time.perf_counter()
+    for i in range(SERVE_SEQUENCES):
+        sid = m.seq_create()
+        toks = gs.random_prompt(SERVE_PROMPT, spec.vocab, seed=1000 + i)
+        firsts.append(int(np.argmax(m.seq_prefill(sid, toks, 0))))
+        ids.append(sid)
+    prefill_s = time.perf_counter() - t0
+    warm = m.decode_batch_steps(firsts, ids, 4)
+    t0 = time.perf_counter()
+    out = m.decode_batch_steps(warm[-1], ids, SERVE_DECODE - 4)
+    wall = time.perf_counter() - t0
+    dev = m.last_elapsed_ms() * 1e-3
+    steps = SERVE_DECODE - 4
+    # the same through one call per step (tokens host -> device, choices device -> host every step)
+    tok = out[-1]
+    n_e2e = 32
+    t0 = time.perf_counter()
+    for _ in range(n_e2e):
+        if m.seq_length(ids[0]) + 1 >= args.context:
+            break
+        tok = m.decode_batch(tok, ids)
+    e2e = time.perf_counter() - t0
+    for sid in ids:
+        m.seq_destroy(sid)
+    bpt = spec.decode_bytes_per_token(args.qtype)
+    return {
+        "workload": f"{SERVE_SEQUENCES} sequences x ({SERVE_PROMPT}-token prompt + {SERVE_DECODE} greedy tokens), one batched step per token",
+        "decode_tok_s_device": SERVE_SEQUENCES * steps / dev, "decode_tok_s_wall": SERVE_SEQUENCES * steps / wall,
+        "decode_tok_s_per_step_calls": SERVE_SEQUENCES * n_e2e / e2e,
+        "ms_per_step": dev / steps * 1e3,
+        "prefill_tok_s_wall": SERVE_SEQUENCES * SERVE_PROMPT / prefill_s,
+        "roofline": {"bound": "hbm", "achieved": bpt / (dev / steps) / 1e9, "peak": hbm_peak, "unit": "GB/s",
+                     "frac": bpt / (dev / steps) / 1e9 / hbm_peak,
+                     "note": "weight bytes once per batched step; at 64 rows the step is bound by the exact GEMM's epilogue, not by HBM"},
+    }
+
+
 def workload_config(args, spec):
     return {
         "workload": f"{spec.name} {args.qtype.upper()} bs=1: {PROMPT_TOKENS}-token uniform-random prompt prefill (untimed), "
@@ -385,11 +431,16 @@ def main():
             for n, ub in ((128, 512), (1024, 512), (4096, 512), (4096, 0)):
                 toks = gs.random_prompt(n, spec.vocab, seed=7)
                 m.forward_prefill_chunked(toks, 0, st, ub)          # warm
-                t0 = time.perf_counter()
-                m.forward_prefill_chunked(toks, 0, st, ub)          # Session::append_tokens; ubatch 512 is wick's default
-                tps = n / (time.perf_counter() - t0)
+                wall, dev = [], []
+                for _ in range(PREFILL_REPEATS):
+                    t0 = time.perf_counter()
+                    m.forward_prefill_chunked(toks, 0, st, ub)      # Session::append_tokens; ubatch 512 is wick's default
+                    wall.append(time.perf_counter() - t0)
+                    dev.append(m.last_chunked_device_ms * 1e-3)
+                tps = n / statistics.median(wall)                   # p50 of the host wall clock of the whole call (wick bench's clock)
                 key = f"prefill_{mode}_p{n}" + ("_one_call" if ub == 0 else "") + "_tok_s"
                 extra[key] = tps
+                extra[key.replace("_tok_s", "_device_tok_s")] = n / statistics.median(dev)   # p50, CUDA events around each chunk
                 if n == 4096 and mode != "exact-cuda-cores":
                     extra[key.replace("_tok_s", "_gemm_frac_of_int8_peak")] = tps * flop_tok / 1e12 / tensor_peak
         m.set_prefill_mode("exact")
@@ -399,6 +450,11 @@ def main():
         logits = m.forward_prefill(prompt, 0, st)
         m.generate_greedy(int(np.argmax(logits)), 512, st)
         extra["decode_tg512_tok_s"] = 512 / (m.last_elapsed_ms() * 1e-3)
+        extra["prefill_repeats"] = PREFILL_REPEATS
+        try:
+            extra["serving"] = serving_side_line(m, spec, args, gs, peak)
+        except Exception as e:                              # e.g. not enough device memory for the sequence slots
+            extra["serving"] = f"unavailable: {e}"
         extra["prefill_paths"] = {"exact": "default: bit-exact GEMM on tcgen05 (lane partials in tensor memory, eight unfused chains) + exact-order attention",
                                   "tensor": "tcgen05 int8 GEMM (exact block sums, one fused f32 chain) + exact-order attention",
                                   "exact-cuda-cores": "bit-exact CUDA-core integer GEMM + exact-order attention"}

@@ -361,10 +361,13 @@ def _flash_ref(orc, q, kc, vc, n, start, nh, nkv, hd):
     return out
 
 
-@pytest.mark.parametrize("n,start,nh,nkv", [(8, 4, 4, 2), (1, 0, 4, 2), (31, 0, 8, 2), (64, 33, 4, 4), (100, 0, 6, 2), (257, 300, 8, 2)])
-def test_attention_flash_bit_exact(ops, orc, n, start, nh, nkv):
-    hd = 64
-    rng = np.random.default_rng(n * 3 + start)
+@pytest.mark.parametrize("hd", [64, 32, 128])
+@pytest.mark.parametrize("n,start,nh,nkv", [(8, 4, 4, 2), (1, 0, 4, 2), (31, 0, 8, 2), (64, 33, 4, 4), (100, 0, 6, 2), (257, 300, 8, 2),
+                                            (300, 0, 8, 1), (513, 1027, 16, 4)])
+def test_attention_flash_bit_exact(ops, orc, n, start, nh, nkv, hd):
+    """Ragged query counts (not multiples of the 8 queries a warp owns), 1 to 8 query heads per KV head, start
+    positions that are not multiples of the 32-key tile, all three head sizes."""
+    rng = np.random.default_rng(n * 3 + start + hd)
     q = rng.standard_normal((n, nh * hd), dtype=F32)
     kc = rng.standard_normal((start + n, nkv * hd), dtype=F32)
     vc = rng.standard_normal((start + n, nkv * hd), dtype=F32)
@@ -381,6 +384,16 @@ def test_attention_flash_reference_case(ops, orc):
     assert np.abs(fl - nv).max() < 1e-4
     assert_bit_equal(fl, _flash_ref(orc, q, kc, vc, n, sp, nh, nkv, hd))
     assert_bit_equal(nv, _naive_ref(orc, q, kc, vc, n, sp, nh, nkv, hd))
+
+
+def test_attention_flash_rejects_unsupported_shapes(ops):
+    from wick_b200._lib import WickCudaError
+    z = torch.zeros((4, 16 * 96), dtype=torch.float32, device="cuda")
+    with pytest.raises(WickCudaError):
+        ops.attention_prefill(z, z, z, 4, 0, 16, 16, 96, True)      # head_dim 96
+    z = torch.zeros((4, 16 * 64), dtype=torch.float32, device="cuda")
+    with pytest.raises(WickCudaError):
+        ops.attention_prefill(z, z[:, :64].contiguous(), z[:, :64].contiguous(), 4, 0, 16, 1, 64, True)   # 16 query heads per KV head
 
 
 def test_attention_softmax_is_normalised_large(ops):

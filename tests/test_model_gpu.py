@@ -343,3 +343,32 @@ def test_flagged_hidden_handover_matches_barrier_path(wick, orc, model_dir, monk
     assert list(b.generate_greedy(tok, 100, sb)) == want
     # the persistent kernel is what ran (a fallback to the per-kernel graph would not exercise the hand-over)
     assert a.decode_path() == "persistent" and b.decode_path() == "persistent"
+
+
+def test_head_dim_128_prefill_and_decode(wick, orc, model_dir):
+    """128-wide heads: a 300-token prompt (tiled attention path, n >= 256), a continuation chunk and decode steps,
+    all bit-equal to the oracle."""
+    from wick_b200 import gguf_synth as gs
+    path = _model_path(model_dir, "tiny-hd128", "q4_0", norm_jitter=0.2, weight_std=0.05)
+    cm, om = wick.CudaLfm2Model(path, 1024), orc.OracleModel(path, 1024)
+    st = wick.InferenceState()
+    toks = gs.random_prompt(300 + 260, cm.config().vocab_size, seed=9)
+    assert_logits_equal(cm.forward_prefill(toks[:300], 0, st), om.forward_prefill(toks[:300], 0), "hd128 prefill 300")
+    assert_logits_equal(cm.forward_prefill(toks[300:], 300, st), om.forward_prefill(toks[300:], 300), "hd128 continuation 260")
+    first = 5
+    assert list(cm.generate_greedy(first, 12, st)) == list(om.generate_greedy(first, 12))
+
+
+def test_two_models_with_different_long_contexts(wick, orc, model_dir):
+    """The per-token attention kernel's opt-in shared-memory limit belongs to the kernel on a device, not to a model:
+    a second model with a shorter (but still > 48 KB of scores) context must not lower it under the first."""
+    from wick_b200 import gguf_synth as gs
+    path = _model_path(model_dir, "tiny-longctx", "q4_0")
+    m1 = wick.CudaLfm2Model(path, 32768)
+    m2 = wick.CudaLfm2Model(path, 16384)
+    st1, st2 = wick.InferenceState(), wick.InferenceState()
+    toks = gs.random_prompt(40, m1.config().vocab_size, seed=2)
+    om = orc.OracleModel(path, 32768)
+    want = om.forward_prefill(toks, 0)
+    assert_logits_equal(m2.forward_prefill(toks, 0, st2), want, "second model")
+    assert_logits_equal(m1.forward_prefill(toks, 0, st1), want, "first model, after the second one was created and used")

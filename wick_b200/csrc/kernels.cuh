@@ -63,9 +63,12 @@ void launch_attention_naive(cudaStream_t st, const float* q, const float* k_cach
 // Opt-in to more than 48 KB of dynamic shared memory for the kernel above; call before any
 // stream capture that contains it.
 void configure_naive_attention_smem(size_t bytes);
-// Exact tiled online-softmax attention (cpu.rs:1696-1850).
-void launch_attention_flash(cudaStream_t st, const float* q, const float* k_cache, const float* v_cache, float* out,
-                            int n, int start_pos, int n_heads, int n_kv_heads, int head_dim);
+// Exact tiled online-softmax attention (cpu.rs:1696-1850) for head_dim 32, 64 or 128 and up to 8 query heads per
+// KV head (attention_flash_supported); other shapes return cudaErrorInvalidValue without launching.  `err` is a
+// device word that receives a non-zero code if a bounded wait inside the kernel runs out.
+bool attention_flash_supported(int n_heads, int n_kv_heads, int head_dim);
+cudaError_t launch_attention_flash(cudaStream_t st, const float* q, const float* k_cache, const float* v_cache, float* out,
+                                   int n, int start_pos, int n_heads, int n_kv_heads, int head_dim, uint32_t* err);
 
 // Q6_K vocabulary matrix (kernels_q6k.cu): re-layout of raw GGUF blocks into the planes of `w` (already
 // pointing at device memory), embedding rows, and the logits mat-vec y[m] (simd.rs:552-672).  The mat-vec

@@ -143,119 +143,281 @@ void launch_attention_naive(cudaStream_t st, const float* q, const float* k_cach
 }
 
 // ── tiled online-softmax prefill attention ─────────────────────────────────
-// flash_attention_gqa_neon (cpu.rs:1696-1850).  One thread runs the reference's loop for
-// one (query head, query): 32-key tiles, tile max, rescale by ggml_expf(old_max - new_max),
-// f64 tile sum in order, acc *= rescale, fused acc += p * v in ascending key order,
-// running_sum = running_sum * rescale + tile_sum in f64, one normalisation at the end.
-// A CTA holds the `group` query heads of ONE KV head for a run of queries, so every thread
-// reads the same K / V tile from shared memory (broadcast).
-constexpr int FLASH_THREADS = 128;
+// flash_attention_gqa_neon (cpu.rs:1696-1850): per (query head, query) 32-key tiles, tile max, rescale by
+// ggml_expf(old_max - new_max), f64 tile sum in key order, acc *= rescale, fused acc += p * v in ascending key
+// order, running_sum = running_sum * rescale + tile_sum in f64, one normalisation at the end.
+//
+// Mapping.  A CTA serves ONE KV head and a run of QB consecutive queries for every query head of its group, so
+// a K / V tile is fetched once for all of them.  A producer warp streams the tiles with bulk asynchronous copies
+// (cp.async.bulk, one per cache row, completion counted on an mbarrier) into a two-deep ring of shared memory;
+// rows are padded to HD + 4 floats so that the accesses below are free of bank conflicts.  A consumer warp owns
+// 8 queries of one head; lane = (query jq = lane / 4, part s = lane % 4):
+//   * q.k: the lane holds its query row in registers and computes the dots of keys t = 4 i + s (i = 0..7) of the
+//     tile with the reference's eight fused chains; the four parts of a query read four different rows (one
+//     128-byte wavefront per 16-byte load, each value feeding 8 queries);
+//   * softmax: tile max over the lane's 8 scores and its three partner lanes; each lane exponentiates its own 8;
+//   * the probabilities travel by warp shuffle, in key order: every lane adds all 32 to the f64 tile sum in the
+//     reference's order and applies them to its quarter of the output dims (acc chains in ascending key order).
+// Keys at or beyond a query's causal limit are skipped by predicate (they may hold anything).
+// Every wait is bounded: on expiry the CTA sets *err, stops waiting and returns.
 constexpr int FLASH_TILE = 32;  // FLASH_TILE_KV, cpu.rs:1513
+constexpr unsigned FLASH_SPIN_LIMIT = 1u << 20;
 
+__device__ __forceinline__ uint32_t fa_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ bool fa_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, 2000;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(fa_smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// false: the wait ran out (or another wait of this CTA did): *err is set and the caller must stop
+__device__ __forceinline__ bool fa_wait(uint64_t* bar, uint32_t parity, volatile int* abort, uint32_t* err, uint32_t code) {
+    unsigned spins = 0;
+    while (!fa_try_wait(bar, parity)) {
+        if (*abort) return false;
+        if (++spins > FLASH_SPIN_LIMIT) {
+            atomicOr(err, code);
+            *abort = 1;
+            return false;
+        }
+    }
+    return !*abort;
+}
+
+#ifndef WICK_FA_MIN_CTAS
+#define WICK_FA_MIN_CTAS 2
+#endif
+#ifndef WICK_FA_KB
+#define WICK_FA_KB 2
+#endif
 template <int HD>
-__global__ void __launch_bounds__(FLASH_THREADS) k_attention_flash(const float* __restrict__ q,
-                                                                    const float* __restrict__ k_cache,
-                                                                    const float* __restrict__ v_cache,
-                                                                    float* __restrict__ out, int n, int start_pos,
-                                                                    int n_heads, int n_kv_heads) {
-    __shared__ __align__(16) float Ks[FLASH_TILE * HD];
-    __shared__ __align__(16) float Vs[FLASH_TILE * HD];
+__global__ void __launch_bounds__(288, HD <= 64 ? WICK_FA_MIN_CTAS : 1) k_attention_flash(const float* __restrict__ q, const float* __restrict__ k_cache,
+                                                          const float* __restrict__ v_cache, float* __restrict__ out, int n, int start_pos,
+                                                          int n_heads, int n_kv_heads, int qb, uint32_t* __restrict__ err) {
+    constexpr int ROW = HD + 4;          // padded row, floats
+    constexpr int DPL = HD / 4;          // output dims per lane
+    constexpr int KB = WICK_FA_KB;       // keys whose dots share one pass over the query row
+    extern __shared__ __align__(128) uint8_t fa_smem[];
+    float* Ks = reinterpret_cast<float*>(fa_smem);                   // [2][32][ROW]
+    float* Vs = Ks + 2 * FLASH_TILE * ROW;                            // [2][32][ROW]
+    float* Qs = Vs + 2 * FLASH_TILE * ROW;                            // [consumer warps][8][ROW]
+    uint64_t* full = reinterpret_cast<uint64_t*>(Qs + 8 * 8 * ROW);   // [2]
+    uint64_t* empty = full + 2;                                       // [2]
+    volatile int* abort = reinterpret_cast<volatile int*>(empty + 2);
+
     const int group = n_heads / n_kv_heads;
-    const int qb = FLASH_THREADS / group;  // queries per CTA
+    const int n_cw = group * (qb / 8);  // consumer warps
     const int kvh = blockIdx.x;
-    const int g = threadIdx.x % group, jq = threadIdx.x / group;
-    const int j = blockIdx.y * qb + jq;
-    const int h = kvh * group + g;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int hs = n_heads * HD, kv_dim = n_kv_heads * HD;
-    const bool active = jq < qb && j < n;
+    const int j_first = blockIdx.y * qb;
+    const int j_last = min(n, j_first + qb) - 1;
+    const int cta_max = start_pos + j_last + 1;  // keys this CTA needs
+    const int n_tiles = (cta_max + FLASH_TILE - 1) / FLASH_TILE;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < 2; i++) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(fa_smem_u32(&full[i])), "r"(1));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(fa_smem_u32(&empty[i])), "r"(n_cw));
+        }
+        *abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+
+    if (warp == n_cw) {
+        // producer: tile `it` goes to buffer it & 1 once its previous user has been released by every consumer warp
+        for (int it = 0; it < n_tiles; it++) {
+            const int buf = it & 1;
+            if (it >= 2 && !fa_wait(&empty[buf], ((it >> 1) - 1) & 1, abort, err, 0x100u)) break;
+            const int kv0 = it * FLASH_TILE;
+            const int rows = min(FLASH_TILE, cta_max - kv0);
+            if (lane == 0)
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(fa_smem_u32(&full[buf])), "r"(rows * HD * 8) : "memory");
+            __syncwarp();
+            if (lane < rows) {
+                const size_t src = (size_t)(kv0 + lane) * kv_dim + (size_t)kvh * HD;
+                const uint32_t bar = fa_smem_u32(&full[buf]);
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                                 fa_smem_u32(Ks + (buf * FLASH_TILE + lane) * ROW)),
+                             "l"(k_cache + src), "r"(HD * 4), "r"(bar)
+                             : "memory");
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                                 fa_smem_u32(Vs + (buf * FLASH_TILE + lane) * ROW)),
+                             "l"(v_cache + src), "r"(HD * 4), "r"(bar)
+                             : "memory");
+            }
+        }
+        // never leave with a copy in flight: the last two tiles' bytes must have landed (bounded)
+        for (int it = max(0, n_tiles - 2); it < n_tiles; it++) {
+            unsigned spins = 0;
+            while (!fa_try_wait(&full[it & 1], (it >> 1) & 1) && ++spins < FLASH_SPIN_LIMIT) {
+            }
+        }
+        return;
+    }
+    if (warp > n_cw) return;
+
+    const int g = warp % group, oct = warp / group;
+    const int jq = lane >> 2, s = lane & 3;
+    const int j = j_first + oct * 8 + jq;
+    const int h = kvh * group + g;
+    const bool active = j < n;
     const int my_max = active ? start_pos + j + 1 : 0;
-    int cta_last = min(n, (int)(blockIdx.y + 1) * qb) - 1;
-    const int cta_max = start_pos + cta_last + 1;
     const float scale = __fdiv_rn(1.0f, sqrtf((float)HD));
 
-    float qr[HD], acc[HD];
-#pragma unroll
-    for (int d = 0; d < HD; d++) {
-        qr[d] = active ? q[(size_t)j * hs + h * HD + d] : 0.0f;
-        acc[d] = 0.0f;
+    // the warp's 8 query rows in shared memory (padded like the K rows: the 8 queries of a 16-byte load hit 8
+    // different bank groups); lane L copies 16-byte pieces L, L + 32, ...
+    float* qw = Qs + warp * 8 * ROW;
+    for (int i = lane; i < 8 * (HD / 4); i += 32) {
+        const int r = i / (HD / 4), c = i % (HD / 4);
+        const int jr = j_first + oct * 8 + r;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (jr < n) v = __ldg(reinterpret_cast<const float4*>(q + (size_t)jr * hs + h * HD) + c);
+        reinterpret_cast<float4*>(qw + r * ROW)[c] = v;
     }
+    __syncwarp();
+    const float* qrow = qw + jq * ROW;
+    float acc[DPL];
+#pragma unroll
+    for (int d = 0; d < DPL; d++) acc[d] = 0.0f;
     float running_max = __int_as_float(0xFF800000);
     double running_sum = 0.0;
+    const int src_base = lane & ~3;
 
-    for (int kv0 = 0; kv0 < cta_max; kv0 += FLASH_TILE) {
-        __syncthreads();
-        for (int idx = threadIdx.x; idx < FLASH_TILE * HD / 4; idx += FLASH_THREADS) {
-            int r = idx / (HD / 4), c4 = idx % (HD / 4);
-            float4 kk = make_float4(0.f, 0.f, 0.f, 0.f), vv = kk;
-            if (kv0 + r < cta_max) {
-                size_t o = (size_t)(kv0 + r) * kv_dim + kvh * HD + c4 * 4;
-                kk = *reinterpret_cast<const float4*>(k_cache + o);
-                vv = *reinterpret_cast<const float4*>(v_cache + o);
-            }
-            reinterpret_cast<float4*>(Ks)[idx] = kk;
-            reinterpret_cast<float4*>(Vs)[idx] = vv;
-        }
-        __syncthreads();
-        const int len = min(FLASH_TILE, my_max - kv0);
-        if (len <= 0) continue;
-
-        float ts[FLASH_TILE];
-        float tmax = __int_as_float(0xFF800000);
+    for (int it = 0; it < n_tiles; it++) {
+        const int buf = it & 1, kv0 = it * FLASH_TILE;
+        if (!fa_wait(&full[buf], (it >> 1) & 1, abort, err, 0x200u)) return;
+        const int len = min(FLASH_TILE, my_max - kv0);  // keys of this tile the lane's query attends (<= 0: none)
+        if (__reduce_max_sync(0xffffffffu, len) > 0) {
+            const float* Kt = Ks + buf * FLASH_TILE * ROW;
+            const float* Vt = Vs + buf * FLASH_TILE * ROW;
+            float e[8];
+            float tmax = __int_as_float(0xFF800000);
+            // the lane's 8 keys in blocks of KB: a 16-byte piece of the query row is loaded once per block
 #pragma unroll
-        for (int ti = 0; ti < FLASH_TILE; ti++) {
-            if (ti < len) {
-                float s = __fmul_rn(qk_dot<HD>(qr, Ks + ti * HD), scale);
-                ts[ti] = s;
-                if (s > tmax) tmax = s;
-            }
-        }
-        const float new_max = fmaxf(running_max, tmax);
-        const float rescale = running_max > __int_as_float(0xFF800000) ? ggml_expf(__fsub_rn(running_max, new_max)) : 0.0f;
-        double tsum = 0.0;
+            for (int i0 = 0; i0 < 8; i0 += KB) {
+                if (4 * i0 + s < len) {  // (keys of a block ascend: if the first is out of range, all are)
+                    float s0[KB][4], s1[KB][4];
 #pragma unroll
-        for (int ti = 0; ti < FLASH_TILE; ti++) {
-            if (ti < len) {
-                float e = ggml_expf(__fsub_rn(ts[ti], new_max));
-                ts[ti] = e;
-                tsum += (double)e;
-            }
-        }
+                    for (int u = 0; u < KB; u++)
 #pragma unroll
-        for (int d = 0; d < HD; d++) acc[d] = __fmul_rn(acc[d], rescale);
+                        for (int l = 0; l < 4; l++) s0[u][l] = s1[u][l] = 0.0f;
 #pragma unroll
-        for (int ti = 0; ti < FLASH_TILE; ti++) {
-            if (ti < len) {
-                const float s = ts[ti];
+                    for (int d = 0; d < HD; d += 8) {
+                        const float4 qa = *reinterpret_cast<const float4*>(qrow + d);
+                        const float4 qb4 = *reinterpret_cast<const float4*>(qrow + d + 4);
 #pragma unroll
-                for (int d = 0; d < HD; d += 4) {
-                    float4 vv = *reinterpret_cast<const float4*>(Vs + ti * HD + d);
-                    acc[d + 0] = __fmaf_rn(s, vv.x, acc[d + 0]);
-                    acc[d + 1] = __fmaf_rn(s, vv.y, acc[d + 1]);
-                    acc[d + 2] = __fmaf_rn(s, vv.z, acc[d + 2]);
-                    acc[d + 3] = __fmaf_rn(s, vv.w, acc[d + 3]);
+                        for (int u = 0; u < KB; u++) {
+                            const float* kr = Kt + (4 * (i0 + u) + s) * ROW + d;
+                            const float4 ka = *reinterpret_cast<const float4*>(kr);
+                            const float4 kb = *reinterpret_cast<const float4*>(kr + 4);
+                            s0[u][0] = __fmaf_rn(qa.x, ka.x, s0[u][0]);
+                            s0[u][1] = __fmaf_rn(qa.y, ka.y, s0[u][1]);
+                            s0[u][2] = __fmaf_rn(qa.z, ka.z, s0[u][2]);
+                            s0[u][3] = __fmaf_rn(qa.w, ka.w, s0[u][3]);
+                            s1[u][0] = __fmaf_rn(qb4.x, kb.x, s1[u][0]);
+                            s1[u][1] = __fmaf_rn(qb4.y, kb.y, s1[u][1]);
+                            s1[u][2] = __fmaf_rn(qb4.z, kb.z, s1[u][2]);
+                            s1[u][3] = __fmaf_rn(qb4.w, kb.w, s1[u][3]);
+                        }
+                    }
+#pragma unroll
+                    for (int u = 0; u < KB; u++) {
+                        const float v0 = __fadd_rn(s0[u][0], s1[u][0]), v1 = __fadd_rn(s0[u][1], s1[u][1]);
+                        const float v2 = __fadd_rn(s0[u][2], s1[u][2]), v3 = __fadd_rn(s0[u][3], s1[u][3]);
+                        const float sc = __fmul_rn(__fadd_rn(__fadd_rn(v0, v1), __fadd_rn(v2, v3)), scale);
+                        const bool in = 4 * (i0 + u) + s < len;
+                        e[i0 + u] = in ? sc : __int_as_float(0xFF800000);
+                        if (in && sc > tmax) tmax = sc;
+                    }
+                } else {
+#pragma unroll
+                    for (int u = 0; u < KB; u++) e[i0 + u] = __int_as_float(0xFF800000);
                 }
             }
+            tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
+            tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
+            const float new_max = fmaxf(running_max, tmax);
+            const float rescale = running_max > __int_as_float(0xFF800000) ? ggml_expf(__fsub_rn(running_max, new_max)) : 0.0f;
+#pragma unroll
+            for (int i = 0; i < 8; i++) e[i] = (4 * i + s < len) ? ggml_expf(__fsub_rn(e[i], new_max)) : 0.0f;
+#pragma unroll
+            for (int d = 0; d < DPL; d++) acc[d] = __fmul_rn(acc[d], rescale);
+            double tsum = 0.0;
+#pragma unroll
+            for (int t = 0; t < FLASH_TILE; t++) {
+                const float p = __shfl_sync(0xffffffffu, e[t >> 2], src_base | (t & 3));
+                if (t < len) {
+                    tsum += (double)p;
+                    const float4* vp = reinterpret_cast<const float4*>(Vt + t * ROW + s * DPL);
+#pragma unroll
+                    for (int c = 0; c < DPL / 4; c++) {
+                        const float4 vv = vp[c];
+                        acc[4 * c + 0] = __fmaf_rn(p, vv.x, acc[4 * c + 0]);
+                        acc[4 * c + 1] = __fmaf_rn(p, vv.y, acc[4 * c + 1]);
+                        acc[4 * c + 2] = __fmaf_rn(p, vv.z, acc[4 * c + 2]);
+                        acc[4 * c + 3] = __fmaf_rn(p, vv.w, acc[4 * c + 3]);
+                    }
+                }
+            }
+            if (len > 0) {
+                running_sum = running_sum * (double)rescale + tsum;
+                running_max = new_max;
+            }
         }
-        running_sum = running_sum * (double)rescale + tsum;
-        running_max = new_max;
+        __syncwarp();
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(fa_smem_u32(&empty[buf])) : "memory");
     }
     if (active) {
         const float inv = (float)(1.0 / running_sum);
+        float4* op = reinterpret_cast<float4*>(out + (size_t)j * hs + h * HD + s * DPL);
 #pragma unroll
-        for (int d = 0; d < HD; d++) out[(size_t)j * hs + h * HD + d] = __fmul_rn(acc[d], inv);
+        for (int c = 0; c < DPL / 4; c++)
+            op[c] = make_float4(__fmul_rn(acc[4 * c + 0], inv), __fmul_rn(acc[4 * c + 1], inv), __fmul_rn(acc[4 * c + 2], inv),
+                                __fmul_rn(acc[4 * c + 3], inv));
     }
 }
 
-void launch_attention_flash(cudaStream_t st, const float* q, const float* k_cache, const float* v_cache, float* out,
-                            int n, int start_pos, int n_heads, int n_kv_heads, int head_dim) {
+bool attention_flash_supported(int n_heads, int n_kv_heads, int head_dim) {
+    if (head_dim != 32 && head_dim != 64 && head_dim != 128) return false;
+    return n_kv_heads > 0 && n_heads % n_kv_heads == 0 && n_heads / n_kv_heads <= 8;
+}
+
+template <int HD>
+static cudaError_t launch_flash_hd(cudaStream_t st, const float* q, const float* k_cache, const float* v_cache, float* out, int n,
+                                   int start_pos, int n_heads, int n_kv_heads, uint32_t* err) {
     const int group = n_heads / n_kv_heads;
-    const int qb = FLASH_THREADS / group;
+    const int qb = group <= 4 ? 16 : 8;  // queries per CTA: 8 per consumer warp, at most 8 consumer warps
+    const size_t smem = (size_t)(4 * FLASH_TILE + 64) * (HD + 4) * sizeof(float) + 4 * sizeof(uint64_t) + 16;
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (smem > 48 * 1024 && (dev < 0 || dev >= 64 || !configured[dev])) {
+        e = cudaFuncSetAttribute(k_attention_flash<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
     dim3 grid(n_kv_heads, (n + qb - 1) / qb);
+    const int threads = (group * (qb / 8) + 1) * 32;
     g_kernel_launches++;
-    if (head_dim == 64)
-        k_attention_flash<64><<<grid, FLASH_THREADS, 0, st>>>(q, k_cache, v_cache, out, n, start_pos, n_heads, n_kv_heads);
-    else if (head_dim == 32)
-        k_attention_flash<32><<<grid, FLASH_THREADS, 0, st>>>(q, k_cache, v_cache, out, n, start_pos, n_heads, n_kv_heads);
+    k_attention_flash<HD><<<grid, threads, smem, st>>>(q, k_cache, v_cache, out, n, start_pos, n_heads, n_kv_heads, qb, err);
+    return cudaSuccess;
+}
+
+cudaError_t launch_attention_flash(cudaStream_t st, const float* q, const float* k_cache, const float* v_cache, float* out,
+                                   int n, int start_pos, int n_heads, int n_kv_heads, int head_dim, uint32_t* err) {
+    if (!attention_flash_supported(n_heads, n_kv_heads, head_dim)) return cudaErrorInvalidValue;
+    if (head_dim == 64) return launch_flash_hd<64>(st, q, k_cache, v_cache, out, n, start_pos, n_heads, n_kv_heads, err);
+    if (head_dim == 32) return launch_flash_hd<32>(st, q, k_cache, v_cache, out, n, start_pos, n_heads, n_kv_heads, err);
+    return launch_flash_hd<128>(st, q, k_cache, v_cache, out, n, start_pos, n_heads, n_kv_heads, err);
 }
 
 }  // namespace wick

@@ -657,8 +657,8 @@ void enqueue_prefill_chunk(wick_cuda_model* m, int n, int start_pos, bool flash,
             gemms({{&L.q, &L.tc_q, m->qbuf}, {&L.k, &L.tc_k, m->kbuf}, {&L.v, &L.tc_v, m->vbuf}});
             launch_qknorm_rope_kv(st, m->qbuf, m->kbuf, m->vbuf, L.q_norm, L.k_norm, eps, m->rope_cos, m->rope_sin, L.k_cache,
                                   L.v_cache, n, start_pos, nullptr, m->cfg.n_heads, L.n_kv, hd);
-            if (flash)
-                launch_attention_flash(st, m->qbuf, L.k_cache, L.v_cache, m->attn_out, n, start_pos, m->cfg.n_heads, L.n_kv, hd);
+            if (flash)  // (shapes the tiled kernel does not take were refused when the model was created)
+                launch_attention_flash(st, m->qbuf, L.k_cache, L.v_cache, m->attn_out, n, start_pos, m->cfg.n_heads, L.n_kv, hd, m->tc_err);
             else
                 launch_attention_naive(st, m->qbuf, L.k_cache, L.v_cache, m->attn_out, n, start_pos, nullptr, m->cfg.n_heads,
                                        L.n_kv, hd, m->cfg.max_seq_len);
@@ -688,12 +688,12 @@ int32_t build_tc(wick_cuda_model* m) {
     if (mode && strcmp(mode, "tensor") == 0) m->prefill_mode = WICK_CUDA_PREFILL_TENSOR;
     if (mode && strcmp(mode, "exact-cuda-cores") == 0) m->prefill_mode = WICK_CUDA_PREFILL_EXACT_CUDA_CORES;
     bool ok = tc_gemm_supported(hs, hs) && tc_gemm_supported(hs, is);
+    W_TRY(dev_alloc(m, &m->tc_err, 1));  // error word of the prefill kernels with bounded waits (GEMM and tiled attention)
+    CU_TRY(cudaMemset(m->tc_err, 0, 4));
     if (!ok) {
         if (m->prefill_mode == WICK_CUDA_PREFILL_TENSOR) m->prefill_mode = WICK_CUDA_PREFILL_EXACT;
         return WICK_CUDA_OK;
     }
-    W_TRY(dev_alloc(m, &m->tc_err, 1));
-    CU_TRY(cudaMemset(m->tc_err, 0, 4));
     auto fill = [&](const DevWeight& w, TcWeight* t) -> int32_t {
         t->m_pad = (w.m + 127) / 128 * 128;
         t->m = w.m;
@@ -795,6 +795,11 @@ int32_t build_model(wick_cuda_model* m, const GgufImage& g, uint32_t context_siz
                                                         ") must be > 0 and divide n_heads (" + std::to_string(c.n_heads) + ")");
             L.n_kv = nkv;
             c.n_kv_heads = std::max<uint32_t>(c.n_kv_heads, nkv);
+            // prompts of 256 tokens and more take the tiled attention kernel (lfm2.rs:1646-1647): refuse shapes it lacks
+            if (!attention_flash_supported((int)c.n_heads, nkv, hd))
+                return fail(WICK_CUDA_ERR_UNSUPPORTED_DTYPE, "layer " + std::to_string(i) + ": attention with head_dim " + std::to_string(hd) + " and " +
+                                                                 std::to_string(c.n_heads / nkv) + " query heads per KV head is not supported "
+                                                                 "(head_dim 32, 64 or 128; at most 8 query heads per KV head)");
         }
     }
     // staging buffer for the largest quantised tensor
@@ -1282,7 +1287,7 @@ static int32_t prefill_core(wick_cuda_model* m, const uint32_t* tokens_host, con
     if (m->h_u32[2] != 0) {
         const uint32_t code = m->h_u32[2];
         cudaMemsetAsync(m->tc_err, 0, 4, m->stream);
-        return fail(WICK_CUDA_ERR_TIMEOUT, "tensor-core prefill GEMM: a bounded wait expired (role code " + std::to_string(code) + ")");
+        return fail(WICK_CUDA_ERR_TIMEOUT, "prefill kernel (tensor-core GEMM or tiled attention): a bounded wait expired (code " + std::to_string(code) + ")");
     }
     if (logits_host) memcpy(logits_host, m->h_logits, (size_t)m->cfg.vocab_size * 4);
     if (hidden_host) CU_TRY(cudaMemcpy(hidden_host, m->normed_last, (size_t)hs * 4, cudaMemcpyDeviceToHost));
@@ -1843,9 +1848,19 @@ int32_t wick_cuda_attention_prefill(const float* q_dev, const float* k_cache_dev
     if (!n_kv_heads || n_heads % n_kv_heads || head_dim % 8 || head_dim > 256 || n == 0)
         return fail(WICK_CUDA_ERR_BAD_ARG, "bad attention shape");
     if (flash) {
-        if (head_dim != 64 && head_dim != 32) return fail(WICK_CUDA_ERR_BAD_ARG, "tiled attention supports head_dim 32 or 64");
-        launch_attention_flash((cudaStream_t)stream, q_dev, k_cache_dev, v_cache_dev, out_dev, (int)n, (int)start_pos, (int)n_heads,
-                               (int)n_kv_heads, (int)head_dim);
+        if (!attention_flash_supported((int)n_heads, (int)n_kv_heads, (int)head_dim))
+            return fail(WICK_CUDA_ERR_BAD_ARG, "tiled attention supports head_dim 32, 64 or 128 and at most 8 query heads per KV head");
+        cudaStream_t st = (cudaStream_t)stream;
+        uint32_t* err = nullptr;
+        CU_TRY(cudaMallocAsync((void**)&err, 4, st));
+        CU_TRY(cudaMemsetAsync(err, 0, 4, st));
+        CU_TRY(launch_attention_flash(st, q_dev, k_cache_dev, v_cache_dev, out_dev, (int)n, (int)start_pos, (int)n_heads, (int)n_kv_heads,
+                                      (int)head_dim, err));
+        uint32_t code = 0;
+        CU_TRY(cudaMemcpyAsync(&code, err, 4, cudaMemcpyDeviceToHost, st));
+        CU_TRY(cudaStreamSynchronize(st));
+        CU_TRY(cudaFreeAsync(err, st));
+        if (code) return fail(WICK_CUDA_ERR_TIMEOUT, "tiled attention: a bounded wait expired (code " + std::to_string(code) + ")");
     } else {
         size_t smem = (size_t)(head_dim + start_pos + n) * 4;
         if (smem > 200 * 1024) return fail(WICK_CUDA_ERR_BAD_ARG, "sequence too long for the per-token attention kernel");

@@ -89,6 +89,8 @@ SPECS: Dict[str, Lfm2Spec] = {
     # small shapes for parity tests that a CPU reference finishes in seconds
     "tiny": Lfm2Spec("tiny", 256, 4, (1, 3), 4, 2, 512, 512, 1024),
     "tiny-wide": Lfm2Spec("tiny-wide", 512, 5, (2, 4), 8, 2, 1152, 1024, 2048),
+    "tiny-hd128": Lfm2Spec("tiny-hd128", 512, 3, (1,), 4, 2, 768, 512, 1024),   # 128-wide heads
+    "tiny-longctx": Lfm2Spec("tiny-longctx", 256, 4, (1, 3), 4, 2, 512, 512, 40000),  # contexts beyond 12K positions
 }
 
 

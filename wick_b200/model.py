@@ -185,9 +185,11 @@ class CudaLfm2Model:
         t = np.ascontiguousarray(tokens, dtype=np.uint32)
         ub = max(t.size, 1) if ubatch == 0 else ubatch
         consumed, last = 0, None
+        self.last_chunked_device_ms = 0.0   # GPU time of the chunks of this call (CUDA events on the library's stream)
         for c0 in range(0, t.size, ub):
             chunk = t[c0:c0 + ub]
             last = self.forward_prefill(chunk, start_pos + consumed, state)
+            self.last_chunked_device_ms += self.last_elapsed_ms()
             consumed += chunk.size
             if cancel is not None and cancel.is_set() and consumed < t.size:
                 break
