@@ -250,6 +250,15 @@ int32_t wick_cuda_expf(const float* x_dev, float* y_dev, uint64_t count, void* s
  * exactly as the reference does and uploaded by this call. */
 int32_t wick_cuda_rope(float* q_dev, float* k_dev, uint32_t pos, uint32_t n_heads, uint32_t n_kv_heads,
                        uint32_t head_dim, float freq_base, void* stream);
+/* Per-head RMSNorm of Q and K (shared head_dim-long weights), NeoX RoPE and the KV append of forward_attn_block
+ * (lfm2.rs:783-855) for n rows at positions start_pos..: q [n][n_heads*head_dim] is rotated in place; the rotated K rows
+ * and the V rows go to rows start_pos + j of the caches [rows][n_kv_heads*head_dim].  rope_cos / rope_sin are
+ * [positions][head_dim/2] tables (cpu.rs:2145-2158 gives the values: theta starts at the position and is multiplied
+ * by base^(-2/head_dim) pair by pair). */
+int32_t wick_cuda_qknorm_rope_kv(float* q_dev, const float* k_dev, const float* v_dev, const float* q_norm_dev,
+                                 const float* k_norm_dev, float eps, const float* rope_cos_dev, const float* rope_sin_dev,
+                                 float* k_cache_dev, float* v_cache_dev, uint32_t n, uint32_t start_pos, uint32_t n_heads,
+                                 uint32_t n_kv_heads, uint32_t head_dim, void* stream);
 /* Single-query attention of forward_attn_block (lfm2.rs:980-1007): attn_scores, softmax_inplace,
  * attn_values (cpu.rs:1320-1509, :715-731) for all heads over `seq` cached rows. */
 int32_t wick_cuda_attention_decode(const float* q_dev, const float* k_cache_dev, const float* v_cache_dev,
@@ -299,6 +308,35 @@ int32_t wick_cuda_decode_batch_steps(wick_cuda_model* m, const uint32_t* first_t
                                      uint32_t* out_tokens_host);
 int32_t wick_cuda_decode_batch_logits(wick_cuda_model* m, const uint32_t* tokens_host, const uint32_t* seq_ids_host,
                                       uint32_t bs, float* logits_host);
+
+/* ---- tensor-parallel all-reduce over peer memory (extension) -----------------
+ * wick runs on one device; there is no counterpart in its tree.  For a tensor-parallel split of the LFM2 layers over
+ * the GPUs of one NVLink node (one process per GPU): after every row-split mat-vec (attention output, short-conv
+ * out_proj, FFN down; the steps of run_layers, wick/src/model/lfm2.rs:1020-1124) each rank holds a partial sum of the
+ * hidden row.  wick_cuda_tp_allreduce_add_rmsnorm_quant adds the partials of all ranks (in rank order, so every
+ * rank gets the same bits), adds the sum to `hidden_dev` in place, and - when norm_w_dev is given - applies
+ * cpu::rmsnorm (cpu.rs:577-594) and the Q8_0 activation quantiser (simd.rs:255-323) for the next mat-vec, all in one
+ * kernel that reads the peers' buffers directly (plain loads over NVLink, no multicast).
+ *
+ * Set-up, once per rank: create (allocates this rank's buffer), export its 64-byte IPC handle, gather the handles of
+ * all ranks in rank order by any means (e.g. a host all-gather), connect.  Per call: the rank's partial [dim] must be
+ * written to the address wick_cuda_tp_partial_buffer() returns (it alternates between two halves, ask before every
+ * call) by work enqueued on `stream` before the call.  Every rank must make the same sequence of calls.
+ * The call is asynchronous; device-side waits are bounded (about a second): wick_cuda_tp_status synchronises the
+ * stream and returns WICK_CUDA_ERR_TIMEOUT with the mask of ranks that never arrived (outputs of that call are
+ * then undefined, the context stays usable).  Messages: wick_cuda_tp_last_error(). */
+#define WICK_CUDA_TP_HANDLE_BYTES 64
+typedef struct wick_cuda_tp_comm wick_cuda_tp_comm;
+int32_t wick_cuda_tp_comm_create(uint32_t world, uint32_t rank, uint32_t max_floats, wick_cuda_tp_comm** out);
+int32_t wick_cuda_tp_comm_export(wick_cuda_tp_comm* c, uint8_t* handle_out /* WICK_CUDA_TP_HANDLE_BYTES */);
+int32_t wick_cuda_tp_comm_connect(wick_cuda_tp_comm* c, const uint8_t* handles /* world * WICK_CUDA_TP_HANDLE_BYTES */);
+int32_t wick_cuda_tp_partial_buffer(wick_cuda_tp_comm* c, float** partial_dev);
+int32_t wick_cuda_tp_allreduce_add_rmsnorm_quant(wick_cuda_tp_comm* c, float* hidden_dev, const float* norm_w_dev, float eps,
+                                                 uint32_t dim, float* q8s_dev, int8_t* q8q_dev, float* normed_out_dev,
+                                                 void* stream);
+int32_t wick_cuda_tp_status(wick_cuda_tp_comm* c, void* stream, uint32_t* gave_up_mask);
+void wick_cuda_tp_comm_destroy(wick_cuda_tp_comm* c);
+const char* wick_cuda_tp_last_error(void);
 
 /* ---- allocation-free variant ------------------------------------------------
  * No counterpart in wick: this entry point exists for callers of this library that are not allowed

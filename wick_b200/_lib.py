@@ -76,6 +76,12 @@ SIGNATURES = {
     "wick_cuda_decode_batch": [_vp, _vp, _vp, _u32, _vp],
     "wick_cuda_decode_batch_steps": [_vp, _vp, _vp, _u32, _u32, _vp],
     "wick_cuda_decode_batch_logits": [_vp, _vp, _vp, _u32, _vp],
+    "wick_cuda_tp_comm_create": [_u32, _u32, _u32, C.POINTER(_vp)],
+    "wick_cuda_tp_comm_export": [_vp, _vp],
+    "wick_cuda_tp_comm_connect": [_vp, _vp],
+    "wick_cuda_tp_partial_buffer": [_vp, C.POINTER(_vp)],
+    "wick_cuda_tp_allreduce_add_rmsnorm_quant": [_vp, _vp, _vp, _f, _u32, _vp, _vp, _vp, _vp],
+    "wick_cuda_tp_status": [_vp, _vp, C.POINTER(_u32)],
     "wick_cuda_weight_create": [_i32, _vp, _u32, _u32, C.POINTER(_vp)],
     "wick_cuda_quantize_q8_0": [_vp, _u32, _u32, _vp, _vp, _vp],
     "wick_cuda_gemv_q8": [_vp, _vp, _vp, _vp, _vp],
@@ -87,14 +93,16 @@ SIGNATURES = {
     "wick_cuda_silu_mul": [_vp, _vp, _u64, _vp],
     "wick_cuda_expf": [_vp, _vp, _u64, _vp],
     "wick_cuda_rope": [_vp, _vp, _u32, _u32, _u32, _u32, _f, _vp],
+    "wick_cuda_qknorm_rope_kv": [_vp, _vp, _vp, _vp, _vp, _f, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _vp],
     "wick_cuda_attention_decode": [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _vp],
     "wick_cuda_attention_prefill": [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _i32, _vp],
     "wick_cuda_shortconv": [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _vp],
     "wick_cuda_argmax": [_vp, _u32, _vp, _vp],
     "wick_cuda_argmax_noalloc": [_vp, _u32, _vp, _vp],
 }
-VOID_FUNCS = {"wick_cuda_model_destroy": [_vp], "wick_cuda_weight_destroy": [_vp]}
-ALL_SYMBOLS = sorted(list(SIGNATURES) + list(VOID_FUNCS) + ["wick_cuda_last_error", "wick_cuda_argmax_noalloc_last_error"])
+VOID_FUNCS = {"wick_cuda_model_destroy": [_vp], "wick_cuda_weight_destroy": [_vp], "wick_cuda_tp_comm_destroy": [_vp]}
+ALL_SYMBOLS = sorted(list(SIGNATURES) + list(VOID_FUNCS) + ["wick_cuda_last_error", "wick_cuda_argmax_noalloc_last_error",
+                                                            "wick_cuda_tp_last_error"])
 
 _lib = None
 
@@ -120,11 +128,17 @@ def load() -> C.CDLL:
     lib.wick_cuda_last_error.restype = C.c_char_p
     lib.wick_cuda_argmax_noalloc_last_error.argtypes = []
     lib.wick_cuda_argmax_noalloc_last_error.restype = C.c_char_p
+    lib.wick_cuda_tp_last_error.argtypes = []
+    lib.wick_cuda_tp_last_error.restype = C.c_char_p
     _lib = lib
     return lib
 
 
-def check(code: int) -> None:
+def check(code: int, message=None) -> None:
+    """Raises on a non-zero status; `message` (a callable returning str) overrides the library's general error text
+    for entry points that keep their own (the tensor-parallel communicator)."""
     if code != OK:
+        if message is not None:
+            raise WickCudaError(code, message())
         msg = load().wick_cuda_last_error()
         raise WickCudaError(code, msg.decode("utf-8", "replace") if msg else "")

@@ -1835,6 +1835,18 @@ int32_t wick_cuda_rope(float* q_dev, float* k_dev, uint32_t pos, uint32_t n_head
     OP_END();
 }
 
+int32_t wick_cuda_qknorm_rope_kv(float* q_dev, const float* k_dev, const float* v_dev, const float* q_norm_dev, const float* k_norm_dev,
+                                 float eps, const float* rope_cos_dev, const float* rope_sin_dev, float* k_cache_dev, float* v_cache_dev,
+                                 uint32_t n, uint32_t start_pos, uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim, void* stream) {
+    if (!q_dev || !k_dev || !v_dev || !q_norm_dev || !k_norm_dev || !rope_cos_dev || !rope_sin_dev || !k_cache_dev || !v_cache_dev)
+        return fail(WICK_CUDA_ERR_BAD_ARG, "NULL argument");
+    if (!n_heads || !n_kv_heads || head_dim % 2 || head_dim > 256 || head_dim == 0) return fail(WICK_CUDA_ERR_BAD_ARG, "bad head shape");
+    if (n)
+        launch_qknorm_rope_kv((cudaStream_t)stream, q_dev, k_dev, v_dev, q_norm_dev, k_norm_dev, eps, rope_cos_dev, rope_sin_dev, k_cache_dev,
+                              v_cache_dev, (int)n, (int)start_pos, nullptr, (int)n_heads, (int)n_kv_heads, (int)head_dim);
+    OP_END();
+}
+
 int32_t wick_cuda_attention_decode(const float* q_dev, const float* k_cache_dev, const float* v_cache_dev, float* out_dev,
                                    uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim, uint32_t seq, void* stream) {
     return wick_cuda_attention_prefill(q_dev, k_cache_dev, v_cache_dev, out_dev, 1, seq ? seq - 1 : 0, n_heads, n_kv_heads,

@@ -127,6 +127,16 @@ def rope_(q: torch.Tensor, k: torch.Tensor, pos: int, n_heads: int, n_kv_heads: 
     return q, k
 
 
+def qknorm_rope_kv_(q, k, v, q_norm, k_norm, eps: float, rope_cos, rope_sin, k_cache, v_cache, start_pos: int, n_heads: int,
+                    n_kv_heads: int, head_dim: int):
+    """Per-head RMSNorm of Q and K, RoPE from a (position, pair) cos / sin table, and the append of the rotated K rows
+    and the V rows to the caches at rows start_pos.. (lfm2.rs:783-855) for the n rows of q [n, n_heads * head_dim]."""
+    n = q.shape[0]
+    check(_lib.load().wick_cuda_qknorm_rope_kv(_ptr(q), _ptr(k), _ptr(v), _ptr(q_norm), _ptr(k_norm), eps, _ptr(rope_cos), _ptr(rope_sin),
+                                               _ptr(k_cache), _ptr(v_cache), n, start_pos, n_heads, n_kv_heads, head_dim, _stream()))
+    return q
+
+
 def attention_decode(q, k_cache, v_cache, n_heads, n_kv_heads, head_dim, seq) -> torch.Tensor:
     out = torch.empty(n_heads * head_dim, dtype=torch.float32, device=q.device)
     check(_lib.load().wick_cuda_attention_decode(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), n_heads, n_kv_heads,
