@@ -314,7 +314,7 @@ int32_t wick_cuda_decode_batch_logits(wick_cuda_model* m, const uint32_t* tokens
  * the GPUs of one NVLink node (one process per GPU): after every row-split mat-vec (attention output, short-conv
  * out_proj, FFN down; the steps of run_layers, wick/src/model/lfm2.rs:1020-1124) each rank holds a partial sum of the
  * hidden row.  wick_cuda_tp_allreduce_add_rmsnorm_quant adds the partials of all ranks (in rank order, so every
- * rank gets the same bits), adds the sum to `hidden_dev` in place, and - when norm_w_dev is given - applies
+ * rank gets the same bits), adds the sum to `hidden_dev` (16-byte aligned) in place, and - when norm_w_dev is given - applies
  * cpu::rmsnorm (cpu.rs:577-594) and the Q8_0 activation quantiser (simd.rs:255-323) for the next mat-vec, all in one
  * kernel that reads the peers' buffers directly (plain loads over NVLink, no multicast).
  *

@@ -45,9 +45,9 @@ __device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
 __device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
-__device__ __forceinline__ float ld_peer(const float* p) {
-    float v;
-    asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+__device__ __forceinline__ float4 ld_peer4(const float* p) {  // 16-byte aligned
+    float4 v;
+    asm volatile("ld.relaxed.sys.global.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
     return v;
 }
 
@@ -57,7 +57,7 @@ __global__ void __launch_bounds__(TP_THREADS) k_tp_allreduce_add_rmsnorm_quant(T
                                                                                const float* __restrict__ weight, float eps, int dim,
                                                                                float* __restrict__ q8s, int8_t* __restrict__ q8q,
                                                                                float* __restrict__ normed_out, unsigned int* __restrict__ status) {
-    extern __shared__ float xs[];
+    extern __shared__ __align__(16) float xs[];
     __shared__ double red[32];
     __shared__ int failed;
     const int half = (int)(seq & 1u);
@@ -84,12 +84,28 @@ __global__ void __launch_bounds__(TP_THREADS) k_tp_allreduce_add_rmsnorm_quant(T
     }
     __syncthreads();
     if (failed) return;
-    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
-        float sum = 0.0f;
-        for (int p = 0; p < world; p++) sum = __fadd_rn(sum, ld_peer(peers.data[p] + (size_t)half * max_floats + i));
-        const float v = __fadd_rn(hidden[i], sum);
-        hidden[i] = v;
-        xs[i] = v;
+    // every peer's piece is requested before the first addition, so the loop costs one NVLink round trip, not `world`
+    for (int i4 = threadIdx.x; i4 < dim / 4; i4 += blockDim.x) {
+        float4 part[TP_MAX_WORLD];
+#pragma unroll
+        for (int p = 0; p < TP_MAX_WORLD; p++)
+            if (p < world) part[p] = ld_peer4(peers.data[p] + (size_t)half * max_floats + 4 * i4);
+        float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int p = 0; p < TP_MAX_WORLD; p++)
+            if (p < world) {
+                sum.x = __fadd_rn(sum.x, part[p].x);
+                sum.y = __fadd_rn(sum.y, part[p].y);
+                sum.z = __fadd_rn(sum.z, part[p].z);
+                sum.w = __fadd_rn(sum.w, part[p].w);
+            }
+        float4 h = reinterpret_cast<float4*>(hidden)[i4];
+        h.x = __fadd_rn(h.x, sum.x);
+        h.y = __fadd_rn(h.y, sum.y);
+        h.z = __fadd_rn(h.z, sum.z);
+        h.w = __fadd_rn(h.w, sum.w);
+        reinterpret_cast<float4*>(hidden)[i4] = h;
+        reinterpret_cast<float4*>(xs)[i4] = h;
     }
     __syncthreads();
     if (!weight) return;  // plain all-reduce + residual add
@@ -207,6 +223,7 @@ int32_t wick_cuda_tp_allreduce_add_rmsnorm_quant(wick_cuda_tp_comm* c, float* hi
     if (!c || !hidden_dev) return tp_fail(WICK_CUDA_ERR_BAD_ARG, "NULL argument");
     if (!c->connected) return tp_fail(WICK_CUDA_ERR_BAD_ARG, "communicator is not connected");
     if (dim == 0 || dim % QK || (int)dim > c->max_floats) return tp_fail(WICK_CUDA_ERR_BAD_ARG, "dim must be a multiple of 32 within the communicator's size");
+    if ((uintptr_t)hidden_dev & 15) return tp_fail(WICK_CUDA_ERR_BAD_ARG, "hidden_dev must be 16-byte aligned");
     if (norm_w_dev && q8q_dev && !q8s_dev) return tp_fail(WICK_CUDA_ERR_BAD_ARG, "q8s_dev is NULL");
     c->seq += 1;
     g_kernel_launches++;
