@@ -190,3 +190,21 @@ def test_config4_many_sequences_one_model(wick, orc, model_dir):
             assert np.array_equal(bits(lg), bits(lo))
             first = orc.argmax(lo)
             assert list(cm.generate_greedy(first, 32, st)) == list(om.generate_greedy(first, 32))
+
+
+def test_device_memory_of_the_1p6b_q4_0_model(wick, model_dir):
+    """wick asserts < 800 MB of GPU memory for its 1.6B-class Q4_0 model at a 4096-token context
+    (wick/tests/bench_perf.rs:209-220).  Decode and short prompts stay under that here; the first prompt chunk of 16 tokens
+    or more adds the int8 weight copies of the tensor-core GEMM (reported, bounded)."""
+    from wick_b200 import gguf_synth as gs
+    path = _path(model_dir, "lfm2.5-1.6b", "q4_0")
+    cm = wick.CudaLfm2Model(path, 4096)
+    st = wick.InferenceState()
+    cm.forward_prefill(gs.random_prompt(8, cm.config().vocab_size, seed=1), 0, st)
+    cm.generate_greedy(1, 4, st)
+    base = cm.gpu_memory_bytes()
+    assert base < 800e6, f"{base / 1e6:.0f} MB before any tensor-core prefill"
+    cm.forward_prefill(gs.random_prompt(64, cm.config().vocab_size, seed=1), 0, st)
+    full = cm.gpu_memory_bytes()
+    assert base < full < 2.0e9, f"{full / 1e6:.0f} MB with the tensor-core copies"
+    print(f"gpu memory: {base / 1e6:.0f} MB decode-only, {full / 1e6:.0f} MB after a tensor-core prefill")

@@ -78,7 +78,8 @@ struct wick_cuda_model {
     int max_chunk = 0;  // tokens of scratch
     // tensor-core prefill GEMMs: available when every matrix meets tc_gemm_supported(); prefill_mode
     // picks the bit-exact one (default), the fused-chain one, or the bit-exact CUDA-core kernel
-    bool tc_ok = false;
+    bool tc_ok = false;     // the model's shapes allow the tensor-core GEMM
+    bool tc_built = false;  // its int8 weight copies and buffers exist (made by the first call that needs them)
     int prefill_mode = WICK_CUDA_PREFILL_EXACT;
     CUtensorMap map_x_hs[2], map_x_is[2];  // activations [max_chunk][hs | is], box of 64 / 128 rows
     int8_t* q8m = nullptr;                  // lane-group-masked activations [4 * max_chunk][hs | is] (exact tensor-core GEMM)
@@ -609,7 +610,7 @@ struct GemmTarget {
 void run_gemms(wick_cuda_model* m, int n, std::initializer_list<GemmTarget> list) {
     cudaStream_t st = m->stream;
     const int hs = m->cfg.hidden_size;
-    const bool tc = m->tc_ok && n >= 16 && m->prefill_mode != WICK_CUDA_PREFILL_EXACT_CUDA_CORES;
+    const bool tc = m->tc_built && n >= 16 && m->prefill_mode != WICK_CUDA_PREFILL_EXACT_CUDA_CORES;
     const bool tc_exact = tc && m->prefill_mode == WICK_CUDA_PREFILL_EXACT;
     if (tc) {
         const TcWeight* tw[3];
@@ -679,21 +680,25 @@ void enqueue_prefill_chunk(wick_cuda_model* m, int n, int start_pos, bool flash,
     }
 }
 
-// int8 copies of the layer matrices + activation tensor maps for the tensor-core prefill GEMM.
+// Tensor-core prefill GEMM: decided at load (tc_ok = the shapes allow it), built on first use (ensure_tc): the int8
+// copies of the layer matrices, the activation tensor maps and the masked-activation buffer cost about 1.7 bytes per
+// parameter, which a decode-only user never needs.
 int32_t build_tc(wick_cuda_model* m) {
     const int hs = m->cfg.hidden_size, is = m->cfg.intermediate_size;
-    m->tc_ok = false;
     const char* mode = getenv("WICK_CUDA_PREFILL");
     m->prefill_mode = WICK_CUDA_PREFILL_EXACT;
     if (mode && strcmp(mode, "tensor") == 0) m->prefill_mode = WICK_CUDA_PREFILL_TENSOR;
     if (mode && strcmp(mode, "exact-cuda-cores") == 0) m->prefill_mode = WICK_CUDA_PREFILL_EXACT_CUDA_CORES;
-    bool ok = tc_gemm_supported(hs, hs) && tc_gemm_supported(hs, is);
+    m->tc_ok = tc_gemm_supported(hs, hs) && tc_gemm_supported(hs, is);
     W_TRY(dev_alloc(m, &m->tc_err, 1));  // error word of the prefill kernels with bounded waits (GEMM and tiled attention)
     CU_TRY(cudaMemset(m->tc_err, 0, 4));
-    if (!ok) {
-        if (m->prefill_mode == WICK_CUDA_PREFILL_TENSOR) m->prefill_mode = WICK_CUDA_PREFILL_EXACT;
-        return WICK_CUDA_OK;
-    }
+    if (!m->tc_ok && m->prefill_mode == WICK_CUDA_PREFILL_TENSOR) m->prefill_mode = WICK_CUDA_PREFILL_EXACT;
+    return WICK_CUDA_OK;
+}
+
+int32_t ensure_tc(wick_cuda_model* m) {
+    if (!m->tc_ok || m->tc_built || m->prefill_mode == WICK_CUDA_PREFILL_EXACT_CUDA_CORES) return WICK_CUDA_OK;
+    const int hs = m->cfg.hidden_size, is = m->cfg.intermediate_size;
     auto fill = [&](const DevWeight& w, TcWeight* t) -> int32_t {
         t->m_pad = (w.m + 127) / 128 * 128;
         t->m = w.m;
@@ -725,7 +730,7 @@ int32_t build_tc(wick_cuda_model* m) {
     CU_TRY(tc_make_activation_map(m->q8m, 4 * m->max_chunk, hs, 64, &m->map_xm_hs));
     CU_TRY(tc_make_activation_map(m->q8m, 4 * m->max_chunk, is, 64, &m->map_xm_is));
     CU_TRY(cudaStreamSynchronize(m->stream));
-    m->tc_ok = true;
+    m->tc_built = true;
     return WICK_CUDA_OK;
 }
 
@@ -854,7 +859,14 @@ int32_t build_model(wick_cuda_model* m, const GgufImage& g, uint32_t context_siz
         CU_TRY(cudaMemcpy(m->rope_sin, sn.data(), sn.size() * 4, cudaMemcpyHostToDevice));
     }
     // scratch
-    m->max_chunk = (int)std::min<uint32_t>(c.max_seq_len, 4096);
+    // Tokens of activation scratch (longer prefill calls are cut into pieces of this size internally; results do not
+    // depend on it).  The default is wick's own prefill chunk of 512 tokens (--ubatch-size); WICK_CUDA_MAX_CHUNK
+    // overrides it (e.g. 4096: one GEMM pass per 4096-token call, at 0.45 GB more scratch for a 1.6B-class model).
+    {
+        int want = 512;
+        if (const char* e = getenv("WICK_CUDA_MAX_CHUNK")) want = std::max(16, std::min(atoi(e), 8192));
+        m->max_chunk = (int)std::min<uint32_t>(c.max_seq_len, (uint32_t)want);
+    }
     const size_t N = m->max_chunk;
     const int kvmax = c.n_kv_heads * hd;
     W_TRY(dev_alloc(m, &m->hidden, N * hs));
@@ -1032,6 +1044,7 @@ int32_t decode_rows(wick_cuda_model* m, const uint32_t* tokens_host, const uint3
                                                         std::to_string(m->cfg.max_seq_len));
     }
     CU_TRY(cudaSetDevice(m->device));
+    if (bs >= 16) W_TRY(ensure_tc(m));
     W_TRY(ensure_batch_buffers(m, bs, n_steps));
     const size_t nl = m->layers.size();
     const int cap = m->batch_cap;
@@ -1259,6 +1272,7 @@ static int32_t prefill_core(wick_cuda_model* m, const uint32_t* tokens_host, con
         return fail(WICK_CUDA_ERR_CONTEXT_FULL, "start_pos + n = " + std::to_string((uint64_t)start_pos + n) +
                                                     " exceeds max_seq_len " + std::to_string(m->cfg.max_seq_len));
     CU_TRY(cudaSetDevice(m->device));
+    if (n >= 16) W_TRY(ensure_tc(m));
     if (start_pos == 0) W_TRY(reset_sequence(m));  // new sequence, metal_lfm2.rs:2361-2397
     const bool flash = n >= 256;  // FLASH_ATTN_THRESHOLD, lfm2.rs:1646-1647
     CU_TRY(cudaEventRecord(m->ev0, m->stream));
