@@ -278,6 +278,18 @@ int32_t wick_cuda_shortconv(const float* proj_dev, const float* conv_w_dev, floa
 /* cpu_argmax (sampler.rs:8-19) of `count` logits -> *out_dev. */
 int32_t wick_cuda_argmax(const float* logits_dev, uint32_t count, uint32_t* out_dev, void* stream);
 
+/* Model::forward followed by Sampler::sample (wick/src/sampler.rs:64-158) with the logits kept on the device: temperature
+ * scaling, top-k, top-p, softmax_inplace and the weighted pick, in the reference's order; 4 bytes come back.  `r` is the
+ * uniform draw in [0, 1) that wick takes from its `rand` StdRng (`self.rng.gen::<f32>()`, sampler.rs:151): the generator
+ * stays with the caller.  temperature <= 0 or top_k == 1 is the greedy path.  top_p < 1 needs 1 <= top_k <= 4096
+ * (BAD_ARG otherwise, and when more than 4096 logits tie at the threshold): read the logits back with
+ * wick_cuda_forward and sample on the host in that case.  wick_cuda_sample_logits is the same sampler on any device
+ * logits (operator form, *out_dev on the device; synchronises the stream). */
+int32_t wick_cuda_forward_sample(wick_cuda_model* m, uint32_t token, uint32_t pos, float temperature, uint32_t top_k,
+                                 float top_p, float r, uint32_t* next_token);
+int32_t wick_cuda_sample_logits(const float* logits_dev, uint32_t count, float temperature, uint32_t top_k, float top_p,
+                                float r, uint32_t* out_dev, void* stream);
+
 /* ---- many sequences on one model (extension) --------------------------------
  * wick's Model trait keeps ONE sequence per model instance, serialised behind `infer_lock`
  * (wick/src/model/mod.rs:56-71; the GPU backends keep that sequence's state inside the model,

@@ -46,6 +46,8 @@ def lib() -> C.CDLL:
         _lib.orc_f16_round.restype = C.c_float
         _lib.orc_f16_round.argtypes = [C.c_float]
         _lib.orc_argmax.restype = C.c_uint32
+        _lib.orc_sample.restype = C.c_uint32
+        _lib.orc_sample.argtypes = [C.c_void_p, C.c_int, C.c_float, C.c_int, C.c_float, C.c_float]
         _lib.orc_model_create.restype = C.c_void_p
         _lib.orc_model_seq_len.restype = C.c_int
         _lib.orc_model_kv_rows.restype = C.c_int
@@ -186,6 +188,12 @@ def flash_attention_gqa(q_mat, kc, vc, n_heads_start, group, n_queries, q_stride
 def argmax(x: np.ndarray) -> int:
     x = _f32(x)
     return int(lib().orc_argmax(_p(x), C.c_int(x.size)))
+
+
+def sample(logits: np.ndarray, temperature: float, top_k: int, top_p: float, r: float) -> int:
+    """Sampler::sample (sampler.rs:64-158) with the uniform draw r given by the caller."""
+    x = _f32(logits)
+    return int(lib().orc_sample(x.ctypes.data, C.c_int(x.size), C.c_float(temperature), C.c_int(top_k), C.c_float(top_p), C.c_float(r)))
 
 
 def dequant_row(dtype: int, row: np.ndarray, k: int) -> np.ndarray:

@@ -944,6 +944,55 @@ ORC_API void orc_flash_attention_gqa(const float* q_mat, const float* kc, const 
     }
 }
 ORC_API uint32_t orc_argmax(const float* x, int n) { return argmax(x, n); }
+// Sampler::sample (sampler.rs:64-158) with the uniform draw `r` supplied by the caller (wick draws it from `rand`'s
+// StdRng; the generator is outside this path).  Works on a copy of the logits.  Ties: top-k keeps every value equal to
+// the k-th largest (`*l < threshold` is what gets dropped); top-p orders equal values by ascending index (wick's
+// unstable sort leaves their order unspecified, which can only change WHICH of several equal logits is cut).
+ORC_API uint32_t orc_sample(const float* logits_in, int n, float temperature, int top_k, float top_p, float r) {
+    std::vector<float> logits(logits_in, logits_in + n);
+    if (temperature <= 0.0f || top_k == 1) return argmax(logits.data(), n);
+    const float inv_temp = 1.0f / temperature;
+    for (float& l : logits) l *= inv_temp;
+    if (top_k > 0 && top_k < n) {  // apply_top_k, sampler.rs:100-111
+        std::vector<float> sorted(logits);
+        std::nth_element(sorted.begin(), sorted.begin() + (top_k - 1), sorted.end(), [](float a, float b) { return a > b; });
+        const float threshold = sorted[top_k - 1];
+        for (float& l : logits)
+            if (l < threshold) l = -std::numeric_limits<float>::infinity();
+    }
+    if (top_p < 1.0f) {  // apply_top_p, sampler.rs:113-145
+        std::vector<int> idx;
+        for (int i = 0; i < n; i++)
+            if (std::isfinite(logits[i])) idx.push_back(i);
+        if (!idx.empty()) {
+            std::stable_sort(idx.begin(), idx.end(), [&](int a, int b) { return logits[a] > logits[b]; });
+            const float max_val = logits[idx[0]];
+            std::vector<float> probs(idx.size());
+            for (size_t j = 0; j < idx.size(); j++) probs[j] = expf(logits[idx[j]] - max_val);
+            float sum = 0.0f;
+            for (float p : probs) sum += p;
+            for (float& p : probs) p /= sum;
+            size_t cutoff = probs.size();
+            float cumsum = 0.0f;
+            for (size_t j = 0; j < probs.size(); j++) {
+                cumsum += probs[j];
+                if (cumsum >= top_p) {
+                    cutoff = j + 1;
+                    break;
+                }
+            }
+            for (size_t j = cutoff; j < idx.size(); j++) logits[idx[j]] = -std::numeric_limits<float>::infinity();
+        }
+    }
+    softmax(logits.data(), n);  // cpu::softmax_inplace
+    float cumsum = 0.0f;          // weighted_sample, sampler.rs:147-158
+    for (int i = 0; i < n; i++) {
+        cumsum += logits[i];
+        if (cumsum >= r) return (uint32_t)i;
+    }
+    return (uint32_t)(n - 1);
+}
+
 ORC_API void orc_dequant_row(int dtype, const uint8_t* row, int k, float* out) { dequant_row(dtype, row, k, out); }
 
 ORC_API void* orc_model_create(const OrcModelDesc* d) {

@@ -69,6 +69,8 @@ SIGNATURES = {
     "wick_cuda_decode_path": [_vp, C.POINTER(_i32)],
     "wick_cuda_read_kv": [_vp, _u32, _vp, _vp],
     "wick_cuda_read_conv_state": [_vp, _u32, _vp],
+    "wick_cuda_forward_sample": [_vp, _u32, _u32, _f, _u32, _f, _f, C.POINTER(_u32)],
+    "wick_cuda_sample_logits": [_vp, _u32, _f, _u32, _f, _f, _vp, _vp],
     "wick_cuda_seq_create": [_vp, C.POINTER(_u32)],
     "wick_cuda_seq_destroy": [_vp, _u32],
     "wick_cuda_seq_length": [_vp, _u32, C.POINTER(_u32)],

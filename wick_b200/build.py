@@ -15,7 +15,7 @@ from typing import List
 _HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(_HERE, "csrc")
 LIB_PATH = os.path.join(_HERE, "libwick_cuda.so")
-SOURCES = ["kernels_basic.cu", "kernels_gemv.cu", "kernels_attn.cu", "kernels_q6k.cu", "kernels_batch.cu", "tp_comm.cu", "decode_mega.cu", "gemm_tc.cu", "argmax_noalloc.cu", "wick_cuda.cu"]
+SOURCES = ["kernels_basic.cu", "kernels_gemv.cu", "kernels_attn.cu", "kernels_q6k.cu", "kernels_batch.cu", "kernels_sample.cu", "tp_comm.cu", "decode_mega.cu", "gemm_tc.cu", "argmax_noalloc.cu", "wick_cuda.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

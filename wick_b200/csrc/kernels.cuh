@@ -106,6 +106,11 @@ cudaError_t launch_attention_rows(cudaStream_t st, const float* q, float* const*
 void launch_argmax_rows(cudaStream_t st, const float* logits, int n, int count, uint32_t* out);
 void launch_rows_advance(cudaStream_t st, uint32_t* tokens, const uint32_t* next, uint32_t* positions, uint32_t* out_table, int n, int step);
 
+// Sampler::sample (sampler.rs:64-158) of n device logits with the uniform draw r; val / idx are n-element work arrays.
+// *status gets bit 0 when top-p would need more than 4096 survivors sorted (nothing is written to *out then).
+void launch_sample(cudaStream_t st, const float* logits, int n, float temperature, int top_k, float top_p, float r, float* val, int* idx,
+                   uint32_t* out, uint32_t* status);
+
 // cpu_argmax (sampler.rs:8-19).  Uses ctl->argmax as scratch when ctl != NULL, else `scratch`.
 void launch_argmax(cudaStream_t st, const float* logits, int count, unsigned long long* scratch, uint32_t* out);
 // End of a decode step on the device: token <- argmax, pos += 1, ring[step++] = token.

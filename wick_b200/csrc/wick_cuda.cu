@@ -130,6 +130,9 @@ struct wick_cuda_model {
         std::vector<float*> k_cache, v_cache, conv_state;  // per layer (NULL where the layer has none)
     };
     std::vector<SeqSlot> seqs;
+    float* sample_val = nullptr;        // [vocab] work arrays of the on-device sampler, made on first use
+    int* sample_idx = nullptr;
+    uint32_t* sample_status = nullptr;
     int batch_cap = 0;                  // rows the batch buffers below hold
     float* logits_rows = nullptr;       // [batch_cap][vocab]
     uint32_t *rows_tok = nullptr, *rows_next = nullptr, *rows_pos = nullptr, *rows_out = nullptr;  // device; rows_out [steps][rows]
@@ -1228,6 +1231,47 @@ int32_t wick_cuda_forward_greedy(wick_cuda_model* m, uint32_t token, uint32_t po
     return WICK_CUDA_OK;
 }
 
+// Model::forward followed by Sampler::sample (sampler.rs:64-158) on the device: the logits never leave the GPU.
+int32_t wick_cuda_forward_sample(wick_cuda_model* m, uint32_t token, uint32_t pos, float temperature, uint32_t top_k, float top_p, float r,
+                                 uint32_t* next_token) {
+    W_TRY(pre_step(m, token, pos));
+    if (!next_token) return fail(WICK_CUDA_ERR_BAD_ARG, "next_token is NULL");
+    if (temperature <= 0.0f || top_k == 1) return wick_cuda_forward_greedy(m, token, pos, next_token);  // sampler.rs:71-73
+    if (top_p < 1.0f && (top_k == 0 || top_k > 4096))
+        return fail(WICK_CUDA_ERR_BAD_ARG, "on-device top-p needs 1 <= top_k <= 4096 (read the logits back and sample on the host instead)");
+    if (!m->sample_val) {
+        W_TRY(dev_alloc(m, &m->sample_val, (size_t)m->cfg.vocab_size));
+        W_TRY(dev_alloc(m, &m->sample_idx, (size_t)m->cfg.vocab_size));
+        W_TRY(dev_alloc(m, &m->sample_status, 1));
+        CU_TRY(cudaMemset(m->sample_status, 0, 4));
+    }
+    m->h_u32[0] = token;
+    CU_TRY(cudaEventRecord(m->ev0, m->stream));
+    CU_TRY(cudaMemcpyAsync(&m->ctl->token, m->h_u32, 4, cudaMemcpyHostToDevice, m->stream));
+    if (m->mega_ok) {
+        W_TRY(run_mega(m, 1, false));
+    } else {
+        CU_TRY(cudaGraphLaunch(m->g_logits, m->stream));
+        m->launches += m->nodes_logits;
+    }
+    launch_sample(m->stream, m->logits, (int)m->cfg.vocab_size, temperature, (int)top_k, top_p, r, m->sample_val, m->sample_idx, m->argmax_tok,
+                  m->sample_status);
+    m->launches += 1;
+    CU_TRY(cudaGetLastError());
+    CU_TRY(cudaMemcpyAsync(m->h_u32 + 1, m->argmax_tok, 4, cudaMemcpyDeviceToHost, m->stream));
+    CU_TRY(cudaMemcpyAsync(m->h_u32 + 2, m->sample_status, 4, cudaMemcpyDeviceToHost, m->stream));
+    CU_TRY(cudaEventRecord(m->ev1, m->stream));
+    CU_TRY(cudaStreamSynchronize(m->stream));
+    if (m->mega_ok) W_TRY(check_mega_status(m));
+    m->seq_len += 1;  // the step itself has run
+    if (m->h_u32[2]) {
+        cudaMemsetAsync(m->sample_status, 0, 4, m->stream);
+        return fail(WICK_CUDA_ERR_BAD_ARG, "on-device top-p: more than 4096 logits tie at or above the top-k threshold");
+    }
+    *next_token = m->h_u32[1];
+    return WICK_CUDA_OK;
+}
+
 int32_t wick_cuda_generate_greedy(wick_cuda_model* m, uint32_t first_token, uint32_t n_steps, uint32_t* out_tokens_host) {
     W_TRY(check_model(m));
     if (n_steps == 0) return WICK_CUDA_OK;
@@ -1905,6 +1949,24 @@ int32_t wick_cuda_shortconv(const float* proj_dev, const float* conv_w_dev, floa
     if (hidden % QK || kernel_size < 1 || kernel_size > 8) return fail(WICK_CUDA_ERR_BAD_ARG, "bad short-conv shape");
     launch_shortconv((cudaStream_t)stream, proj_dev, conv_w_dev, state_dev, (int)n, (int)hidden, (int)kernel_size, out_dev, nullptr,
                      nullptr);
+    OP_END();
+}
+
+int32_t wick_cuda_sample_logits(const float* logits_dev, uint32_t count, float temperature, uint32_t top_k, float top_p, float r,
+                                uint32_t* out_dev, void* stream) {
+    if (!logits_dev || !out_dev || !count) return fail(WICK_CUDA_ERR_BAD_ARG, "NULL argument or empty input");
+    if (temperature <= 0.0f || top_k == 1) return wick_cuda_argmax(logits_dev, count, out_dev, stream);
+    cudaStream_t st = (cudaStream_t)stream;
+    uint8_t* scratch = nullptr;
+    CU_TRY(cudaMallocAsync((void**)&scratch, (size_t)count * 8 + 16, st));
+    uint32_t* status = (uint32_t*)(scratch + (size_t)count * 8);
+    CU_TRY(cudaMemsetAsync(status, 0, 4, st));
+    launch_sample(st, logits_dev, (int)count, temperature, (int)top_k, top_p, r, (float*)scratch, (int*)(scratch + (size_t)count * 4), out_dev, status);
+    uint32_t code = 0;
+    CU_TRY(cudaMemcpyAsync(&code, status, 4, cudaMemcpyDeviceToHost, st));
+    CU_TRY(cudaStreamSynchronize(st));
+    CU_TRY(cudaFreeAsync(scratch, st));
+    if (code) return fail(WICK_CUDA_ERR_BAD_ARG, "on-device top-p needs at most 4096 logits at or above the top-k threshold");
     OP_END();
 }
 

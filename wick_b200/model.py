@@ -313,6 +313,17 @@ class CudaLfm2Model:
         return s
 
 
+    def forward_sample(self, tokens: Sequence[int], pos: int, state: InferenceState, temperature: float, top_k: int, top_p: float,
+                       r: float) -> int:
+        """Model::forward + Sampler::sample (sampler.rs:64-158) with the logits kept on the GPU; r is the caller's
+        uniform draw in [0, 1)."""
+        assert len(tokens) == 1, "CUDA forward expects single token"
+        nxt = C.c_uint32(0)
+        with self._lock:
+            check(self._lib.wick_cuda_forward_sample(self._h, int(tokens[0]), int(pos), temperature, int(top_k), top_p, r, C.byref(nxt)))
+        state.seq_len += 1
+        return nxt.value
+
     # ---- many sequences on one model (extension; not part of trait Model) ------
     def seq_create(self) -> int:
         """A new sequence slot (own KV caches, conv buffers, length) on this model's weights."""

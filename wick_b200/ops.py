@@ -165,6 +165,13 @@ def argmax(logits: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def sample_logits(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, r: float) -> int:
+    """Sampler::sample (sampler.rs:64-158) on device logits with the caller's uniform draw r."""
+    out = torch.empty(1, dtype=torch.int32, device=logits.device)
+    check(_lib.load().wick_cuda_sample_logits(_ptr(logits), logits.numel(), temperature, top_k, top_p, r, _ptr(out), _stream()))
+    return int(out.item())
+
+
 ARGMAX_NOALLOC_MAX = 4096 * 1024
 
 

@@ -52,7 +52,7 @@ extern "C" {
     pub fn wick_cuda_restore(m: *mut WickCudaModel, snap: *const u8, len: u64) -> i32;
     pub fn wick_cuda_set_prefill_mode(m: *mut WickCudaModel, mode: i32) -> i32;
     pub fn wick_cuda_generate_greedy(m: *mut WickCudaModel, first: u32, n_steps: u32, out: *mut u32) -> i32;
-    pub fn wick_cuda_sample(m: *mut WickCudaModel, temperature: f32, top_k: u32, top_p: f32, r: f32, token: *mut u32) -> i32;
+    pub fn wick_cuda_forward_sample(m: *mut WickCudaModel, token: u32, pos: u32, temperature: f32, top_k: u32, top_p: f32, r: f32, next: *mut u32) -> i32;
     // many sequences on one model (not part of `trait Model`)
     pub fn wick_cuda_seq_create(m: *mut WickCudaModel, seq_id: *mut u32) -> i32;
     pub fn wick_cuda_seq_destroy(m: *mut WickCudaModel, seq_id: u32) -> i32;

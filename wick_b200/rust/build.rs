@@ -13,6 +13,7 @@ const SOURCES: &[&str] = &[
     "kernels_q6k.cu",
     "kernels_batch.cu",
     "kernels_sample.cu",
+    "tp_comm.cu",
     "decode_mega.cu",
     "gemm_tc.cu",
     "argmax_noalloc.cu",
