@@ -185,6 +185,11 @@ __device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
     asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
     return r;
 }
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
+    f32x2 r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 }  // namespace
@@ -415,9 +420,10 @@ k_gemm_tc(const __grid_constant__ TcJob job, const __grid_constant__ CUtensorMap
             // chains acc[parity of the block][lane group] += float(lane partial) * (f16(d_w) * d_x), blocks
             // in ascending order, combined at the end as ((a0+a1)+(a2+a3)) per parity, even + odd.
             constexpr int TPT = COLS / 4;  // tokens per thread
-            // (scalar on purpose: ptxas contracts a packed mul.rn.f32x2 feeding an add.rn.f32x2 into one fused
-            // multiply-add even with contraction switched off, which changes the rounding)
-            float acc[TPT][2][4];
+            // The products are formed one by one; the chain additions go out two lanes at a time (add.rn.f32x2).  A packed
+            // multiply feeding a packed add directly is turned into a fused multiply-add by the assembler, whatever the
+            // rounding modifiers say (wrong rounding for this contract); scalar products into a packed add are left alone.
+            f32x2 acc2[TPT][2][2];
             for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
                 const TcTile tl = tc_decode_tile(job, t, tiles_n, TOK);
                 const int m = job.m[tl.mat];
@@ -425,7 +431,9 @@ k_gemm_tc(const __grid_constant__ TcJob job, const __grid_constant__ CUtensorMap
 #pragma unroll
                 for (int i = 0; i < TPT; i++)
 #pragma unroll
-                    for (int l = 0; l < 4; l++) acc[i][0][l] = acc[i][1][l] = 0.f;
+                    for (int l = 0; l < 4; l++) {
+                        acc2[i][0][l >> 1] = acc2[i][1][l >> 1] = pack2(0.f, 0.f);
+                    }
                 for (int ks = 0; ks < k_stages && ok; ks++, g++) {
                     const int s = g % TC_STAGES;
                     const uint32_t u = g / TC_STAGES;
@@ -456,9 +464,11 @@ k_gemm_tc(const __grid_constant__ TcJob job, const __grid_constant__ CUtensorMap
                         for (int i = 0; i < TPT; i++) {
                             const float d0 = __fmul_rn(sw0, xs0[i]), d1 = __fmul_rn(sw1, xs1[i]);
 #pragma unroll
-                            for (int l = 0; l < 4; l++) {
-                                acc[i][0][l] = __fadd_rn(acc[i][0][l], __fmul_rn(__int2float_rn(S0[i * 4 + l]), d0));
-                                acc[i][1][l] = __fadd_rn(acc[i][1][l], __fmul_rn(__int2float_rn(S1[i * 4 + l]), d1));
+                            for (int l = 0; l < 4; l += 2) {
+                                acc2[i][0][l >> 1] = add2(acc2[i][0][l >> 1], pack2(__fmul_rn(__int2float_rn(S0[i * 4 + l]), d0),
+                                                                                   __fmul_rn(__int2float_rn(S0[i * 4 + l + 1]), d0)));
+                                acc2[i][1][l >> 1] = add2(acc2[i][1][l >> 1], pack2(__fmul_rn(__int2float_rn(S1[i * 4 + l]), d1),
+                                                                                   __fmul_rn(__int2float_rn(S1[i * 4 + l + 1]), d1)));
                             }
                         }
                     }
@@ -471,8 +481,15 @@ k_gemm_tc(const __grid_constant__ TcJob job, const __grid_constant__ CUtensorMap
 #pragma unroll
                     for (int i = 0; i < TPT; i++) {
                         const int tok = tl.n0 + cg * TPT + i;
-                        const float e = __fadd_rn(__fadd_rn(acc[i][0][0], acc[i][0][1]), __fadd_rn(acc[i][0][2], acc[i][0][3]));
-                        const float o = __fadd_rn(__fadd_rn(acc[i][1][0], acc[i][1][1]), __fadd_rn(acc[i][1][2], acc[i][1][3]));
+                        float acc[1][2][4];
+                        unpack2(acc2[i][0][0], acc[0][0][0], acc[0][0][1]);
+                        unpack2(acc2[i][0][1], acc[0][0][2], acc[0][0][3]);
+                        unpack2(acc2[i][1][0], acc[0][1][0], acc[0][1][1]);
+                        unpack2(acc2[i][1][1], acc[0][1][2], acc[0][1][3]);
+#define WICK_ACC(p, l) acc[0][p][l]
+                        const float e = __fadd_rn(__fadd_rn(WICK_ACC(0, 0), WICK_ACC(0, 1)), __fadd_rn(WICK_ACC(0, 2), WICK_ACC(0, 3)));
+                        const float o = __fadd_rn(__fadd_rn(WICK_ACC(1, 0), WICK_ACC(1, 1)), __fadd_rn(WICK_ACC(1, 2), WICK_ACC(1, 3)));
+#undef WICK_ACC
                         if (tok < n) out[(size_t)tok * m + row] = __fadd_rn(e, o);
                     }
                 }
