@@ -151,13 +151,15 @@ void launch_attention_naive(cudaStream_t st, const float* q, const float* k_cach
 // a K / V tile is fetched once for all of them.  A producer warp streams the tiles with bulk asynchronous copies
 // (cp.async.bulk, one per cache row, completion counted on an mbarrier) into a two-deep ring of shared memory;
 // rows are padded to HD + 4 floats so that the accesses below are free of bank conflicts.  A consumer warp owns
-// 8 queries of one head; lane = (query jq = lane / 4, part s = lane % 4):
-//   * q.k: the lane holds its query row in registers and computes the dots of keys t = 4 i + s (i = 0..7) of the
-//     tile with the reference's eight fused chains; the four parts of a query read four different rows (one
-//     128-byte wavefront per 16-byte load, each value feeding 8 queries);
+// 8 * BQ consecutive queries of one head (their rows sit in shared memory too); lane = (slot jq = lane / 4, part
+// s = lane % 4) computes the BQ queries jq, jq + 8, ...:
+//   * q.k: the dots of keys t = 4 i + s (i = 0..7) of the tile with the reference's eight fused chains, KB keys at a
+//     time; a 16-byte piece of a key row serves the lane's BQ queries and a piece of a query row its KB keys (the
+//     kernel is bound by shared-memory bandwidth, so every loaded value has to feed several multiply-adds);
 //   * softmax: tile max over the lane's 8 scores and its three partner lanes; each lane exponentiates its own 8;
 //   * the probabilities travel by warp shuffle, in key order: every lane adds all 32 to the f64 tile sum in the
-//     reference's order and applies them to its quarter of the output dims (acc chains in ascending key order).
+//     reference's order and applies them to its quarter of the output dims (acc chains in ascending key order); a
+//     piece of a V row again serves the BQ queries.
 // Keys at or beyond a query's causal limit are skipped by predicate (they may hold anything).
 // Every wait is bounded: on expiry the CTA sets *err, stops waiting and returns.
 constexpr int FLASH_TILE = 32;  // FLASH_TILE_KV, cpu.rs:1513
@@ -190,12 +192,15 @@ __device__ __forceinline__ bool fa_wait(uint64_t* bar, uint32_t parity, volatile
 }
 
 #ifndef WICK_FA_MIN_CTAS
-#define WICK_FA_MIN_CTAS 2
+#define WICK_FA_MIN_CTAS 1
 #endif
 #ifndef WICK_FA_KB
 #define WICK_FA_KB 2
 #endif
-template <int HD>
+#ifndef WICK_FA_BQ
+#define WICK_FA_BQ 2
+#endif
+template <int HD, int BQ>
 __global__ void __launch_bounds__(288, HD <= 64 ? WICK_FA_MIN_CTAS : 1) k_attention_flash(const float* __restrict__ q, const float* __restrict__ k_cache,
                                                           const float* __restrict__ v_cache, float* __restrict__ out, int n, int start_pos,
                                                           int n_heads, int n_kv_heads, int qb, uint32_t* __restrict__ err) {
@@ -203,15 +208,15 @@ __global__ void __launch_bounds__(288, HD <= 64 ? WICK_FA_MIN_CTAS : 1) k_attent
     constexpr int DPL = HD / 4;          // output dims per lane
     constexpr int KB = WICK_FA_KB;       // keys whose dots share one pass over the query row
     extern __shared__ __align__(128) uint8_t fa_smem[];
-    float* Ks = reinterpret_cast<float*>(fa_smem);                   // [2][32][ROW]
-    float* Vs = Ks + 2 * FLASH_TILE * ROW;                            // [2][32][ROW]
-    float* Qs = Vs + 2 * FLASH_TILE * ROW;                            // [consumer warps][8][ROW]
-    uint64_t* full = reinterpret_cast<uint64_t*>(Qs + 8 * 8 * ROW);   // [2]
+    uint64_t* full = reinterpret_cast<uint64_t*>(fa_smem);           // [2]
     uint64_t* empty = full + 2;                                       // [2]
     volatile int* abort = reinterpret_cast<volatile int*>(empty + 2);
+    float* Ks = reinterpret_cast<float*>(fa_smem + 64);              // [2][32][ROW]
+    float* Vs = Ks + 2 * FLASH_TILE * ROW;                            // [2][32][ROW]
+    float* Qs = Vs + 2 * FLASH_TILE * ROW;                            // [consumer warps][8 * BQ][ROW]
 
     const int group = n_heads / n_kv_heads;
-    const int n_cw = group * (qb / 8);  // consumer warps
+    const int n_cw = group * (qb / (8 * BQ));  // consumer warps
     const int kvh = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int hs = n_heads * HD, kv_dim = n_kv_heads * HD;
@@ -264,124 +269,178 @@ __global__ void __launch_bounds__(288, HD <= 64 ? WICK_FA_MIN_CTAS : 1) k_attent
     }
     if (warp > n_cw) return;
 
-    const int g = warp % group, oct = warp / group;
+    // A consumer warp owns QPW = 8 * BQ consecutive queries of one head; lane = (slot jq = lane / 4, part s = lane % 4)
+    // computes the BQ queries jq, jq + 8, ... of the warp's run: every K and V value it loads serves BQ queries.
+    constexpr int QPW = 8 * BQ;
+    const int g = warp % group, run = warp / group;
     const int jq = lane >> 2, s = lane & 3;
-    const int j = j_first + oct * 8 + jq;
     const int h = kvh * group + g;
-    const bool active = j < n;
-    const int my_max = active ? start_pos + j + 1 : 0;
+    const int j0 = j_first + run * QPW;
     const float scale = __fdiv_rn(1.0f, sqrtf((float)HD));
+    int my_max[BQ];
+#pragma unroll
+    for (int u = 0; u < BQ; u++) {
+        const int j = j0 + u * 8 + jq;
+        my_max[u] = j < n ? start_pos + j + 1 : 0;
+    }
 
-    // the warp's 8 query rows in shared memory (padded like the K rows: the 8 queries of a 16-byte load hit 8
+    // the warp's query rows in shared memory (padded like the K rows: the 8 slots of a 16-byte load hit 8
     // different bank groups); lane L copies 16-byte pieces L, L + 32, ...
-    float* qw = Qs + warp * 8 * ROW;
-    for (int i = lane; i < 8 * (HD / 4); i += 32) {
+    float* qw = Qs + warp * QPW * ROW;
+    for (int i = lane; i < QPW * (HD / 4); i += 32) {
         const int r = i / (HD / 4), c = i % (HD / 4);
-        const int jr = j_first + oct * 8 + r;
+        const int jr = j0 + r;
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
         if (jr < n) v = __ldg(reinterpret_cast<const float4*>(q + (size_t)jr * hs + h * HD) + c);
         reinterpret_cast<float4*>(qw + r * ROW)[c] = v;
     }
     __syncwarp();
-    const float* qrow = qw + jq * ROW;
-    float acc[DPL];
+    float acc[BQ][DPL];
+    float running_max[BQ];
+    double running_sum[BQ];
 #pragma unroll
-    for (int d = 0; d < DPL; d++) acc[d] = 0.0f;
-    float running_max = __int_as_float(0xFF800000);
-    double running_sum = 0.0;
+    for (int u = 0; u < BQ; u++) {
+#pragma unroll
+        for (int d = 0; d < DPL; d++) acc[u][d] = 0.0f;
+        running_max[u] = __int_as_float(0xFF800000);
+        running_sum[u] = 0.0;
+    }
     const int src_base = lane & ~3;
 
     for (int it = 0; it < n_tiles; it++) {
         const int buf = it & 1, kv0 = it * FLASH_TILE;
         if (!fa_wait(&full[buf], (it >> 1) & 1, abort, err, 0x200u)) return;
-        const int len = min(FLASH_TILE, my_max - kv0);  // keys of this tile the lane's query attends (<= 0: none)
-        if (__reduce_max_sync(0xffffffffu, len) > 0) {
+        int len[BQ], len_max = 0;  // keys of this tile each of the lane's queries attends (<= 0: none)
+#pragma unroll
+        for (int u = 0; u < BQ; u++) {
+            len[u] = min(FLASH_TILE, my_max[u] - kv0);
+            len_max = max(len_max, len[u]);
+        }
+        if (__reduce_max_sync(0xffffffffu, len_max) > 0) {
             const float* Kt = Ks + buf * FLASH_TILE * ROW;
             const float* Vt = Vs + buf * FLASH_TILE * ROW;
-            float e[8];
-            float tmax = __int_as_float(0xFF800000);
-            // the lane's 8 keys in blocks of KB: a 16-byte piece of the query row is loaded once per block
+            float e[BQ][8];
+            float tmax[BQ];
+#pragma unroll
+            for (int u = 0; u < BQ; u++) tmax[u] = __int_as_float(0xFF800000);
+            // the lane's 8 keys in blocks of KB; a 16-byte piece of a key row is loaded once for the BQ queries and a
+            // piece of a query row once for the KB keys
 #pragma unroll
             for (int i0 = 0; i0 < 8; i0 += KB) {
-                if (4 * i0 + s < len) {  // (keys of a block ascend: if the first is out of range, all are)
-                    float s0[KB][4], s1[KB][4];
+                if (4 * i0 + s < len_max) {  // (keys of a block ascend: if the first is out of range for all, so is the rest)
+                    float s0[BQ][KB][4], s1[BQ][KB][4];
 #pragma unroll
-                    for (int u = 0; u < KB; u++)
+                    for (int u = 0; u < BQ; u++)
 #pragma unroll
-                        for (int l = 0; l < 4; l++) s0[u][l] = s1[u][l] = 0.0f;
+                        for (int k = 0; k < KB; k++)
+#pragma unroll
+                            for (int l = 0; l < 4; l++) s0[u][k][l] = s1[u][k][l] = 0.0f;
 #pragma unroll
                     for (int d = 0; d < HD; d += 8) {
-                        const float4 qa = *reinterpret_cast<const float4*>(qrow + d);
-                        const float4 qb4 = *reinterpret_cast<const float4*>(qrow + d + 4);
+                        float4 ka[KB], kb[KB];
 #pragma unroll
-                        for (int u = 0; u < KB; u++) {
-                            const float* kr = Kt + (4 * (i0 + u) + s) * ROW + d;
-                            const float4 ka = *reinterpret_cast<const float4*>(kr);
-                            const float4 kb = *reinterpret_cast<const float4*>(kr + 4);
-                            s0[u][0] = __fmaf_rn(qa.x, ka.x, s0[u][0]);
-                            s0[u][1] = __fmaf_rn(qa.y, ka.y, s0[u][1]);
-                            s0[u][2] = __fmaf_rn(qa.z, ka.z, s0[u][2]);
-                            s0[u][3] = __fmaf_rn(qa.w, ka.w, s0[u][3]);
-                            s1[u][0] = __fmaf_rn(qb4.x, kb.x, s1[u][0]);
-                            s1[u][1] = __fmaf_rn(qb4.y, kb.y, s1[u][1]);
-                            s1[u][2] = __fmaf_rn(qb4.z, kb.z, s1[u][2]);
-                            s1[u][3] = __fmaf_rn(qb4.w, kb.w, s1[u][3]);
+                        for (int k = 0; k < KB; k++) {
+                            const float* kr = Kt + (4 * (i0 + k) + s) * ROW + d;
+                            ka[k] = *reinterpret_cast<const float4*>(kr);
+                            kb[k] = *reinterpret_cast<const float4*>(kr + 4);
+                        }
+#pragma unroll
+                        for (int u = 0; u < BQ; u++) {
+                            const float* qr = qw + (u * 8 + jq) * ROW + d;
+                            const float4 qa = *reinterpret_cast<const float4*>(qr);
+                            const float4 qb4 = *reinterpret_cast<const float4*>(qr + 4);
+#pragma unroll
+                            for (int k = 0; k < KB; k++) {
+                                s0[u][k][0] = __fmaf_rn(qa.x, ka[k].x, s0[u][k][0]);
+                                s0[u][k][1] = __fmaf_rn(qa.y, ka[k].y, s0[u][k][1]);
+                                s0[u][k][2] = __fmaf_rn(qa.z, ka[k].z, s0[u][k][2]);
+                                s0[u][k][3] = __fmaf_rn(qa.w, ka[k].w, s0[u][k][3]);
+                                s1[u][k][0] = __fmaf_rn(qb4.x, kb[k].x, s1[u][k][0]);
+                                s1[u][k][1] = __fmaf_rn(qb4.y, kb[k].y, s1[u][k][1]);
+                                s1[u][k][2] = __fmaf_rn(qb4.z, kb[k].z, s1[u][k][2]);
+                                s1[u][k][3] = __fmaf_rn(qb4.w, kb[k].w, s1[u][k][3]);
+                            }
                         }
                     }
 #pragma unroll
-                    for (int u = 0; u < KB; u++) {
-                        const float v0 = __fadd_rn(s0[u][0], s1[u][0]), v1 = __fadd_rn(s0[u][1], s1[u][1]);
-                        const float v2 = __fadd_rn(s0[u][2], s1[u][2]), v3 = __fadd_rn(s0[u][3], s1[u][3]);
-                        const float sc = __fmul_rn(__fadd_rn(__fadd_rn(v0, v1), __fadd_rn(v2, v3)), scale);
-                        const bool in = 4 * (i0 + u) + s < len;
-                        e[i0 + u] = in ? sc : __int_as_float(0xFF800000);
-                        if (in && sc > tmax) tmax = sc;
-                    }
+                    for (int u = 0; u < BQ; u++)
+#pragma unroll
+                        for (int k = 0; k < KB; k++) {
+                            const float v0 = __fadd_rn(s0[u][k][0], s1[u][k][0]), v1 = __fadd_rn(s0[u][k][1], s1[u][k][1]);
+                            const float v2 = __fadd_rn(s0[u][k][2], s1[u][k][2]), v3 = __fadd_rn(s0[u][k][3], s1[u][k][3]);
+                            const float sc = __fmul_rn(__fadd_rn(__fadd_rn(v0, v1), __fadd_rn(v2, v3)), scale);
+                            const bool in = 4 * (i0 + k) + s < len[u];
+                            e[u][i0 + k] = in ? sc : __int_as_float(0xFF800000);
+                            if (in && sc > tmax[u]) tmax[u] = sc;
+                        }
                 } else {
 #pragma unroll
-                    for (int u = 0; u < KB; u++) e[i0 + u] = __int_as_float(0xFF800000);
+                    for (int u = 0; u < BQ; u++)
+#pragma unroll
+                        for (int k = 0; k < KB; k++) e[u][i0 + k] = __int_as_float(0xFF800000);
                 }
             }
-            tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
-            tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
-            const float new_max = fmaxf(running_max, tmax);
-            const float rescale = running_max > __int_as_float(0xFF800000) ? ggml_expf(__fsub_rn(running_max, new_max)) : 0.0f;
+            float new_max[BQ];
 #pragma unroll
-            for (int i = 0; i < 8; i++) e[i] = (4 * i + s < len) ? ggml_expf(__fsub_rn(e[i], new_max)) : 0.0f;
+            for (int u = 0; u < BQ; u++) {
+                tmax[u] = fmaxf(tmax[u], __shfl_xor_sync(0xffffffffu, tmax[u], 1));
+                tmax[u] = fmaxf(tmax[u], __shfl_xor_sync(0xffffffffu, tmax[u], 2));
+                new_max[u] = fmaxf(running_max[u], tmax[u]);
+                const float rescale = running_max[u] > __int_as_float(0xFF800000) ? ggml_expf(__fsub_rn(running_max[u], new_max[u])) : 0.0f;
 #pragma unroll
-            for (int d = 0; d < DPL; d++) acc[d] = __fmul_rn(acc[d], rescale);
-            double tsum = 0.0;
+                for (int i = 0; i < 8; i++) e[u][i] = (4 * i + s < len[u]) ? ggml_expf(__fsub_rn(e[u][i], new_max[u])) : 0.0f;
+#pragma unroll
+                for (int d = 0; d < DPL; d++) acc[u][d] = __fmul_rn(acc[u][d], rescale);
+                if (len[u] > 0) running_sum[u] = running_sum[u] * (double)rescale;  // (+ the tile sum, below)
+            }
+            double tsum[BQ];
+#pragma unroll
+            for (int u = 0; u < BQ; u++) tsum[u] = 0.0;
 #pragma unroll
             for (int t = 0; t < FLASH_TILE; t++) {
-                const float p = __shfl_sync(0xffffffffu, e[t >> 2], src_base | (t & 3));
-                if (t < len) {
-                    tsum += (double)p;
+                float p[BQ];
+#pragma unroll
+                for (int u = 0; u < BQ; u++) p[u] = __shfl_sync(0xffffffffu, e[u][t >> 2], src_base | (t & 3));
+                if (t < len_max) {
+                    float4 vv[DPL / 4];
                     const float4* vp = reinterpret_cast<const float4*>(Vt + t * ROW + s * DPL);
 #pragma unroll
-                    for (int c = 0; c < DPL / 4; c++) {
-                        const float4 vv = vp[c];
-                        acc[4 * c + 0] = __fmaf_rn(p, vv.x, acc[4 * c + 0]);
-                        acc[4 * c + 1] = __fmaf_rn(p, vv.y, acc[4 * c + 1]);
-                        acc[4 * c + 2] = __fmaf_rn(p, vv.z, acc[4 * c + 2]);
-                        acc[4 * c + 3] = __fmaf_rn(p, vv.w, acc[4 * c + 3]);
-                    }
+                    for (int c = 0; c < DPL / 4; c++) vv[c] = vp[c];
+#pragma unroll
+                    for (int u = 0; u < BQ; u++)
+                        if (t < len[u]) {
+                            tsum[u] += (double)p[u];
+#pragma unroll
+                            for (int c = 0; c < DPL / 4; c++) {
+                                acc[u][4 * c + 0] = __fmaf_rn(p[u], vv[c].x, acc[u][4 * c + 0]);
+                                acc[u][4 * c + 1] = __fmaf_rn(p[u], vv[c].y, acc[u][4 * c + 1]);
+                                acc[u][4 * c + 2] = __fmaf_rn(p[u], vv[c].z, acc[u][4 * c + 2]);
+                                acc[u][4 * c + 3] = __fmaf_rn(p[u], vv[c].w, acc[u][4 * c + 3]);
+                            }
+                        }
                 }
             }
-            if (len > 0) {
-                running_sum = running_sum * (double)rescale + tsum;
-                running_max = new_max;
-            }
+#pragma unroll
+            for (int u = 0; u < BQ; u++)
+                if (len[u] > 0) {
+                    running_sum[u] = running_sum[u] + tsum[u];
+                    running_max[u] = new_max[u];
+                }
         }
         __syncwarp();
         if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(fa_smem_u32(&empty[buf])) : "memory");
     }
-    if (active) {
-        const float inv = (float)(1.0 / running_sum);
-        float4* op = reinterpret_cast<float4*>(out + (size_t)j * hs + h * HD + s * DPL);
 #pragma unroll
-        for (int c = 0; c < DPL / 4; c++)
-            op[c] = make_float4(__fmul_rn(acc[4 * c + 0], inv), __fmul_rn(acc[4 * c + 1], inv), __fmul_rn(acc[4 * c + 2], inv),
-                                __fmul_rn(acc[4 * c + 3], inv));
+    for (int u = 0; u < BQ; u++) {
+        const int j = j0 + u * 8 + jq;
+        if (j < n) {
+            const float inv = (float)(1.0 / running_sum[u]);
+            float4* op = reinterpret_cast<float4*>(out + (size_t)j * hs + h * HD + s * DPL);
+#pragma unroll
+            for (int c = 0; c < DPL / 4; c++)
+                op[c] = make_float4(__fmul_rn(acc[u][4 * c + 0], inv), __fmul_rn(acc[u][4 * c + 1], inv), __fmul_rn(acc[u][4 * c + 2], inv),
+                                    __fmul_rn(acc[u][4 * c + 3], inv));
+        }
     }
 }
 
@@ -393,22 +452,25 @@ bool attention_flash_supported(int n_heads, int n_kv_heads, int head_dim) {
 template <int HD>
 static cudaError_t launch_flash_hd(cudaStream_t st, const float* q, const float* k_cache, const float* v_cache, float* out, int n,
                                    int start_pos, int n_heads, int n_kv_heads, uint32_t* err) {
+    constexpr int BQ = WICK_FA_BQ;
     const int group = n_heads / n_kv_heads;
-    const int qb = group <= 4 ? 16 : 8;  // queries per CTA: 8 per consumer warp, at most 8 consumer warps
-    const size_t smem = (size_t)(4 * FLASH_TILE + 64) * (HD + 4) * sizeof(float) + 4 * sizeof(uint64_t) + 16;
-    static bool configured[64] = {};
+    const int runs = group >= 4 ? 1 : 4 / group;  // runs of 8 * BQ queries per head and CTA: 4 consumer warps (8 when group is 5..8)
+    const int qb = runs * 8 * BQ;                 // queries per CTA
+    const int n_cw = group * runs;
+    const size_t smem = 64 + (size_t)(4 * FLASH_TILE + n_cw * 8 * BQ) * (HD + 4) * sizeof(float);
+    static size_t configured[64] = {};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
-    if (smem > 48 * 1024 && (dev < 0 || dev >= 64 || !configured[dev])) {
-        e = cudaFuncSetAttribute(k_attention_flash<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (smem > 48 * 1024 && (dev < 0 || dev >= 64 || configured[dev] < smem)) {
+        e = cudaFuncSetAttribute(k_attention_flash<HD, BQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
-        if (dev >= 0 && dev < 64) configured[dev] = true;
+        if (dev >= 0 && dev < 64) configured[dev] = smem;
     }
     dim3 grid(n_kv_heads, (n + qb - 1) / qb);
-    const int threads = (group * (qb / 8) + 1) * 32;
+    const int threads = (n_cw + 1) * 32;
     g_kernel_launches++;
-    k_attention_flash<HD><<<grid, threads, smem, st>>>(q, k_cache, v_cache, out, n, start_pos, n_heads, n_kv_heads, qb, err);
+    k_attention_flash<HD, BQ><<<grid, threads, smem, st>>>(q, k_cache, v_cache, out, n, start_pos, n_heads, n_kv_heads, qb, err);
     return cudaSuccess;
 }
 
