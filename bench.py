@@ -444,6 +444,15 @@ def main():
                 if n == 4096 and mode != "exact-cuda-cores":
                     extra[key.replace("_tok_s", "_gemm_frac_of_int8_peak")] = tps * flop_tok / 1e12 / tensor_peak
         m.set_prefill_mode("exact")
+        # where a 4096-token exact prefill (ubatch 512) spends its device time, by kernel category
+        toks = gs.random_prompt(4096, spec.vocab, seed=7)
+        m.profile_enable(True)
+        m.forward_prefill_chunked(toks, 0, st, 512)
+        cats = m.profile_read()
+        m.profile_enable(False)
+        tot_ms = sum(cats.values()) or 1.0
+        extra["prefill_exact_p4096_device_ms_by_category"] = {k: round(v, 3) for k, v in cats.items()}
+        extra["prefill_exact_p4096_attention_share"] = cats.get("attention", 0.0) / tot_ms
         extra["int8_peak_tflops_used"] = tensor_peak
         extra["int8_peak_source"] = peak_src
         extra["gemm_gflop_per_token"] = flop_tok / 1e9

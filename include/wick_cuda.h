@@ -278,6 +278,18 @@ int32_t wick_cuda_shortconv(const float* proj_dev, const float* conv_w_dev, floa
 /* cpu_argmax (sampler.rs:8-19) of `count` logits -> *out_dev. */
 int32_t wick_cuda_argmax(const float* logits_dev, uint32_t count, uint32_t* out_dev, void* stream);
 
+/* Per-category device timers of forward_prefill: the counterpart of wick's WICK_PROFILE=timing / gpu switches
+ * (wick/src/model/metal_lfm2.rs:529-533, :596-600).  Enabled with the environment variable WICK_CUDA_PROFILE=events at model
+ * creation or with wick_cuda_profile_enable (which also clears the totals); while enabled, every prefill chunk records
+ * a CUDA event after each group of kernels of one kind and adds the differences to a running total per category
+ * (milliseconds since the last enable).  wick_cuda_profile_category_name(i), i < WICK_CUDA_PROFILE_CATEGORIES, names them:
+ * embedding, rmsnorm+quantise, gemm, short-conv, qk-norm+rope+kv-append, attention, activation+quantise,
+ * output-norm+logits.  (The persistent decode kernel has its own per-phase timeline: wick_cuda_decode_profile.) */
+#define WICK_CUDA_PROFILE_CATEGORIES 8
+int32_t wick_cuda_profile_enable(wick_cuda_model* m, int32_t on);
+int32_t wick_cuda_profile_read(wick_cuda_model* m, double* ms_out, uint32_t capacity);
+const char* wick_cuda_profile_category_name(uint32_t i);
+
 /* Model::forward followed by Sampler::sample (wick/src/sampler.rs:64-158) with the logits kept on the device: temperature
  * scaling, top-k, top-p, softmax_inplace and the weighted pick, in the reference's order; 4 bytes come back.  `r` is the
  * uniform draw in [0, 1) that wick takes from its `rand` StdRng (`self.rng.gen::<f32>()`, sampler.rs:151): the generator

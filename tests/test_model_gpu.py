@@ -372,3 +372,24 @@ def test_two_models_with_different_long_contexts(wick, orc, model_dir):
     want = om.forward_prefill(toks, 0)
     assert_logits_equal(m2.forward_prefill(toks, 0, st2), want, "second model")
     assert_logits_equal(m1.forward_prefill(toks, 0, st1), want, "first model, after the second one was created and used")
+
+
+def test_prefill_category_timers(wick, model_dir):
+    """The per-category device timers change nothing in the results and account for the time of a prefill call."""
+    from wick_b200 import gguf_synth as gs
+    path = _model_path(model_dir, "tiny-wide", "q4_0")
+    m = wick.CudaLfm2Model(path, 1024)
+    st = wick.InferenceState()
+    toks = gs.random_prompt(600, m.config().vocab_size, seed=5)
+    plain = m.forward_prefill(toks, 0, st)
+    m.profile_enable(True)
+    timed = m.forward_prefill(toks, 0, st)
+    total_ms = m.last_elapsed_ms()
+    prof = m.profile_read()
+    m.profile_enable(False)
+    assert np.array_equal(plain, timed)
+    assert set(prof) == {"embedding", "rmsnorm+quantise", "gemm", "short-conv", "qk-norm+rope+kv-append", "attention",
+                         "activation+quantise", "output-norm+logits"}
+    assert all(v >= 0 for v in prof.values()) and prof["gemm"] > 0 and prof["attention"] > 0
+    assert 0.5 * total_ms <= sum(prof.values()) <= 1.05 * total_ms, (prof, total_ms)
+    assert all(v == 0 for v in m.profile_read().values())        # disabling clears the totals

@@ -64,6 +64,8 @@ SIGNATURES = {
     "wick_cuda_restore": [_vp, _vp, _u64],
     "wick_cuda_last_elapsed_ms": [_vp, C.POINTER(_f)],
     "wick_cuda_kernel_launches": [_vp, C.POINTER(_u64)],
+    "wick_cuda_profile_enable": [_vp, _i32],
+    "wick_cuda_profile_read": [_vp, _vp, _u32],
     "wick_cuda_decode_profile": [_vp, _vp, _vp, _u32, C.POINTER(_u32)],
     "wick_cuda_debug_skew_barrier": [_vp, C.c_int64],
     "wick_cuda_decode_path": [_vp, C.POINTER(_i32)],
@@ -104,7 +106,7 @@ SIGNATURES = {
 }
 VOID_FUNCS = {"wick_cuda_model_destroy": [_vp], "wick_cuda_weight_destroy": [_vp], "wick_cuda_tp_comm_destroy": [_vp]}
 ALL_SYMBOLS = sorted(list(SIGNATURES) + list(VOID_FUNCS) + ["wick_cuda_last_error", "wick_cuda_argmax_noalloc_last_error",
-                                                            "wick_cuda_tp_last_error"])
+                                                            "wick_cuda_tp_last_error", "wick_cuda_profile_category_name"])
 
 _lib = None
 
@@ -132,6 +134,8 @@ def load() -> C.CDLL:
     lib.wick_cuda_argmax_noalloc_last_error.restype = C.c_char_p
     lib.wick_cuda_tp_last_error.argtypes = []
     lib.wick_cuda_tp_last_error.restype = C.c_char_p
+    lib.wick_cuda_profile_category_name.argtypes = [_u32]
+    lib.wick_cuda_profile_category_name.restype = C.c_char_p
     _lib = lib
     return lib
 

@@ -130,6 +130,12 @@ struct wick_cuda_model {
         std::vector<float*> k_cache, v_cache, conv_state;  // per layer (NULL where the layer has none)
     };
     std::vector<SeqSlot> seqs;
+    // per-category device timers of the prefill pipeline (WICK_CUDA_PROFILE=events or wick_cuda_profile_enable)
+    bool prof_on = false;
+    std::vector<cudaEvent_t> prof_events;   // pool, reused chunk after chunk
+    std::vector<int> prof_marks;            // category that ENDS at event i + 1 of the current chunk
+    size_t prof_used = 0;
+    double prof_ms[WICK_CUDA_PROFILE_CATEGORIES] = {};
     float* sample_val = nullptr;        // [vocab] work arrays of the on-device sampler, made on first use
     int* sample_idx = nullptr;
     uint32_t* sample_status = nullptr;
@@ -148,6 +154,7 @@ struct wick_cuda_model {
         if (g_greedy) cudaGraphExecDestroy(g_greedy);
         if (ev0) cudaEventDestroy(ev0);
         if (ev1) cudaEventDestroy(ev1);
+        for (cudaEvent_t e : prof_events) cudaEventDestroy(e);
         for (void* p : allocs) cudaFree(p);
         if (h_u32) cudaFreeHost(h_u32);
         if (h_logits) cudaFreeHost(h_logits);
@@ -603,6 +610,44 @@ int32_t capture_graph(wick_cuda_model* m, bool greedy, cudaGraphExec_t* out, uin
     return WICK_CUDA_OK;
 }
 
+// Per-category device timers (the counterpart of wick's WICK_PROFILE=timing|gpu switches, metal_lfm2.rs:529-533,
+// :596-600): an event after every group of kernels of one kind; the differences are added up per category once the
+// chunk has finished.  Off by default: an event per kernel group costs a little launch time.
+enum ProfCat { PC_EMBED = 0, PC_NORM_QUANT, PC_GEMM, PC_SHORTCONV, PC_QK_ROPE_KV, PC_ATTENTION, PC_ACT_QUANT, PC_LOGITS };
+static const char* const PROF_NAMES[WICK_CUDA_PROFILE_CATEGORIES] = {"embedding", "rmsnorm+quantise", "gemm", "short-conv", "qk-norm+rope+kv-append",
+                                                                      "attention", "activation+quantise", "output-norm+logits"};
+void prof_begin(wick_cuda_model* m) {
+    if (!m->prof_on) return;
+    m->prof_used = 0;
+    m->prof_marks.clear();
+    if (m->prof_events.empty()) {
+        cudaEvent_t e;
+        if (cudaEventCreate(&e) == cudaSuccess) m->prof_events.push_back(e);
+    }
+    if (!m->prof_events.empty()) {
+        cudaEventRecord(m->prof_events[0], m->stream);
+        m->prof_used = 1;
+    }
+}
+void prof_mark(wick_cuda_model* m, int cat) {  // the kernels enqueued since the previous mark belong to `cat`
+    if (!m->prof_on || m->prof_used == 0) return;
+    if (m->prof_used == m->prof_events.size()) {
+        cudaEvent_t e;
+        if (cudaEventCreate(&e) != cudaSuccess) return;
+        m->prof_events.push_back(e);
+    }
+    cudaEventRecord(m->prof_events[m->prof_used++], m->stream);
+    m->prof_marks.push_back(cat);
+}
+void prof_collect(wick_cuda_model* m) {  // after the stream has been synchronised
+    if (!m->prof_on) return;
+    for (size_t i = 0; i + 1 < m->prof_used; i++) {
+        float ms = 0.f;
+        if (cudaEventElapsedTime(&ms, m->prof_events[i], m->prof_events[i + 1]) == cudaSuccess) m->prof_ms[m->prof_marks[i]] += ms;
+    }
+    m->prof_used = 0;
+}
+
 // Integer GEMMs of n quantised rows (m->q8q / m->q8s) with up to three matrices that read the same input, as one
 // launch on the tensor cores when the chunk is wide enough to fill an MMA tile, else the exact CUDA-core kernel.
 struct GemmTarget {
@@ -648,31 +693,46 @@ void enqueue_prefill_chunk(wick_cuda_model* m, int n, int start_pos, bool flash,
     const int hs = m->cfg.hidden_size, is = m->cfg.intermediate_size, hd = m->head_dim;
     const float eps = m->cfg.rms_norm_eps;
     auto gemms = [&](std::initializer_list<GemmTarget> list) { run_gemms(m, n, list); };
+    prof_begin(m);
     if (embed) embed_rows(m, m->tokens_dev, nullptr, n);
+    prof_mark(m, PC_EMBED);
     const float* pending = nullptr;
     for (size_t li = 0; li < m->layers.size(); li++) {
         Layer& L = m->layers[li];
         launch_add_rmsnorm_quant(st, m->hidden, pending, L.attn_norm, eps, n, hs, m->q8s, m->q8q, nullptr);
+        prof_mark(m, PC_NORM_QUANT);
         if (!L.is_attn) {
             gemms({{&L.in_proj, &L.tc_in_proj, m->proj}});
+            prof_mark(m, PC_GEMM);
             launch_shortconv(st, m->proj, L.conv_w, L.conv_state, n, hs, m->cfg.conv_kernel_size, nullptr, m->q8s, m->q8q);
+            prof_mark(m, PC_SHORTCONV);
             gemms({{&L.out_proj, &L.tc_out_proj, m->block_out}});
+            prof_mark(m, PC_GEMM);
         } else {
             gemms({{&L.q, &L.tc_q, m->qbuf}, {&L.k, &L.tc_k, m->kbuf}, {&L.v, &L.tc_v, m->vbuf}});
+            prof_mark(m, PC_GEMM);
             launch_qknorm_rope_kv(st, m->qbuf, m->kbuf, m->vbuf, L.q_norm, L.k_norm, eps, m->rope_cos, m->rope_sin, L.k_cache,
                                   L.v_cache, n, start_pos, nullptr, m->cfg.n_heads, L.n_kv, hd);
+            prof_mark(m, PC_QK_ROPE_KV);
             if (flash)  // (shapes the tiled kernel does not take were refused when the model was created)
                 launch_attention_flash(st, m->qbuf, L.k_cache, L.v_cache, m->attn_out, n, start_pos, m->cfg.n_heads, L.n_kv, hd, m->tc_err);
             else
                 launch_attention_naive(st, m->qbuf, L.k_cache, L.v_cache, m->attn_out, n, start_pos, nullptr, m->cfg.n_heads,
                                        L.n_kv, hd, m->cfg.max_seq_len);
+            prof_mark(m, PC_ATTENTION);
             launch_quant_rows(st, m->attn_out, n, hs, m->q8s, m->q8q);
+            prof_mark(m, PC_ACT_QUANT);
             gemms({{&L.o, &L.tc_o, m->block_out}});
+            prof_mark(m, PC_GEMM);
         }
         launch_add_rmsnorm_quant(st, m->hidden, m->block_out, L.ffn_norm, eps, n, hs, m->q8s, m->q8q, nullptr);
+        prof_mark(m, PC_NORM_QUANT);
         gemms({{&L.gate, &L.tc_gate, m->gate}, {&L.up, &L.tc_up, m->up}});
+        prof_mark(m, PC_GEMM);
         launch_silu_mul_quant(st, m->gate, m->up, n, is, m->q8s, m->q8q, nullptr);
+        prof_mark(m, PC_ACT_QUANT);
         gemms({{&L.down, &L.tc_down, m->ffn_out}});
+        prof_mark(m, PC_GEMM);
         pending = m->ffn_out;
     }
     if (last) {
@@ -680,6 +740,7 @@ void enqueue_prefill_chunk(wick_cuda_model* m, int n, int start_pos, bool flash,
         size_t lastrow = (size_t)(n - 1) * hs;
         launch_add_rmsnorm_quant(st, m->hidden + lastrow, pending + lastrow, m->output_norm, eps, 1, hs, m->q8s, m->q8q, m->normed_last);
         if (want_logits) logits_matvec(m);
+        prof_mark(m, PC_LOGITS);
     }
 }
 
@@ -903,6 +964,10 @@ int32_t build_model(wick_cuda_model* m, const GgufImage& g, uint32_t context_siz
     }
     CU_TRY(cudaEventCreate(&m->ev0));
     CU_TRY(cudaEventCreate(&m->ev1));
+    {
+        const char* pe = getenv("WICK_CUDA_PROFILE");
+        m->prof_on = pe && strcmp(pe, "events") == 0;
+    }
     W_TRY(build_tc(m));
     W_TRY(build_mega(m));
     W_TRY(capture_graph(m, false, &m->g_logits, &m->nodes_logits));
@@ -1333,6 +1398,7 @@ static int32_t prefill_core(wick_cuda_model* m, const uint32_t* tokens_host, con
         m->launches += g_kernel_launches - before;
         CU_TRY(cudaGetLastError());
         CU_TRY(cudaStreamSynchronize(m->stream));  // h_u32 is reused by the next chunk
+        prof_collect(m);
     }
     uint32_t newpos[2] = {0, start_pos + n};
     memcpy(m->h_u32, newpos, 8);
@@ -1571,6 +1637,22 @@ int32_t wick_cuda_kernel_launches(const wick_cuda_model* m, uint64_t* count) {
     *count = m->launches;
     return WICK_CUDA_OK;
 }
+
+int32_t wick_cuda_profile_enable(wick_cuda_model* m, int32_t on) {
+    W_TRY(check_model(m));
+    m->prof_on = on != 0;
+    for (double& v : m->prof_ms) v = 0.0;
+    return WICK_CUDA_OK;
+}
+
+int32_t wick_cuda_profile_read(wick_cuda_model* m, double* ms_out, uint32_t capacity) {
+    W_TRY(check_model(m));
+    if (!ms_out || capacity < WICK_CUDA_PROFILE_CATEGORIES) return fail(WICK_CUDA_ERR_BAD_ARG, "ms_out is NULL or shorter than WICK_CUDA_PROFILE_CATEGORIES");
+    for (int i = 0; i < WICK_CUDA_PROFILE_CATEGORIES; i++) ms_out[i] = m->prof_ms[i];
+    return WICK_CUDA_OK;
+}
+
+const char* wick_cuda_profile_category_name(uint32_t i) { return i < WICK_CUDA_PROFILE_CATEGORIES ? PROF_NAMES[i] : ""; }
 
 int32_t wick_cuda_decode_profile(wick_cuda_model* m, uint64_t* ns_out, int32_t* kinds_out, uint32_t capacity, uint32_t* n_phases) {
     W_TRY(check_model(m));

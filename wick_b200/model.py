@@ -289,6 +289,17 @@ class CudaLfm2Model:
         check(self._lib.wick_cuda_prefill_uses_tensor_cores(self._h, C.byref(v)))
         return bool(v.value)
 
+    def profile_enable(self, on: bool = True) -> None:
+        """Per-category device timers of forward_prefill (WICK_PROFILE in wick's GPU backends); clears the totals."""
+        check(self._lib.wick_cuda_profile_enable(self._h, 1 if on else 0))
+
+    def profile_read(self) -> dict:
+        """Milliseconds per kernel category accumulated since profile_enable()."""
+        n = 8
+        ms = (C.c_double * n)()
+        check(self._lib.wick_cuda_profile_read(self._h, ms, n))
+        return {self._lib.wick_cuda_profile_category_name(i).decode(): float(ms[i]) for i in range(n)}
+
     def decode_profile(self):
         """Timeline of the last decode step of the persistent kernel: (kinds [n], ns [n, 4])."""
         n = C.c_uint32(0)
