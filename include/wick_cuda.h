@@ -278,6 +278,22 @@ int32_t wick_cuda_shortconv(const float* proj_dev, const float* conv_w_dev, floa
 /* cpu_argmax (sampler.rs:8-19) of `count` logits -> *out_dev. */
 int32_t wick_cuda_argmax(const float* logits_dev, uint32_t count, uint32_t* out_dev, void* stream);
 
+/* Split-K decode attention (opt-in).  The default single-query attention keeps the CPU path's one serial accumulation per
+ * output dim over all cached keys (attn_values, cpu.rs:1463-1509), which is bit-exact and, at thousands of keys, slow.
+ * WICK_CUDA_DECODE_ATTENTION_SPLITK splits the keys of every head into runs of 256 and merges the runs' (max, sum,
+ * weighted V) partials, the scheme of wick's Metal kernels (shaders/attention_splitk.metal:30 attention_split_compute,
+ * :162 attention_split_merge).  Results then agree with the CPU path within rounding (about 1e-6 relative on the attention
+ * output), not bit for bit, so greedy tokens can differ where two logits are close.  It applies to the multi-sequence
+ * step (wick_cuda_decode_batch*) and to single-sequence decode when that runs as captured graphs; the persistent decode
+ * kernel always uses the exact form.  Also selectable with WICK_CUDA_DECODE_ATTENTION=splitk in the environment at model
+ * creation.  wick_cuda_attention_decode_splitk is the operator form (q [n_heads*head_dim], caches [seq][n_kv_heads*head_dim]). */
+#define WICK_CUDA_DECODE_ATTENTION_EXACT 0
+#define WICK_CUDA_DECODE_ATTENTION_SPLITK 1
+int32_t wick_cuda_set_decode_attention(wick_cuda_model* m, int32_t mode);
+int32_t wick_cuda_attention_decode_splitk(const float* q_dev, const float* k_cache_dev, const float* v_cache_dev,
+                                          float* out_dev, uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim,
+                                          uint32_t seq, void* stream);
+
 /* Per-category device timers of forward_prefill: the counterpart of wick's WICK_PROFILE=timing / gpu switches
  * (wick/src/model/metal_lfm2.rs:529-533, :596-600).  Enabled with the environment variable WICK_CUDA_PROFILE=events at model
  * creation or with wick_cuda_profile_enable (which also clears the totals); while enabled, every prefill chunk records

@@ -64,6 +64,8 @@ SIGNATURES = {
     "wick_cuda_restore": [_vp, _vp, _u64],
     "wick_cuda_last_elapsed_ms": [_vp, C.POINTER(_f)],
     "wick_cuda_kernel_launches": [_vp, C.POINTER(_u64)],
+    "wick_cuda_set_decode_attention": [_vp, _i32],
+    "wick_cuda_attention_decode_splitk": [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _vp],
     "wick_cuda_profile_enable": [_vp, _i32],
     "wick_cuda_profile_read": [_vp, _vp, _u32],
     "wick_cuda_decode_profile": [_vp, _vp, _vp, _u32, C.POINTER(_u32)],

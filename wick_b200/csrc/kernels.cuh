@@ -103,6 +103,13 @@ void launch_qknorm_rope_kv_rows(cudaStream_t st, float* q, const float* k, const
                                 const uint32_t* positions, int n, int n_heads, int n_kv_heads, int head_dim);
 cudaError_t launch_attention_rows(cudaStream_t st, const float* q, float* const* k_caches, float* const* v_caches, const uint32_t* positions,
                                   float* out, int n, int n_heads, int n_kv_heads, int head_dim, int max_seq);
+// Opt-in split-K form of the single-query attention (keys of every (row, head) in runs of 256 + a merge pass; rounding
+// differs from the exact kernel).  Caches per row (k_caches / v_caches) or one pair for all rows (k_single / v_single);
+// positions[j] = cached rows before row j's token.  scratch: attention_splitk_scratch_floats() floats.
+size_t attention_splitk_scratch_floats(int n, int n_heads, int head_dim, int max_seq);
+void launch_attention_splitk(cudaStream_t st, const float* q, float* const* k_caches, float* const* v_caches, const float* k_single,
+                             const float* v_single, const uint32_t* positions, float* out, float* scratch, int n, int n_heads, int n_kv_heads,
+                             int head_dim, int max_seq);
 void launch_argmax_rows(cudaStream_t st, const float* logits, int n, int count, uint32_t* out);
 void launch_rows_advance(cudaStream_t st, uint32_t* tokens, const uint32_t* next, uint32_t* positions, uint32_t* out_table, int n, int step);
 

@@ -194,6 +194,113 @@ cudaError_t launch_attention_rows(cudaStream_t st, const float* q, float* const*
     return cudaSuccess;
 }
 
+// ── split-K single-query attention (opt-in) ────────────────────────────────
+// The exact kernel above keeps the reference's one serial chain per output dim over ALL keys, which at thousands of
+// cached keys is the whole cost of a decode step.  This pair splits the keys of every (row, head) into runs of
+// SPLIT_KEYS: `k_attention_split` computes for each run its score maximum m, the sum l of exp(score - m) and the
+// weighted V sum, `k_attention_merge` combines the runs as  out = sum_i acc_i e^(m_i - M) / sum_i l_i e^(m_i - M)
+// (the scheme of wick's Metal split-K kernels, shaders/attention_splitk.metal:30, :162).  Inside a run the arithmetic
+// is the reference's (NEON-order dots, ggml_expf, fused chains in ascending key order); ACROSS runs the summation
+// order differs from the CPU path, so results agree within rounding (about 1e-6 relative), not bit for bit: this
+// path is never the default.
+constexpr int SPLIT_KEYS = 256;
+constexpr int SPLIT_THREADS = 128;
+
+// grid (heads, splits, rows); partial layout [row][head][split][hd + 2] = acc[hd], m, l
+__global__ void __launch_bounds__(SPLIT_THREADS) k_attention_split(const float* __restrict__ q, float* const* __restrict__ k_caches,
+                                                                   float* const* __restrict__ v_caches, const float* __restrict__ k_single,
+                                                                   const float* __restrict__ v_single, const uint32_t* __restrict__ positions,
+                                                                   float* __restrict__ partial, int n_heads, int n_kv_heads, int hd, int max_splits) {
+    __shared__ float qs[256];
+    __shared__ float sc[SPLIT_KEYS];
+    __shared__ float redf[SPLIT_THREADS / 32];
+    __shared__ double red[SPLIT_THREADS / 32];
+    const int h = blockIdx.x, sp = blockIdx.y, j = blockIdx.z;
+    const int seq = (int)positions[j] + 1;
+    const int t0 = sp * SPLIT_KEYS;
+    if (t0 >= seq) return;
+    const int cnt = min(SPLIT_KEYS, seq - t0);
+    const int hs = n_heads * hd, kv_dim = n_kv_heads * hd;
+    const int off = (h / (n_heads / n_kv_heads)) * hd;
+    const float* k_cache = k_caches ? k_caches[j] : k_single;
+    const float* v_cache = v_caches ? v_caches[j] : v_single;
+    const float scale = __fdiv_rn(1.0f, sqrtf((float)hd));
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = SPLIT_THREADS / 32;
+    for (int i = tid; i < hd; i += SPLIT_THREADS) qs[i] = q[(size_t)j * hs + h * hd + i];
+    __syncthreads();
+    float mx = __int_as_float(0xFF800000);
+    for (int t = tid; t < cnt; t += SPLIT_THREADS) {
+        const float s = __fmul_rn(qk_dot_rows(qs, k_cache + (size_t)(t0 + t) * kv_dim + off, hd), scale);
+        sc[t] = s;
+        mx = fmaxf(mx, s);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if (lane == 0) redf[warp] = mx;
+    __syncthreads();
+    mx = redf[0];
+    for (int i = 1; i < nw; i++) mx = fmaxf(mx, redf[i]);
+    double sum = 0.0;
+    for (int t = tid; t < cnt; t += SPLIT_THREADS) {
+        const float e = ggml_expf(__fsub_rn(sc[t], mx));
+        sc[t] = e;
+        sum += (double)e;
+    }
+    sum = warp_sum_f64(sum);
+    if (lane == 0) red[warp] = sum;
+    __syncthreads();
+    float* out = partial + (((size_t)j * n_heads + h) * max_splits + sp) * (hd + 2);
+    for (int d = tid; d < hd; d += SPLIT_THREADS) {
+        const float* vp = v_cache + (size_t)t0 * kv_dim + off + d;
+        float acc = 0.0f;
+#pragma unroll 8
+        for (int t = 0; t < cnt; t++) acc = __fmaf_rn(sc[t], vp[(size_t)t * kv_dim], acc);
+        out[d] = acc;
+    }
+    if (tid == 0) {
+        double tot = 0.0;
+        for (int i = 0; i < nw; i++) tot += red[i];
+        out[hd] = mx;
+        out[hd + 1] = (float)tot;
+    }
+}
+
+// grid (heads, rows), one thread per output dim
+__global__ void k_attention_merge(const float* __restrict__ partial, const uint32_t* __restrict__ positions, float* __restrict__ out, int n_heads,
+                                  int hd, int max_splits) {
+    const int h = blockIdx.x, j = blockIdx.y;
+    const int seq = (int)positions[j] + 1;
+    const int ns = (seq + SPLIT_KEYS - 1) / SPLIT_KEYS;
+    const float* p = partial + ((size_t)j * n_heads + h) * max_splits * (hd + 2);
+    float M = __int_as_float(0xFF800000);
+    for (int i = 0; i < ns; i++) M = fmaxf(M, p[(size_t)i * (hd + 2) + hd]);
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+        float L = 0.0f, acc = 0.0f;
+        for (int i = 0; i < ns; i++) {
+            const float w = ggml_expf(__fsub_rn(p[(size_t)i * (hd + 2) + hd], M));
+            L = __fmaf_rn(p[(size_t)i * (hd + 2) + hd + 1], w, L);
+            acc = __fmaf_rn(p[(size_t)i * (hd + 2) + d], w, acc);
+        }
+        out[(size_t)j * n_heads * hd + h * hd + d] = __fdiv_rn(acc, L);
+    }
+}
+
+size_t attention_splitk_scratch_floats(int n, int n_heads, int head_dim, int max_seq) {
+    const int max_splits = (max_seq + SPLIT_KEYS - 1) / SPLIT_KEYS;
+    return (size_t)n * n_heads * max_splits * (head_dim + 2);
+}
+
+void launch_attention_splitk(cudaStream_t st, const float* q, float* const* k_caches, float* const* v_caches, const float* k_single,
+                             const float* v_single, const uint32_t* positions, float* out, float* scratch, int n, int n_heads, int n_kv_heads,
+                             int head_dim, int max_seq) {
+    if (!n) return;
+    const int max_splits = (max_seq + SPLIT_KEYS - 1) / SPLIT_KEYS;
+    g_kernel_launches += 2;
+    k_attention_split<<<dim3(n_heads, max_splits, n), SPLIT_THREADS, 0, st>>>(q, k_caches, v_caches, k_single, v_single, positions, scratch, n_heads,
+                                                                               n_kv_heads, head_dim, max_splits);
+    k_attention_merge<<<dim3(n_heads, n), 64, 0, st>>>(scratch, positions, out, n_heads, head_dim, max_splits);
+}
+
 // ── cpu_argmax (sampler.rs:8-19) of every row of logits [n][count]; one CTA per row ──
 __global__ void __launch_bounds__(1024) k_argmax_rows(const float* __restrict__ x, int count, uint32_t* __restrict__ out) {
     __shared__ unsigned long long sh[32];

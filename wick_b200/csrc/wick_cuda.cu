@@ -136,6 +136,10 @@ struct wick_cuda_model {
     std::vector<int> prof_marks;            // category that ENDS at event i + 1 of the current chunk
     size_t prof_used = 0;
     double prof_ms[WICK_CUDA_PROFILE_CATEGORIES] = {};
+    // opt-in split-K decode attention (graph decode path and the multi-sequence step; the persistent kernel stays exact)
+    bool attn_splitk = false;
+    float* splitk_scratch = nullptr;
+    size_t splitk_floats = 0;
     float* sample_val = nullptr;        // [vocab] work arrays of the on-device sampler, made on first use
     int* sample_idx = nullptr;
     uint32_t* sample_status = nullptr;
@@ -542,6 +546,15 @@ void logits_matvec(wick_cuda_model* m) {
     }
 }
 
+int32_t ensure_splitk_scratch(wick_cuda_model* m, int rows) {
+    const size_t need = attention_splitk_scratch_floats(rows, (int)m->cfg.n_heads, m->head_dim, (int)m->cfg.max_seq_len);
+    if (need > m->splitk_floats) {
+        W_TRY(dev_alloc(m, &m->splitk_scratch, need));
+        m->splitk_floats = need;
+    }
+    return WICK_CUDA_OK;
+}
+
 void enqueue_decode(wick_cuda_model* m, bool greedy) {
     cudaStream_t st = m->stream;
     const int hs = m->cfg.hidden_size, is = m->cfg.intermediate_size, hd = m->head_dim;
@@ -567,8 +580,12 @@ void enqueue_decode(wick_cuda_model* m, bool greedy) {
             launch_gemv(st, j, m->q8s, m->q8q);
             launch_qknorm_rope_kv(st, m->qbuf, m->kbuf, m->vbuf, L.q_norm, L.k_norm, m->cfg.rms_norm_eps, m->rope_cos,
                                   m->rope_sin, L.k_cache, L.v_cache, 1, -1, m->ctl, m->cfg.n_heads, L.n_kv, hd);
-            launch_attention_naive(st, m->qbuf, L.k_cache, L.v_cache, m->attn_out, 1, -1, m->ctl, m->cfg.n_heads, L.n_kv, hd,
-                                   m->cfg.max_seq_len);
+            if (m->attn_splitk)
+                launch_attention_splitk(st, m->qbuf, nullptr, nullptr, L.k_cache, L.v_cache, &m->ctl->pos, m->attn_out, m->splitk_scratch, 1,
+                                        m->cfg.n_heads, L.n_kv, hd, m->cfg.max_seq_len);
+            else
+                launch_attention_naive(st, m->qbuf, L.k_cache, L.v_cache, m->attn_out, 1, -1, m->ctl, m->cfg.n_heads, L.n_kv, hd,
+                                       m->cfg.max_seq_len);
             launch_quant_rows(st, m->attn_out, 1, hs, m->q8s, m->q8q);
             GemvJob o{};
             o.count = 1; o.w[0] = L.o; o.y[0] = m->block_out;
@@ -970,6 +987,13 @@ int32_t build_model(wick_cuda_model* m, const GgufImage& g, uint32_t context_siz
     }
     W_TRY(build_tc(m));
     W_TRY(build_mega(m));
+    {
+        const char* da = getenv("WICK_CUDA_DECODE_ATTENTION");
+        if (da && strcmp(da, "splitk") == 0) {
+            W_TRY(ensure_splitk_scratch(m, 1));
+            m->attn_splitk = true;
+        }
+    }
     W_TRY(capture_graph(m, false, &m->g_logits, &m->nodes_logits));
     W_TRY(capture_graph(m, true, &m->g_greedy, &m->nodes_greedy));
     CU_TRY(cudaStreamSynchronize(m->stream));
@@ -1072,7 +1096,11 @@ int32_t enqueue_decode_rows(wick_cuda_model* m, int n) {
             gemms({{&L.q, &L.tc_q, m->qbuf}, {&L.k, &L.tc_k, m->kbuf}, {&L.v, &L.tc_v, m->vbuf}});
             launch_qknorm_rope_kv_rows(st, m->qbuf, m->kbuf, m->vbuf, L.q_norm, L.k_norm, eps, m->rope_cos, m->rope_sin, p0, p1, m->rows_pos, n,
                                        m->cfg.n_heads, L.n_kv, hd);
-            CU_TRY(launch_attention_rows(st, m->qbuf, p0, p1, m->rows_pos, m->attn_out, n, m->cfg.n_heads, L.n_kv, hd, m->cfg.max_seq_len));
+            if (m->attn_splitk)
+                launch_attention_splitk(st, m->qbuf, p0, p1, nullptr, nullptr, m->rows_pos, m->attn_out, m->splitk_scratch, n, m->cfg.n_heads, L.n_kv,
+                                        hd, m->cfg.max_seq_len);
+            else
+                CU_TRY(launch_attention_rows(st, m->qbuf, p0, p1, m->rows_pos, m->attn_out, n, m->cfg.n_heads, L.n_kv, hd, m->cfg.max_seq_len));
             launch_quant_rows(st, m->attn_out, n, hs, m->q8s, m->q8q);
             gemms({{&L.o, &L.tc_o, m->block_out}});
         }
@@ -1113,6 +1141,7 @@ int32_t decode_rows(wick_cuda_model* m, const uint32_t* tokens_host, const uint3
     }
     CU_TRY(cudaSetDevice(m->device));
     if (bs >= 16) W_TRY(ensure_tc(m));
+    if (m->attn_splitk) W_TRY(ensure_splitk_scratch(m, (int)bs));
     W_TRY(ensure_batch_buffers(m, bs, n_steps));
     const size_t nl = m->layers.size();
     const int cap = m->batch_cap;
@@ -1638,6 +1667,26 @@ int32_t wick_cuda_kernel_launches(const wick_cuda_model* m, uint64_t* count) {
     return WICK_CUDA_OK;
 }
 
+int32_t wick_cuda_set_decode_attention(wick_cuda_model* m, int32_t mode) {
+    W_TRY(check_model(m));
+    if (mode != WICK_CUDA_DECODE_ATTENTION_EXACT && mode != WICK_CUDA_DECODE_ATTENTION_SPLITK)
+        return fail(WICK_CUDA_ERR_BAD_ARG, "unknown decode attention mode " + std::to_string(mode));
+    const bool want = mode == WICK_CUDA_DECODE_ATTENTION_SPLITK;
+    if (want == m->attn_splitk) return WICK_CUDA_OK;
+    CU_TRY(cudaSetDevice(m->device));
+    CU_TRY(cudaStreamSynchronize(m->stream));
+    if (want) W_TRY(ensure_splitk_scratch(m, std::max(1, m->batch_cap)));
+    m->attn_splitk = want;
+    // the captured decode graphs contain the attention kernels: capture them again
+    if (m->g_logits) cudaGraphExecDestroy(m->g_logits);
+    if (m->g_greedy) cudaGraphExecDestroy(m->g_greedy);
+    m->g_logits = m->g_greedy = nullptr;
+    W_TRY(capture_graph(m, false, &m->g_logits, &m->nodes_logits));
+    W_TRY(capture_graph(m, true, &m->g_greedy, &m->nodes_greedy));
+    CU_TRY(cudaStreamSynchronize(m->stream));
+    return WICK_CUDA_OK;
+}
+
 int32_t wick_cuda_profile_enable(wick_cuda_model* m, int32_t on) {
     W_TRY(check_model(m));
     m->prof_on = on != 0;
@@ -1991,6 +2040,24 @@ int32_t wick_cuda_attention_decode(const float* q_dev, const float* k_cache_dev,
                                    uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim, uint32_t seq, void* stream) {
     return wick_cuda_attention_prefill(q_dev, k_cache_dev, v_cache_dev, out_dev, 1, seq ? seq - 1 : 0, n_heads, n_kv_heads,
                                        head_dim, 0, stream);
+}
+
+int32_t wick_cuda_attention_decode_splitk(const float* q_dev, const float* k_cache_dev, const float* v_cache_dev, float* out_dev,
+                                          uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim, uint32_t seq, void* stream) {
+    if (!q_dev || !k_cache_dev || !v_cache_dev || !out_dev) return fail(WICK_CUDA_ERR_BAD_ARG, "NULL argument");
+    if (!n_kv_heads || n_heads % n_kv_heads || head_dim % 8 || head_dim > 256 || seq == 0) return fail(WICK_CUDA_ERR_BAD_ARG, "bad attention shape");
+    cudaStream_t st = (cudaStream_t)stream;
+    const size_t floats = attention_splitk_scratch_floats(1, (int)n_heads, (int)head_dim, (int)seq);
+    float* scratch = nullptr;
+    CU_TRY(cudaMallocAsync((void**)&scratch, floats * 4 + 16, st));
+    uint32_t* pos = (uint32_t*)(scratch + floats);
+    const uint32_t p = seq - 1;
+    CU_TRY(cudaMemcpyAsync(pos, &p, 4, cudaMemcpyHostToDevice, st));
+    launch_attention_splitk(st, q_dev, nullptr, nullptr, k_cache_dev, v_cache_dev, pos, out_dev, scratch, 1, (int)n_heads, (int)n_kv_heads,
+                            (int)head_dim, (int)seq);
+    CU_TRY(cudaStreamSynchronize(st));  // `p` is on this function's stack
+    CU_TRY(cudaFreeAsync(scratch, st));
+    OP_END();
 }
 
 int32_t wick_cuda_attention_prefill(const float* q_dev, const float* k_cache_dev, const float* v_cache_dev, float* out_dev,

@@ -289,6 +289,10 @@ class CudaLfm2Model:
         check(self._lib.wick_cuda_prefill_uses_tensor_cores(self._h, C.byref(v)))
         return bool(v.value)
 
+    def set_decode_attention(self, mode: str) -> None:
+        """'exact' (default) or 'splitk' (opt-in, not bit-exact): see wick_cuda_set_decode_attention."""
+        check(self._lib.wick_cuda_set_decode_attention(self._h, {"exact": 0, "splitk": 1}[mode]))
+
     def profile_enable(self, on: bool = True) -> None:
         """Per-category device timers of forward_prefill (WICK_PROFILE in wick's GPU backends); clears the totals."""
         check(self._lib.wick_cuda_profile_enable(self._h, 1 if on else 0))

@@ -144,6 +144,14 @@ def attention_decode(q, k_cache, v_cache, n_heads, n_kv_heads, head_dim, seq) ->
     return out
 
 
+def attention_decode_splitk(q, k_cache, v_cache, n_heads, n_kv_heads, head_dim, seq) -> torch.Tensor:
+    """Opt-in split-K single-query attention (runs of 256 keys + merge); agrees with attention_decode within rounding."""
+    out = torch.empty(n_heads * head_dim, dtype=torch.float32, device=q.device)
+    check(_lib.load().wick_cuda_attention_decode_splitk(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), n_heads, n_kv_heads,
+                                                        head_dim, seq, _stream()))
+    return out
+
+
 def attention_prefill(q, k_cache, v_cache, n, start_pos, n_heads, n_kv_heads, head_dim, flash: bool) -> torch.Tensor:
     out = torch.empty((n, n_heads * head_dim), dtype=torch.float32, device=q.device)
     check(_lib.load().wick_cuda_attention_prefill(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), n, start_pos, n_heads,
