@@ -63,6 +63,8 @@ void launch_attention_naive(cudaStream_t st, const float* q, const float* k_cach
 // Opt-in to more than 48 KB of dynamic shared memory for the kernel above; call before any
 // stream capture that contains it.
 void configure_naive_attention_smem(size_t bytes);
+// Dynamic shared memory the kernel needs for this head size and longest sequence.
+size_t naive_attention_smem_bytes(int head_dim, int max_seq);
 // Exact tiled online-softmax attention (cpu.rs:1696-1850) for head_dim 32, 64 or 128 and up to 8 query heads per
 // KV head (attention_flash_supported); other shapes return cudaErrorInvalidValue without launching.  `err` is a
 // device word that receives a non-zero code if a bounded wait inside the kernel runs out.

@@ -1,4 +1,5 @@
 // Attention kernels that reproduce the CPU path's operation order exactly.
+#include "attn_common.cuh"
 #include "kernels.cuh"
 
 namespace wick {
@@ -59,8 +60,8 @@ __global__ void __launch_bounds__(NAIVE_THREADS) k_attention_naive(const float* 
                                                                     const float* __restrict__ v_cache,
                                                                     float* __restrict__ out, int start_pos,
                                                                     const DecodeCtl* __restrict__ ctl, int n_heads,
-                                                                    int n_kv_heads, int hd) {
-    extern __shared__ float sm[];
+                                                                    int n_kv_heads, int hd, int max_seq) {
+    extern __shared__ __align__(16) float sm[];
     __shared__ double red[32];
     __shared__ float redf[32];
     float* qs = sm;           // hd floats
@@ -103,7 +104,12 @@ __global__ void __launch_bounds__(NAIVE_THREADS) k_attention_naive(const float* 
     for (int t = tid; t < seq; t += NAIVE_THREADS) sc[t] = __fmul_rn(sc[t], inv);
     __syncthreads();
 
-    for (int d = tid; d < hd; d += NAIVE_THREADS) {
+    if (hd <= NAIVE_THREADS && hd % 4 == 0) {
+        float* vt = sc + ((max_seq + 3) & ~3);  // staging area behind the scores (16-byte aligned: hd is a multiple of 4)
+        attn_values_staged(sc, v_cache + off, kv_dim, hd, seq, vt, out + (size_t)j * hs + h * hd);
+        return;
+    }
+    for (int d = tid; d < hd; d += NAIVE_THREADS) {  // heads wider than the CTA: rows straight from global memory
         const float* vp = v_cache + off + d;
         float acc = 0.0f;
 #pragma unroll 8
@@ -131,15 +137,20 @@ static cudaError_t raise_naive_attention_smem(size_t bytes) {
 
 void configure_naive_attention_smem(size_t bytes) { raise_naive_attention_smem(bytes); }
 
+// q row, scores of up to max_seq keys (padded to a multiple of 4), two staged V tiles
+size_t naive_attention_smem_bytes(int head_dim, int max_seq) {
+    return (size_t)(head_dim + ((max_seq + 3) & ~3) + 2 * ATTN_V_TILE * head_dim) * sizeof(float);
+}
+
 void launch_attention_naive(cudaStream_t st, const float* q, const float* k_cache, const float* v_cache, float* out,
                             int n, int start_pos, const DecodeCtl* ctl, int n_heads, int n_kv_heads, int head_dim,
                             int max_seq) {
     dim3 grid(n_heads, n);
-    size_t smem = (size_t)(head_dim + max_seq) * sizeof(float);
+    size_t smem = naive_attention_smem_bytes(head_dim, max_seq);
     raise_naive_attention_smem(smem);  // no-op once granted; a failure surfaces as the launch error
     g_kernel_launches++;
     k_attention_naive<<<grid, NAIVE_THREADS, smem, st>>>(q, k_cache, v_cache, out, start_pos, ctl, n_heads, n_kv_heads,
-                                                        head_dim);
+                                                        head_dim, max_seq);
 }
 
 // ── tiled online-softmax prefill attention ─────────────────────────────────

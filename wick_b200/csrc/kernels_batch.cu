@@ -4,6 +4,7 @@
 // copy of the weights.  The mat-vecs of the step are the batched integer GEMMs of the prefill path (weights read
 // once for all rows); everything sequence-specific is here, with the arithmetic of the single-sequence kernels
 // (kernels_basic.cu, kernels_attn.cu) so that every row equals the same sequence decoded alone, bit for bit.
+#include "attn_common.cuh"
 #include "kernels.cuh"
 
 namespace wick {
@@ -122,8 +123,8 @@ __device__ __forceinline__ float qk_dot_rows(const float* __restrict__ q, const 
 
 __global__ void __launch_bounds__(ROWS_ATTN_THREADS) k_attention_rows(const float* __restrict__ q, float* const* __restrict__ k_caches,
                                                                       float* const* __restrict__ v_caches, const uint32_t* __restrict__ positions,
-                                                                      float* __restrict__ out, int n_heads, int n_kv_heads, int hd) {
-    extern __shared__ float sm[];
+                                                                      float* __restrict__ out, int n_heads, int n_kv_heads, int hd, int max_seq) {
+    extern __shared__ __align__(16) float sm[];
     __shared__ double red[32];
     __shared__ float redf[32];
     float* qs = sm;       // hd floats
@@ -165,6 +166,11 @@ __global__ void __launch_bounds__(ROWS_ATTN_THREADS) k_attention_rows(const floa
     const float inv = (float)(1.0 / tot);
     for (int t = tid; t < seq; t += ROWS_ATTN_THREADS) sc[t] = __fmul_rn(sc[t], inv);
     __syncthreads();
+    if (hd <= ROWS_ATTN_THREADS && hd % 4 == 0) {
+        float* vt = sc + ((max_seq + 3) & ~3);
+        attn_values_staged(sc, v_cache + off, kv_dim, hd, seq, vt, out + (size_t)j * hs + h * hd);
+        return;
+    }
     for (int d = tid; d < hd; d += ROWS_ATTN_THREADS) {
         const float* vp = v_cache + off + d;
         float acc = 0.0f;
@@ -177,7 +183,7 @@ __global__ void __launch_bounds__(ROWS_ATTN_THREADS) k_attention_rows(const floa
 cudaError_t launch_attention_rows(cudaStream_t st, const float* q, float* const* k_caches, float* const* v_caches, const uint32_t* positions,
                                   float* out, int n, int n_heads, int n_kv_heads, int head_dim, int max_seq) {
     static size_t granted[64] = {};  // opt-in shared-memory limit of this kernel per device: only ever raised
-    const size_t smem = (size_t)(head_dim + max_seq) * sizeof(float);
+    const size_t smem = naive_attention_smem_bytes(head_dim, max_seq);
     if (smem > 48 * 1024) {
         int dev = 0;
         cudaError_t e = cudaGetDevice(&dev);
@@ -190,7 +196,7 @@ cudaError_t launch_attention_rows(cudaStream_t st, const float* q, float* const*
     }
     dim3 grid(n_heads, n);
     g_kernel_launches++;
-    k_attention_rows<<<grid, ROWS_ATTN_THREADS, smem, st>>>(q, k_caches, v_caches, positions, out, n_heads, n_kv_heads, head_dim);
+    k_attention_rows<<<grid, ROWS_ATTN_THREADS, smem, st>>>(q, k_caches, v_caches, positions, out, n_heads, n_kv_heads, head_dim, max_seq);
     return cudaSuccess;
 }
 

@@ -71,6 +71,7 @@ struct wick_cuda_model {
     int head_dim = 0;
     std::vector<Layer> layers;
     DevWeight embd;
+    TcWeight tc_embd;       // tensor-core copy of the vocabulary matrix, made for the multi-sequence step only
     bool embd_q6k = false;  // token_embd is Q6_K: embd6 is used for the embedding rows and the logits, embd is empty
     DevQ6K embd6;
     float* output_norm = nullptr;
@@ -525,7 +526,7 @@ int32_t check_mega_status(wick_cuda_model* m) {
     return WICK_CUDA_OK;
 }
 
-size_t naive_attn_smem(const wick_cuda_model* m) { return (size_t)(m->head_dim + m->cfg.max_seq_len) * sizeof(float); }
+size_t naive_attn_smem(const wick_cuda_model* m) { return naive_attention_smem_bytes(m->head_dim, (int)m->cfg.max_seq_len); }
 
 // One decode step on the stream; token and position come from m->ctl (run_layers,
 // lfm2.rs:1020-1124, then the tied-embedding logits GEMV, lfm2.rs:2268-2288).
@@ -1057,6 +1058,17 @@ int32_t ensure_batch_buffers(wick_cuda_model* m, uint32_t rows, uint32_t steps) 
         m->batch_cap = cap;
         m->rows_out_cap = 0;
     }
+    if (m->tc_built && !m->embd_q6k && !m->tc_embd.q && rows >= 16) {
+        // the vocabulary head of a batched step is a 64-row GEMM: worth a tensor-core copy of the matrix
+        TcWeight* t = &m->tc_embd;
+        t->m_pad = (m->embd.m + 127) / 128 * 128;
+        t->m = m->embd.m;
+        t->k = m->embd.k;
+        W_TRY(dev_alloc(m, &t->q, t->q_bytes()));
+        W_TRY(dev_alloc(m, &t->scales_t, t->s_bytes() / sizeof(float)));
+        CU_TRY(tc_weight_fill(m->stream, m->embd, t));
+        CU_TRY(cudaStreamSynchronize(m->stream));
+    }
     const size_t out_need = (size_t)steps * rows;
     if (out_need > m->rows_out_cap) {
         W_TRY(dev_alloc(m, &m->rows_out, out_need));
@@ -1114,6 +1126,8 @@ int32_t enqueue_decode_rows(wick_cuda_model* m, int n) {
     if (m->embd_q6k) {
         for (int j = 0; j < n; j++)
             launch_gemv_q6k(st, m->embd6, m->q8s + (size_t)j * (hs / QK), m->q8q + (size_t)j * hs, m->logits_rows + (size_t)j * m->cfg.vocab_size);
+    } else if (m->tc_embd.q) {
+        gemms({{&m->embd, &m->tc_embd, m->logits_rows}});
     } else {
         launch_gemm(st, m->embd, m->q8s, m->q8q, n, m->logits_rows);
     }
@@ -2081,7 +2095,7 @@ int32_t wick_cuda_attention_prefill(const float* q_dev, const float* k_cache_dev
         CU_TRY(cudaFreeAsync(err, st));
         if (code) return fail(WICK_CUDA_ERR_TIMEOUT, "tiled attention: a bounded wait expired (code " + std::to_string(code) + ")");
     } else {
-        size_t smem = (size_t)(head_dim + start_pos + n) * 4;
+        size_t smem = naive_attention_smem_bytes((int)head_dim, (int)(start_pos + n));
         if (smem > 200 * 1024) return fail(WICK_CUDA_ERR_BAD_ARG, "sequence too long for the per-token attention kernel");
         if (smem > 48 * 1024) {
                 configure_naive_attention_smem(smem);
