@@ -375,6 +375,18 @@ def test_attention_flash_bit_exact(ops, orc, n, start, nh, nkv, hd):
     assert_bit_equal(out, _flash_ref(orc, q, kc, vc, n, start, nh, nkv, hd), "flash attention")
 
 
+def test_attention_flash_last_chunk_of_a_4096_prompt(ops, orc):
+    """The 1.6B model's shape (32 query heads, 8 KV heads, head size 64) for the last 512-token chunk of a 4096-token
+    prompt: every query attends 3585..4096 keys.  Also the case the profiler summaries of this kernel are taken on."""
+    n, start, nh, nkv, hd = 512, 3584, 32, 8, 64
+    rng = np.random.default_rng(4096)
+    q = rng.standard_normal((n, nh * hd), dtype=F32)
+    kc = rng.standard_normal((start + n, nkv * hd), dtype=F32)
+    vc = rng.standard_normal((start + n, nkv * hd), dtype=F32)
+    out = host(ops.attention_prefill(dev(q), dev(kc), dev(vc), n, start, nh, nkv, hd, True))
+    assert_bit_equal(out, _flash_ref(orc, q, kc, vc, n, start, nh, nkv, hd), "flash attention, p4096 last chunk")
+
+
 def test_attention_flash_reference_case(ops, orc):
     """cpu.rs:3011-3144 (LCG inputs): flash == naive within 1e-4, and each equals its oracle twin."""
     nh, nkv, hd, n, sp, q_mat, kc, vc = rc.flash_vs_naive_case()

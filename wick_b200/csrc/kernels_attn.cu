@@ -162,15 +162,17 @@ void launch_attention_naive(cudaStream_t st, const float* q, const float* k_cach
 // a K / V tile is fetched once for all of them.  A producer warp streams the tiles with bulk asynchronous copies
 // (cp.async.bulk, one per cache row, completion counted on an mbarrier) into a two-deep ring of shared memory;
 // rows are padded to HD + 4 floats so that the accesses below are free of bank conflicts.  A consumer warp owns
-// 8 * BQ consecutive queries of one head (their rows sit in shared memory too); lane = (slot jq = lane / 4, part
-// s = lane % 4) computes the BQ queries jq, jq + 8, ...:
-//   * q.k: the dots of keys t = 4 i + s (i = 0..7) of the tile with the reference's eight fused chains, KB keys at a
-//     time; a 16-byte piece of a key row serves the lane's BQ queries and a piece of a query row its KB keys (the
-//     kernel is bound by shared-memory bandwidth, so every loaded value has to feed several multiply-adds);
-//   * softmax: tile max over the lane's 8 scores and its three partner lanes; each lane exponentiates its own 8;
+// 8 * BQ consecutive queries of one head (their rows sit in shared memory too); lane = (part g = lane / 8, chain /
+// slot c = lane % 8):
+//   * q.k: in passes of 8 queries x the 8 keys of the part, lane c runs chain c (dims c, c + 8, ...) of all 64 dots,
+//     so a loaded query or key value feeds 8 multiply-adds (the first version, one lane per dot, was bound by
+//     shared-memory wavefronts); the 8 chains of a dot are then added across lanes in the reference's order by three
+//     halving exchanges, which leave lane c with the 8 scores of query c of the pass;
+//   * softmax: tile max over the lane's 8 scores and the three lanes holding the same query's other parts; each
+//     lane exponentiates its own 8;
 //   * the probabilities travel by warp shuffle, in key order: every lane adds all 32 to the f64 tile sum in the
-//     reference's order and applies them to its quarter of the output dims (acc chains in ascending key order); a
-//     piece of a V row again serves the BQ queries.
+//     reference's order and applies them to its 4-float pieces of the output (acc chains in ascending key order); a
+//     piece of a V row serves the lane's BQ queries.
 // Keys at or beyond a query's causal limit are skipped by predicate (they may hold anything).
 // Every wait is bounded: on expiry the CTA sets *err, stops waiting and returns.
 constexpr int FLASH_TILE = 32;  // FLASH_TILE_KV, cpu.rs:1513
@@ -203,21 +205,17 @@ __device__ __forceinline__ bool fa_wait(uint64_t* bar, uint32_t parity, volatile
 }
 
 #ifndef WICK_FA_MIN_CTAS
-#define WICK_FA_MIN_CTAS 1
-#endif
-#ifndef WICK_FA_KB
-#define WICK_FA_KB 2
+#define WICK_FA_MIN_CTAS 2
 #endif
 #ifndef WICK_FA_BQ
 #define WICK_FA_BQ 2
 #endif
-template <int HD, int BQ>
-__global__ void __launch_bounds__(288, HD <= 64 ? WICK_FA_MIN_CTAS : 1) k_attention_flash(const float* __restrict__ q, const float* __restrict__ k_cache,
+template <int HD, int BQ, int MAXW>  // MAXW: the most consumer warps a launch of this instance has (4 or 8)
+__global__ void __launch_bounds__((MAXW + 1) * 32, MAXW == 4 ? WICK_FA_MIN_CTAS : 1) k_attention_flash(const float* __restrict__ q, const float* __restrict__ k_cache,
                                                           const float* __restrict__ v_cache, float* __restrict__ out, int n, int start_pos,
                                                           int n_heads, int n_kv_heads, int qb, uint32_t* __restrict__ err) {
     constexpr int ROW = HD + 4;          // padded row, floats
     constexpr int DPL = HD / 4;          // output dims per lane
-    constexpr int KB = WICK_FA_KB;       // keys whose dots share one pass over the query row
     extern __shared__ __align__(128) uint8_t fa_smem[];
     uint64_t* full = reinterpret_cast<uint64_t*>(fa_smem);           // [2]
     uint64_t* empty = full + 2;                                       // [2]
@@ -227,7 +225,7 @@ __global__ void __launch_bounds__(288, HD <= 64 ? WICK_FA_MIN_CTAS : 1) k_attent
     float* Qs = Vs + 2 * FLASH_TILE * ROW;                            // [consumer warps][8 * BQ][ROW]
 
     const int group = n_heads / n_kv_heads;
-    const int n_cw = group * (qb / (8 * BQ));  // consumer warps
+    const int n_cw = group * (qb / (8 * BQ));  // consumer warps (<= MAXW)
     const int kvh = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int hs = n_heads * HD, kv_dim = n_kv_heads * HD;
@@ -280,30 +278,37 @@ __global__ void __launch_bounds__(288, HD <= 64 ? WICK_FA_MIN_CTAS : 1) k_attent
     }
     if (warp > n_cw) return;
 
-    // A consumer warp owns QPW = 8 * BQ consecutive queries of one head; lane = (slot jq = lane / 4, part s = lane % 4)
-    // computes the BQ queries jq, jq + 8, ... of the warp's run: every K and V value it loads serves BQ queries.
+    // A consumer warp owns QPW = 8 * BQ consecutive queries of one head.  lane = (part g = lane / 8, chain c = lane % 8).
+    //   q.k: part g owns keys t = 8 (u / 2) + 2 g + (u % 2), u = 0..7, of the tile (rows two apart for neighbouring
+    //   parts: with the padded rows their 8-word reads fall into four different bank octets).  A pass handles 8 queries
+    //   x the part's 8 keys; lane c runs chain c of all 64 dots (dims c, c + 8, ...: chains 0..3 are the reference's sum0
+    //   lanes, 4..7 its sum1 lanes), so every loaded query or key value feeds 8 multiply-adds.  The chains of a dot are then
+    //   added across the 8 lanes in the reference's order - (sum0[l] + sum1[l]) by an exchange with lane c ^ 4, then
+    //   lanes c ^ 1, then c ^ 2 - each exchange halving what a lane keeps, so that lane c ends with the 8 scores of
+    //   query c of the pass (a + b == b + a bit for bit, so both partners hold the same sums).
+    //   softmax and weighted V: lane (g, c) is "slot c, part g": it owns the scores of queries c, c + 8, ... for its part's
+    //   keys and, of those queries' outputs, the 4-float pieces g, g + 4, g + 8, ... of the head.
     constexpr int QPW = 8 * BQ;
     const int g = warp % group, run = warp / group;
-    const int jq = lane >> 2, s = lane & 3;
+    const int part = lane >> 3, c = lane & 7;
     const int h = kvh * group + g;
     const int j0 = j_first + run * QPW;
     const float scale = __fdiv_rn(1.0f, sqrtf((float)HD));
     int my_max[BQ];
 #pragma unroll
     for (int u = 0; u < BQ; u++) {
-        const int j = j0 + u * 8 + jq;
+        const int j = j0 + u * 8 + c;
         my_max[u] = j < n ? start_pos + j + 1 : 0;
     }
 
-    // the warp's query rows in shared memory (padded like the K rows: the 8 slots of a 16-byte load hit 8
-    // different bank groups); lane L copies 16-byte pieces L, L + 32, ...
+    // the warp's query rows in shared memory (padded like the K rows); lane L copies 16-byte pieces L, L + 32, ...
     float* qw = Qs + warp * QPW * ROW;
     for (int i = lane; i < QPW * (HD / 4); i += 32) {
-        const int r = i / (HD / 4), c = i % (HD / 4);
+        const int r = i / (HD / 4), cc = i % (HD / 4);
         const int jr = j0 + r;
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (jr < n) v = __ldg(reinterpret_cast<const float4*>(q + (size_t)jr * hs + h * HD) + c);
-        reinterpret_cast<float4*>(qw + r * ROW)[c] = v;
+        if (jr < n) v = __ldg(reinterpret_cast<const float4*>(q + (size_t)jr * hs + h * HD) + cc);
+        reinterpret_cast<float4*>(qw + r * ROW)[cc] = v;
     }
     __syncwarp();
     float acc[BQ][DPL];
@@ -316,7 +321,8 @@ __global__ void __launch_bounds__(288, HD <= 64 ? WICK_FA_MIN_CTAS : 1) k_attent
         running_max[u] = __int_as_float(0xFF800000);
         running_sum[u] = 0.0;
     }
-    const int src_base = lane & ~3;
+    // key index of the part's u-th key, and where the probability of key t of this lane's queries lives
+    auto part_key = [&](int u) { return 8 * (u >> 1) + 2 * part + (u & 1); };
 
     for (int it = 0; it < n_tiles; it++) {
         const int buf = it & 1, kv0 = it * FLASH_TILE;
@@ -333,73 +339,72 @@ __global__ void __launch_bounds__(288, HD <= 64 ? WICK_FA_MIN_CTAS : 1) k_attent
             float e[BQ][8];
             float tmax[BQ];
 #pragma unroll
-            for (int u = 0; u < BQ; u++) tmax[u] = __int_as_float(0xFF800000);
-            // the lane's 8 keys in blocks of KB; a 16-byte piece of a key row is loaded once for the BQ queries and a
-            // piece of a query row once for the KB keys
+            for (int pass = 0; pass < BQ; pass++) {
+                // chain c of the 8 x 8 dots of this pass
+                float d8[8][8];
 #pragma unroll
-            for (int i0 = 0; i0 < 8; i0 += KB) {
-                if (4 * i0 + s < len_max) {  // (keys of a block ascend: if the first is out of range for all, so is the rest)
-                    float s0[BQ][KB][4], s1[BQ][KB][4];
+                for (int j = 0; j < 8; j++)
 #pragma unroll
-                    for (int u = 0; u < BQ; u++)
+                    for (int u = 0; u < 8; u++) d8[j][u] = 0.0f;
+                const float* qp = qw + (pass * 8) * ROW + c;
+                const float* kp = Kt + (2 * part) * ROW + c;
+#pragma unroll 2
+                for (int i = 0; i < HD; i += 8) {
+                    float qv[8], kv[8];
 #pragma unroll
-                        for (int k = 0; k < KB; k++)
+                    for (int j = 0; j < 8; j++) qv[j] = qp[j * ROW + i];
 #pragma unroll
-                            for (int l = 0; l < 4; l++) s0[u][k][l] = s1[u][k][l] = 0.0f;
+                    for (int u = 0; u < 8; u++) kv[u] = kp[(8 * (u >> 1) + (u & 1)) * ROW + i];
 #pragma unroll
-                    for (int d = 0; d < HD; d += 8) {
-                        float4 ka[KB], kb[KB];
+                    for (int j = 0; j < 8; j++)
 #pragma unroll
-                        for (int k = 0; k < KB; k++) {
-                            const float* kr = Kt + (4 * (i0 + k) + s) * ROW + d;
-                            ka[k] = *reinterpret_cast<const float4*>(kr);
-                            kb[k] = *reinterpret_cast<const float4*>(kr + 4);
-                        }
-#pragma unroll
-                        for (int u = 0; u < BQ; u++) {
-                            const float* qr = qw + (u * 8 + jq) * ROW + d;
-                            const float4 qa = *reinterpret_cast<const float4*>(qr);
-                            const float4 qb4 = *reinterpret_cast<const float4*>(qr + 4);
-#pragma unroll
-                            for (int k = 0; k < KB; k++) {
-                                s0[u][k][0] = __fmaf_rn(qa.x, ka[k].x, s0[u][k][0]);
-                                s0[u][k][1] = __fmaf_rn(qa.y, ka[k].y, s0[u][k][1]);
-                                s0[u][k][2] = __fmaf_rn(qa.z, ka[k].z, s0[u][k][2]);
-                                s0[u][k][3] = __fmaf_rn(qa.w, ka[k].w, s0[u][k][3]);
-                                s1[u][k][0] = __fmaf_rn(qb4.x, kb[k].x, s1[u][k][0]);
-                                s1[u][k][1] = __fmaf_rn(qb4.y, kb[k].y, s1[u][k][1]);
-                                s1[u][k][2] = __fmaf_rn(qb4.z, kb[k].z, s1[u][k][2]);
-                                s1[u][k][3] = __fmaf_rn(qb4.w, kb[k].w, s1[u][k][3]);
-                            }
-                        }
-                    }
-#pragma unroll
-                    for (int u = 0; u < BQ; u++)
-#pragma unroll
-                        for (int k = 0; k < KB; k++) {
-                            const float v0 = __fadd_rn(s0[u][k][0], s1[u][k][0]), v1 = __fadd_rn(s0[u][k][1], s1[u][k][1]);
-                            const float v2 = __fadd_rn(s0[u][k][2], s1[u][k][2]), v3 = __fadd_rn(s0[u][k][3], s1[u][k][3]);
-                            const float sc = __fmul_rn(__fadd_rn(__fadd_rn(v0, v1), __fadd_rn(v2, v3)), scale);
-                            const bool in = 4 * (i0 + k) + s < len[u];
-                            e[u][i0 + k] = in ? sc : __int_as_float(0xFF800000);
-                            if (in && sc > tmax[u]) tmax[u] = sc;
-                        }
-                } else {
-#pragma unroll
-                    for (int u = 0; u < BQ; u++)
-#pragma unroll
-                        for (int k = 0; k < KB; k++) e[u][i0 + k] = __int_as_float(0xFF800000);
+                        for (int u = 0; u < 8; u++) d8[j][u] = __fmaf_rn(qv[j], kv[u], d8[j][u]);
                 }
+                // sum0[l] + sum1[l]: exchange with lane c ^ 4, keeping the queries whose bit 2 equals this lane's
+                float r1[4][8];
+                const bool hi4 = (c & 4) != 0;
+#pragma unroll
+                for (int jj = 0; jj < 4; jj++)
+#pragma unroll
+                    for (int u = 0; u < 8; u++) {
+                        const float mine = hi4 ? d8[jj + 4][u] : d8[jj][u];
+                        const float other = hi4 ? d8[jj][u] : d8[jj + 4][u];
+                        r1[jj][u] = __fadd_rn(mine, __shfl_xor_sync(0xffffffffu, other, 4));
+                    }
+                // (v0 + v1), (v2 + v3): exchange with lane c ^ 1, keeping the queries whose bit 0 equals this lane's
+                float r2[2][8];
+                const bool hi1 = (c & 1) != 0;
+#pragma unroll
+                for (int m = 0; m < 2; m++)
+#pragma unroll
+                    for (int u = 0; u < 8; u++) {
+                        const float mine = hi1 ? r1[2 * m + 1][u] : r1[2 * m][u];
+                        const float other = hi1 ? r1[2 * m][u] : r1[2 * m + 1][u];
+                        r2[m][u] = __fadd_rn(mine, __shfl_xor_sync(0xffffffffu, other, 1));
+                    }
+                // (v0 + v1) + (v2 + v3): exchange with lane c ^ 2: query c of the pass remains
+                const bool hi2 = (c & 2) != 0;
+                float mx = __int_as_float(0xFF800000);
+#pragma unroll
+                for (int u = 0; u < 8; u++) {
+                    const float mine = hi2 ? r2[1][u] : r2[0][u];
+                    const float other = hi2 ? r2[0][u] : r2[1][u];
+                    const float sc = __fmul_rn(__fadd_rn(mine, __shfl_xor_sync(0xffffffffu, other, 2)), scale);
+                    const bool in = part_key(u) < len[pass];
+                    e[pass][u] = in ? sc : __int_as_float(0xFF800000);
+                    if (in && sc > mx) mx = sc;
+                }
+                tmax[pass] = mx;
             }
             float new_max[BQ];
 #pragma unroll
             for (int u = 0; u < BQ; u++) {
-                tmax[u] = fmaxf(tmax[u], __shfl_xor_sync(0xffffffffu, tmax[u], 1));
-                tmax[u] = fmaxf(tmax[u], __shfl_xor_sync(0xffffffffu, tmax[u], 2));
+                tmax[u] = fmaxf(tmax[u], __shfl_xor_sync(0xffffffffu, tmax[u], 8));
+                tmax[u] = fmaxf(tmax[u], __shfl_xor_sync(0xffffffffu, tmax[u], 16));
                 new_max[u] = fmaxf(running_max[u], tmax[u]);
                 const float rescale = running_max[u] > __int_as_float(0xFF800000) ? ggml_expf(__fsub_rn(running_max[u], new_max[u])) : 0.0f;
 #pragma unroll
-                for (int i = 0; i < 8; i++) e[u][i] = (4 * i + s < len[u]) ? ggml_expf(__fsub_rn(e[u][i], new_max[u])) : 0.0f;
+                for (int i = 0; i < 8; i++) e[u][i] = (part_key(i) < len[u]) ? ggml_expf(__fsub_rn(e[u][i], new_max[u])) : 0.0f;
 #pragma unroll
                 for (int d = 0; d < DPL; d++) acc[u][d] = __fmul_rn(acc[u][d], rescale);
                 if (len[u] > 0) running_sum[u] = running_sum[u] * (double)rescale;  // (+ the tile sum, below)
@@ -409,24 +414,25 @@ __global__ void __launch_bounds__(288, HD <= 64 ? WICK_FA_MIN_CTAS : 1) k_attent
             for (int u = 0; u < BQ; u++) tsum[u] = 0.0;
 #pragma unroll
             for (int t = 0; t < FLASH_TILE; t++) {
+                // key t belongs to part (t % 8) / 2, as its key number 2 (t / 8) + t % 2
                 float p[BQ];
 #pragma unroll
-                for (int u = 0; u < BQ; u++) p[u] = __shfl_sync(0xffffffffu, e[u][t >> 2], src_base | (t & 3));
+                for (int u = 0; u < BQ; u++) p[u] = __shfl_sync(0xffffffffu, e[u][2 * (t >> 3) + (t & 1)], (((t & 7) >> 1) << 3) | c);
                 if (t < len_max) {
                     float4 vv[DPL / 4];
-                    const float4* vp = reinterpret_cast<const float4*>(Vt + t * ROW + s * DPL);
+                    const float4* vp = reinterpret_cast<const float4*>(Vt + t * ROW) + part;
 #pragma unroll
-                    for (int c = 0; c < DPL / 4; c++) vv[c] = vp[c];
+                    for (int cc = 0; cc < DPL / 4; cc++) vv[cc] = vp[4 * cc];  // the four parts read 64 consecutive bytes
 #pragma unroll
                     for (int u = 0; u < BQ; u++)
                         if (t < len[u]) {
                             tsum[u] += (double)p[u];
 #pragma unroll
-                            for (int c = 0; c < DPL / 4; c++) {
-                                acc[u][4 * c + 0] = __fmaf_rn(p[u], vv[c].x, acc[u][4 * c + 0]);
-                                acc[u][4 * c + 1] = __fmaf_rn(p[u], vv[c].y, acc[u][4 * c + 1]);
-                                acc[u][4 * c + 2] = __fmaf_rn(p[u], vv[c].z, acc[u][4 * c + 2]);
-                                acc[u][4 * c + 3] = __fmaf_rn(p[u], vv[c].w, acc[u][4 * c + 3]);
+                            for (int cc = 0; cc < DPL / 4; cc++) {
+                                acc[u][4 * cc + 0] = __fmaf_rn(p[u], vv[cc].x, acc[u][4 * cc + 0]);
+                                acc[u][4 * cc + 1] = __fmaf_rn(p[u], vv[cc].y, acc[u][4 * cc + 1]);
+                                acc[u][4 * cc + 2] = __fmaf_rn(p[u], vv[cc].z, acc[u][4 * cc + 2]);
+                                acc[u][4 * cc + 3] = __fmaf_rn(p[u], vv[cc].w, acc[u][4 * cc + 3]);
                             }
                         }
                 }
@@ -443,14 +449,14 @@ __global__ void __launch_bounds__(288, HD <= 64 ? WICK_FA_MIN_CTAS : 1) k_attent
     }
 #pragma unroll
     for (int u = 0; u < BQ; u++) {
-        const int j = j0 + u * 8 + jq;
+        const int j = j0 + u * 8 + c;
         if (j < n) {
             const float inv = (float)(1.0 / running_sum[u]);
-            float4* op = reinterpret_cast<float4*>(out + (size_t)j * hs + h * HD + s * DPL);
+            float4* op = reinterpret_cast<float4*>(out + (size_t)j * hs + h * HD) + part;
 #pragma unroll
-            for (int c = 0; c < DPL / 4; c++)
-                op[c] = make_float4(__fmul_rn(acc[u][4 * c + 0], inv), __fmul_rn(acc[u][4 * c + 1], inv), __fmul_rn(acc[u][4 * c + 2], inv),
-                                    __fmul_rn(acc[u][4 * c + 3], inv));
+            for (int cc = 0; cc < DPL / 4; cc++)
+                op[4 * cc] = make_float4(__fmul_rn(acc[u][4 * cc + 0], inv), __fmul_rn(acc[u][4 * cc + 1], inv), __fmul_rn(acc[u][4 * cc + 2], inv),
+                                     __fmul_rn(acc[u][4 * cc + 3], inv));
         }
     }
 }
@@ -474,14 +480,23 @@ static cudaError_t launch_flash_hd(cudaStream_t st, const float* q, const float*
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
     if (smem > 48 * 1024 && (dev < 0 || dev >= 64 || configured[dev] < smem)) {
-        e = cudaFuncSetAttribute(k_attention_flash<HD, BQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        e = cudaFuncSetAttribute(k_attention_flash<HD, BQ, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        e = cudaFuncSetAttribute(k_attention_flash<HD, BQ, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) configured[dev] = smem;
+    }
+    static bool carved[64] = {};
+    if (dev >= 0 && dev < 64 && !carved[dev]) {  // several CTAs per SM only fit when the SM's L1/shared split favours shared memory
+        cudaFuncSetAttribute(k_attention_flash<HD, BQ, 4>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        cudaFuncSetAttribute(k_attention_flash<HD, BQ, 8>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        carved[dev] = true;
     }
     dim3 grid(n_kv_heads, (n + qb - 1) / qb);
     const int threads = (n_cw + 1) * 32;
     g_kernel_launches++;
-    k_attention_flash<HD, BQ><<<grid, threads, smem, st>>>(q, k_cache, v_cache, out, n, start_pos, n_heads, n_kv_heads, qb, err);
+    if (n_cw <= 4) k_attention_flash<HD, BQ, 4><<<grid, threads, smem, st>>>(q, k_cache, v_cache, out, n, start_pos, n_heads, n_kv_heads, qb, err);
+    else k_attention_flash<HD, BQ, 8><<<grid, threads, smem, st>>>(q, k_cache, v_cache, out, n, start_pos, n_heads, n_kv_heads, qb, err);
     return cudaSuccess;
 }
 
