@@ -205,13 +205,13 @@ __device__ __forceinline__ bool fa_wait(uint64_t* bar, uint32_t parity, volatile
 }
 
 #ifndef WICK_FA_MIN_CTAS
-#define WICK_FA_MIN_CTAS 2
+#define WICK_FA_MIN_CTAS 4
 #endif
 #ifndef WICK_FA_BQ
-#define WICK_FA_BQ 2
+#define WICK_FA_BQ 1
 #endif
 template <int HD, int BQ, int MAXW>  // MAXW: the most consumer warps a launch of this instance has (4 or 8)
-__global__ void __launch_bounds__((MAXW + 1) * 32, MAXW == 4 ? WICK_FA_MIN_CTAS : 1) k_attention_flash(const float* __restrict__ q, const float* __restrict__ k_cache,
+__global__ void __launch_bounds__((MAXW + 1) * 32, MAXW == 4 ? (HD <= 64 ? WICK_FA_MIN_CTAS : 2) : 1) k_attention_flash(const float* __restrict__ q, const float* __restrict__ k_cache,
                                                           const float* __restrict__ v_cache, float* __restrict__ out, int n, int start_pos,
                                                           int n_heads, int n_kv_heads, int qb, uint32_t* __restrict__ err) {
     constexpr int ROW = HD + 4;          // padded row, floats
