@@ -137,6 +137,41 @@ def test_gemm_tc_extreme_values(ops, orc):
     assert np.abs(host(out) - exact).max() <= 1e-5 * np.abs(exact).max()
 
 
+def test_gemm_tc_exact_extreme_lane_partials(ops, orc):
+    """The bit-exact kernel on the largest lane partials (8 * 8 * 127 = 8128 per NEON lane group and block) and on
+    low-bit patterns next to them: hand-built integer operands that survive both quantisers unchanged."""
+    from wick_b200 import gguf_synth as gs
+    m, k, n = 128, 512, 48
+    rng = np.random.default_rng(8128)
+    # weights: integers of [-8, 7] times a power-of-two block scale; one -8 per block pins the scale
+    wq = rng.choice(np.array([-8, -8, -8, -7, 7, 7, 6, -1, 1, 0]), size=(m, k))
+    wq[:, ::32] = -8
+    wq[:16] = -8                                   # rows of all -8
+    wq[16:32] = np.where(np.arange(k) % 2 == 0, -8, 7)
+    raw = gs.quantize_q4_0((wq * 0.0625).astype(F32))
+    # activations: integers of [-127, 127] times a power-of-two scale; one +/-127 per block pins the scale
+    xq = rng.choice(np.array([127, -127, 126, -126, 113, -113, 1, -1, 15, -16, 17, 0]), size=(n, k))
+    xq[:, 5::32] = 127
+    xq[0] = 127
+    xq[1] = -127
+    xq[2] = np.where(np.arange(k) % 2 == 0, 127, -127)
+    xq[3] = np.where(np.arange(k) % 3 == 0, 127, 126)
+    xq[3, 5::32] = 127
+    x = (xq * 0.5).astype(F32)
+    bs, bq = orc.quantize_q8_0(x)
+    assert np.array_equal(bq.reshape(n, k).astype(np.int64), xq), "the test's activations must survive the quantiser"
+    w = ops.QuantWeight(orc.DT_Q4_0, raw, m, k)
+    S = orc.block_sums(orc.DT_Q4_0, raw, bq[0], m, k)[0]
+    assert np.abs(S).max() == 32 * 8 * 127
+    out = host(ops.gemm_q8_tc_exact(w, dev(bs), dev(bq)))
+    exact = host(ops.gemm_q8(w, dev(bs), dev(bq)))
+    assert np.array_equal(out.view(np.uint32), exact.view(np.uint32)), \
+        f"{int((out.view(np.uint32) != exact.view(np.uint32)).sum())} outputs differ"
+    for j in range(0, n, 7):
+        ref = orc.gemv(orc.DT_Q4_0, raw, bs[j], bq[j], m, k)
+        assert np.array_equal(out[j].view(np.uint32), ref.view(np.uint32))
+
+
 def test_gemm_tc_properties_full_size(ops, orc):
     """Size-independent properties at n = 4096: power-of-two activation scales commute with the product
     bit for bit, tokens are independent of their position in the batch, and repeated runs are identical."""

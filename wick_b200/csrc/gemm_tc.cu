@@ -20,7 +20,7 @@
 // Roles in a CTA of 20 warps (one CTA per SM, persistent over output tiles):
 //   warp 0  lane 0: TMA producer, one K=128 stage (4 blocks) of W rows and activation rows per step
 //   warp 1  lane 0: issues tcgen05.mma / tcgen05.commit; the whole warp owns the TMEM allocation
-//   warp 2        : copies the stage's weight scales and (transposed) activation scales into smem
+//   warp 2        : copies the stage's weight scales and (transposed) activation scales into smem (cp.async)
 //   warps 4..19   : epilogue; warp w reads TMEM lanes 32*(w%4).. and columns (w-4)/4 * BN/4 ..; four
 //                   warps per scheduler hide the tensor-memory load and barrier latencies
 // Every wait is bounded: on expiry the kernel records an error code, all roles leave their loops and
@@ -104,6 +104,13 @@ __device__ __forceinline__ bool mbar_wait(TcSmem<BN>* sm, uint32_t bar, uint32_t
     sm->abort = 1;
     atomicCAS(err, 0u, code);
     return false;
+}
+
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_4(uint32_t dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
 }
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
@@ -235,7 +242,7 @@ k_gemm_tc(const __grid_constant__ TcJob job, const __grid_constant__ CUtensorMap
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < TC_STAGES; s++) {
-            mbar_init(smem_u32(&sm->full[s]), 2);                 // producer (with tx bytes) + scale warp
+            mbar_init(smem_u32(&sm->full[s]), 1 + 32);            // producer (with tx bytes) + every lane of the scale warp
             mbar_init(smem_u32(&sm->empty[s]), 1 + TC_EPI_WARPS);  // MMA commit + epilogue warps
         }
         for (int b = 0; b < NBUF; b++) {
@@ -327,22 +334,26 @@ k_gemm_tc(const __grid_constant__ TcJob job, const __grid_constant__ CUtensorMap
                 if (!ok) break;
                 TcStage<BN>& st = sm->stage[s];
                 const int b0 = ks * TC_KB_PER_STAGE;
+                // Asynchronous copies (cp.async), each lane's arrival on the stage's barrier deferred until its own copies
+                // have landed: the warp never waits for a load, so the scales of as many stages as the ring has free are
+                // in flight at once (with plain loads every stage cost this warp one dependent trip to L2).
 #pragma unroll
-                for (int kk = 0; kk < TC_KB_PER_STAGE; kk++) {
-                    const float4 v = __ldg(reinterpret_cast<const float4*>(wst + (size_t)(b0 + kk) * m_pad + tl.m0) + lane);
-                    reinterpret_cast<float4*>(st.sw[kk])[lane] = v;
-                }
+                for (int kk = 0; kk < TC_KB_PER_STAGE; kk++)
+                    cp_async_16(smem_u32(reinterpret_cast<float4*>(st.sw[kk]) + lane),
+                                reinterpret_cast<const float4*>(wst + (size_t)(b0 + kk) * m_pad + tl.m0) + lane);
 #pragma unroll
                 for (int c = lane; c < TOK; c += 32) {
-                    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (tl.n0 + c < n) v = __ldg(reinterpret_cast<const float4*>(x_scales + (size_t)(tl.n0 + c) * nb + b0));
-                    st.sx[0][c] = v.x;
-                    st.sx[1][c] = v.y;
-                    st.sx[2][c] = v.z;
-                    st.sx[3][c] = v.w;
+                    if (tl.n0 + c < n) {
+                        const float* src = x_scales + (size_t)(tl.n0 + c) * nb + b0;
+#pragma unroll
+                        for (int kk = 0; kk < TC_KB_PER_STAGE; kk++) cp_async_4(smem_u32(&st.sx[kk][c]), src + kk);
+                    } else {
+#pragma unroll
+                        for (int kk = 0; kk < TC_KB_PER_STAGE; kk++) st.sx[kk][c] = 0.0f;
+                    }
                 }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&sm->full[s]));
+                // .noinc: the arrival was counted when the barrier was initialised (33 = producer + 32 lanes)
+                asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&sm->full[s])) : "memory");
             }
         }
     } else if (warp >= 4) {
