@@ -84,3 +84,25 @@ def test_model_load_without_gpu_fails_loudly(cuda_lib, model_dir):
     with pytest.raises(WickCudaError) as e:
         CudaLfm2Model(path, 64)
     assert e.value.code in (-2, -1)
+
+
+def test_gguf_wrapping_tensor_shape_is_rejected(cuda_lib, model_dir):
+    """A tensor whose dimensions multiply to more than 2^64 (the product wraps to a tiny element count) must not pass
+    the 'fits in the file' check."""
+    import struct
+    from wick_b200 import _lib, gguf_synth as gs
+    path = gs.cached_model("tiny", "q4_0", 0, cache_dir=model_dir)
+    data = bytearray(open(path, "rb").read())
+    name = b"token_embd.weight"
+    at = data.find(struct.pack("<Q", len(name)) + name)
+    assert at > 0
+    dims_at = at + 8 + len(name)
+    (n_dims,) = struct.unpack_from("<I", data, dims_at)
+    assert n_dims == 2
+    h = C.c_void_p()
+    for d0, d1 in ((1 << 63, 2), (1 << 32, 1 << 32), (1 << 31, 64)):
+        bad = bytearray(data)
+        struct.pack_into("<QQ", bad, dims_at + 4, d0, d1)
+        buf = (C.c_uint8 * len(bad)).from_buffer(bad)
+        assert cuda_lib.wick_cuda_model_create(C.addressof(buf), len(bad), 64, 0, C.byref(h)) == _lib.ERR_BAD_GGUF
+        assert b"implausible shape" in cuda_lib.wick_cuda_last_error()

@@ -145,6 +145,7 @@ class GgufImage {
                         v.ints.push_back((int64_t)e.u);
                     }
                 } else {
+                    if (es != 0 && v.count > (n_ - pos_) / es) throw std::runtime_error("GGUF: truncated header");  // (the product could wrap)
                     need(es * v.count);
                     pos_ += es * v.count;
                 }
@@ -196,7 +197,12 @@ class GgufImage {
         uint64_t data0 = (pos_ + align - 1) / align * align;
         for (auto& r : raw) {
             uint64_t ne = 1;
-            for (uint64_t d : r.t.dims) ne *= d;
+            for (uint64_t d : r.t.dims) {
+                // every dimension fits an int and the element count stays far below 2^64 (a wrapped count would pass the
+                // size check below with a tiny size)
+                if (d > 0x7fffffffull || (d != 0 && ne > (1ull << 40) / d)) throw std::runtime_error("tensor " + r.name + ": implausible shape");
+                ne *= d;
+            }
             r.t.size = type_size(r.t.type, ne);
             r.t.offset += data0;
             if (r.t.size && (r.t.offset + r.t.size > n_ || r.t.offset + r.t.size < r.t.offset))
