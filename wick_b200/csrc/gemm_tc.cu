@@ -302,9 +302,11 @@ k_gemm_tc(const __grid_constant__ TcJob job, const __grid_constant__ CUtensorMap
                     for (int kk = 0; kk < TC_KB_PER_STAGE; kk++) {
                         const uint32_t j = g * TC_KB_PER_STAGE + kk;
                         const uint32_t buf = j % NBUF;
-                        if (!EXACT || (kk & 1) == 0) {
-                            // EXACT hands buffers over in (even block, odd block) pairs: barrier index = pair
-                            const uint32_t bi = EXACT ? buf >> 1 : buf, ub = EXACT ? (j >> 1) / (NBUF / 2) : j / NBUF;
+                        if (!EXACT || kk == 0) {
+                            // EXACT hands the buffers over a stage (4 blocks = half of tensor memory) at a time: every
+                            // hand-over costs each epilogue warp a barrier wait and an arrival, both long dependent
+                            // steps of its loop, and that loop - not the tensor pipe - sets the pace of the kernel
+                            const uint32_t bi = EXACT ? (g & 1u) : buf, ub = EXACT ? (g >> 1) : j / NBUF;
                             ok = mbar_wait<BN, 64>(sm, smem_u32(&sm->tmem_empty[bi]), (ub & 1) ^ 1, err, 3);
                             if (!ok) break;
                             tc_fence_after();
@@ -312,7 +314,7 @@ k_gemm_tc(const __grid_constant__ TcJob job, const __grid_constant__ CUtensorMap
                         // 32 bytes further along K inside the swizzle atom: +2 in the 16-byte address field
                         umma_i8(tmem_base + buf * BN, da + (unsigned long long)(kk * 2), db + (unsigned long long)(kk * 2), idesc);
                         if (!EXACT) umma_commit(smem_u32(&sm->tmem_full[buf]));
-                        else if (kk & 1) umma_commit(smem_u32(&sm->tmem_full[buf >> 1]));
+                        else if (kk == TC_KB_PER_STAGE - 1) umma_commit(smem_u32(&sm->tmem_full[g & 1u]));
                     }
                     if (ok) umma_commit(smem_u32(&sm->empty[s]));
                 }
@@ -448,25 +450,25 @@ k_gemm_tc(const __grid_constant__ TcJob job, const __grid_constant__ CUtensorMap
                 for (int ks = 0; ks < k_stages && ok; ks++, g++) {
                     const int s = g % TC_STAGES;
                     const uint32_t u = g / TC_STAGES;
-                    ok = mbar_wait(sm, smem_u32(&sm->full[s]), u & 1, err, 5);
-                    ok = __all_sync(0xffffffffu, ok);
+                    // (every lane of a warp runs the same wait on the same barrier and gets the same answer)
+                    ok = mbar_wait(sm, smem_u32(&sm->full[s]), u & 1, err, 5);  // the stage's scales
                     if (!ok) break;
+                    const uint32_t unit = g & 1u;                                // the half of tensor memory with its 4 blocks
+                    ok = mbar_wait(sm, smem_u32(&sm->tmem_full[unit]), (g >> 1) & 1, err, 6);
+                    if (!ok) break;
+                    tc_fence_after();
                     const TcStage<BN>& st = sm->stage[s];
-#pragma unroll 1
+#pragma unroll
                     for (int kp = 0; kp < TC_KB_PER_STAGE / 2; kp++) {
-                        const uint32_t jp = g * (TC_KB_PER_STAGE / 2) + kp;
-                        const uint32_t pb = jp % (NBUF / 2), ub = jp / (NBUF / 2);
-                        ok = mbar_wait(sm, smem_u32(&sm->tmem_full[pb]), ub & 1, err, 6);
-                        ok = __all_sync(0xffffffffu, ok);
-                        if (!ok) break;
-                        tc_fence_after();
                         int32_t S0[COLS], S1[COLS];
-                        tmem_ld<COLS>(lane_base + (2 * pb) * BN, S0);
-                        tmem_ld<COLS>(lane_base + (2 * pb + 1) * BN, S1);
+                        tmem_ld<COLS>(lane_base + (unit * TC_KB_PER_STAGE + 2 * kp) * BN, S0);
+                        tmem_ld<COLS>(lane_base + (unit * TC_KB_PER_STAGE + 2 * kp + 1) * BN, S1);
                         tmem_ld_wait();
-                        tc_fence_before();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(smem_u32(&sm->tmem_empty[pb]));
+                        if (kp == TC_KB_PER_STAGE / 2 - 1) {  // all four blocks are in registers: the unit may be refilled
+                            tc_fence_before();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(smem_u32(&sm->tmem_empty[unit]));
+                        }
                         const float sw0 = st.sw[2 * kp][row_in_tile], sw1 = st.sw[2 * kp + 1][row_in_tile];
                         const float4 x0 = *reinterpret_cast<const float4*>(&st.sx[2 * kp][cg * TPT]);
                         const float4 x1 = *reinterpret_cast<const float4*>(&st.sx[2 * kp + 1][cg * TPT]);
@@ -483,7 +485,6 @@ k_gemm_tc(const __grid_constant__ TcJob job, const __grid_constant__ CUtensorMap
                             }
                         }
                     }
-                    if (!ok) break;
                     __syncwarp();
                     if (lane == 0) mbar_arrive(smem_u32(&sm->empty[s]));
                 }
