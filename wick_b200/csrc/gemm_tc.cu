@@ -458,32 +458,38 @@ k_gemm_tc(const __grid_constant__ TcJob job, const __grid_constant__ CUtensorMap
                     if (!ok) break;
                     tc_fence_after();
                     const TcStage<BN>& st = sm->stage[s];
+                    {
+                        // the load of block kk + 1 is in flight while the chains of block kk run
+                        int32_t SA[COLS], SB[COLS];
+                        auto chains = [&](const int32_t (&S)[COLS], const int kk) {
+                            const float sw = st.sw[kk][row_in_tile];
+                            const float4 x = *reinterpret_cast<const float4*>(&st.sx[kk][cg * TPT]);
+                            const float xs[4] = {x.x, x.y, x.z, x.w};
 #pragma unroll
-                    for (int kp = 0; kp < TC_KB_PER_STAGE / 2; kp++) {
-                        int32_t S0[COLS], S1[COLS];
-                        tmem_ld<COLS>(lane_base + (unit * TC_KB_PER_STAGE + 2 * kp) * BN, S0);
-                        tmem_ld<COLS>(lane_base + (unit * TC_KB_PER_STAGE + 2 * kp + 1) * BN, S1);
-                        tmem_ld_wait();
-                        if (kp == TC_KB_PER_STAGE / 2 - 1) {  // all four blocks are in registers: the unit may be refilled
-                            tc_fence_before();
-                            __syncwarp();
-                            if (lane == 0) mbar_arrive(smem_u32(&sm->tmem_empty[unit]));
-                        }
-                        const float sw0 = st.sw[2 * kp][row_in_tile], sw1 = st.sw[2 * kp + 1][row_in_tile];
-                        const float4 x0 = *reinterpret_cast<const float4*>(&st.sx[2 * kp][cg * TPT]);
-                        const float4 x1 = *reinterpret_cast<const float4*>(&st.sx[2 * kp + 1][cg * TPT]);
-                        const float xs0[4] = {x0.x, x0.y, x0.z, x0.w}, xs1[4] = {x1.x, x1.y, x1.z, x1.w};
+                            for (int i = 0; i < TPT; i++) {
+                                const float d = __fmul_rn(sw, xs[i]);
 #pragma unroll
-                        for (int i = 0; i < TPT; i++) {
-                            const float d0 = __fmul_rn(sw0, xs0[i]), d1 = __fmul_rn(sw1, xs1[i]);
-#pragma unroll
-                            for (int l = 0; l < 4; l += 2) {
-                                acc2[i][0][l >> 1] = add2(acc2[i][0][l >> 1], pack2(__fmul_rn(__int2float_rn(S0[i * 4 + l]), d0),
-                                                                                   __fmul_rn(__int2float_rn(S0[i * 4 + l + 1]), d0)));
-                                acc2[i][1][l >> 1] = add2(acc2[i][1][l >> 1], pack2(__fmul_rn(__int2float_rn(S1[i * 4 + l]), d1),
-                                                                                   __fmul_rn(__int2float_rn(S1[i * 4 + l + 1]), d1)));
+                                for (int l = 0; l < 4; l += 2)
+                                    acc2[i][kk & 1][l >> 1] = add2(acc2[i][kk & 1][l >> 1], pack2(__fmul_rn(__int2float_rn(S[i * 4 + l]), d),
+                                                                                                 __fmul_rn(__int2float_rn(S[i * 4 + l + 1]), d)));
                             }
-                        }
+                        };
+                        const uint32_t t0 = lane_base + (unit * TC_KB_PER_STAGE) * BN;
+                        tmem_ld<COLS>(t0, SA);
+                        tmem_ld_wait();
+                        tmem_ld<COLS>(t0 + BN, SB);
+                        chains(SA, 0);
+                        tmem_ld_wait();
+                        tmem_ld<COLS>(t0 + 2 * BN, SA);
+                        chains(SB, 1);
+                        tmem_ld_wait();
+                        tmem_ld<COLS>(t0 + 3 * BN, SB);
+                        chains(SA, 2);
+                        tmem_ld_wait();
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(smem_u32(&sm->tmem_empty[unit]));
+                        chains(SB, 3);
                     }
                     __syncwarp();
                     if (lane == 0) mbar_arrive(smem_u32(&sm->empty[s]));
