@@ -227,6 +227,8 @@ k_gemm_tc(const __grid_constant__ TcJob job, const __grid_constant__ CUtensorMap
     extern __shared__ uint8_t tc_smem_raw[];
     TcSmem<BN>* sm = reinterpret_cast<TcSmem<BN>*>((reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
     constexpr int NBUF = 512 / BN;
+    constexpr int UNIT = NBUF / 2 < TC_KB_PER_STAGE ? NBUF / 2 : TC_KB_PER_STAGE;  // blocks per hand-over: two units in flight
+    static_assert(TC_KB_PER_STAGE % UNIT == 0 && NBUF == 2 * UNIT, "two hand-over units that tile a stage");
     constexpr int TC_STAGES = tc_stages<BN>();
     constexpr int COLS = BN / TC_COL_GROUPS;  // columns per epilogue thread
     // EXACT: a column is (token, NEON lane group); the activation rows arrive masked to one lane group
@@ -302,19 +304,18 @@ k_gemm_tc(const __grid_constant__ TcJob job, const __grid_constant__ CUtensorMap
                     for (int kk = 0; kk < TC_KB_PER_STAGE; kk++) {
                         const uint32_t j = g * TC_KB_PER_STAGE + kk;
                         const uint32_t buf = j % NBUF;
-                        if (!EXACT || kk == 0) {
-                            // EXACT hands the buffers over a stage (4 blocks = half of tensor memory) at a time: every
-                            // hand-over costs each epilogue warp a barrier wait and an arrival, both long dependent
-                            // steps of its loop, and that loop - not the tensor pipe - sets the pace of the kernel
-                            const uint32_t bi = EXACT ? (g & 1u) : buf, ub = EXACT ? (g >> 1) : j / NBUF;
-                            ok = mbar_wait<BN, 64>(sm, smem_u32(&sm->tmem_empty[bi]), (ub & 1) ^ 1, err, 3);
+                        if (kk % UNIT == 0) {
+                            // Buffers are handed over half of tensor memory (UNIT blocks) at a time: every hand-over
+                            // costs each epilogue warp a barrier wait and an arrival, both long dependent steps of its
+                            // loop, and that loop - not the tensor pipe - sets the pace of the kernel
+                            const uint32_t un = j / UNIT;
+                            ok = mbar_wait<BN, 64>(sm, smem_u32(&sm->tmem_empty[un & 1u]), ((un >> 1) & 1) ^ 1, err, 3);
                             if (!ok) break;
                             tc_fence_after();
                         }
                         // 32 bytes further along K inside the swizzle atom: +2 in the 16-byte address field
                         umma_i8(tmem_base + buf * BN, da + (unsigned long long)(kk * 2), db + (unsigned long long)(kk * 2), idesc);
-                        if (!EXACT) umma_commit(smem_u32(&sm->tmem_full[buf]));
-                        else if (kk == TC_KB_PER_STAGE - 1) umma_commit(smem_u32(&sm->tmem_full[g & 1u]));
+                        if (kk % UNIT == UNIT - 1) umma_commit(smem_u32(&sm->tmem_full[(j / UNIT) & 1u]));
                     }
                     if (ok) umma_commit(smem_u32(&sm->empty[s]));
                 }
@@ -376,24 +377,27 @@ k_gemm_tc(const __grid_constant__ TcJob job, const __grid_constant__ CUtensorMap
                 for (int ks = 0; ks < k_stages && ok; ks++, g++) {
                     const int s = g % TC_STAGES;
                     const uint32_t u = g / TC_STAGES;
+                    // (every lane of a warp runs the same wait on the same barrier and gets the same answer)
                     ok = mbar_wait(sm, smem_u32(&sm->full[s]), u & 1, err, 5);
-                    ok = __all_sync(0xffffffffu, ok);
                     if (!ok) break;
                     const TcStage<BN>& st = sm->stage[s];
-#pragma unroll 1
+#pragma unroll(BN == 64 && !SUMS ? TC_KB_PER_STAGE : 1)
                     for (int kk = 0; kk < TC_KB_PER_STAGE; kk++) {
                         const uint32_t j = g * TC_KB_PER_STAGE + kk;
-                        const uint32_t buf = j % NBUF, ub = j / NBUF;
-                        ok = mbar_wait(sm, smem_u32(&sm->tmem_full[buf]), ub & 1, err, 6);
-                        ok = __all_sync(0xffffffffu, ok);
-                        if (!ok) break;
-                        tc_fence_after();
+                        const uint32_t buf = j % NBUF, un = j / UNIT;
+                        if (kk % UNIT == 0) {
+                            ok = mbar_wait(sm, smem_u32(&sm->tmem_full[un & 1u]), (un >> 1) & 1, err, 6);
+                            if (!ok) break;
+                            tc_fence_after();
+                        }
                         int32_t S[COLS];
                         tmem_ld<COLS>(lane_base + buf * BN, S);
                         tmem_ld_wait();
-                        tc_fence_before();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(smem_u32(&sm->tmem_empty[buf]));
+                        if (kk % UNIT == UNIT - 1) {  // the unit's blocks are all in registers or consumed
+                            tc_fence_before();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(smem_u32(&sm->tmem_empty[un & 1u]));
+                        }
                         const float sw = st.sw[kk][row_in_tile];
                         const f32x2 sw2 = pack2(sw, sw);
                         const float4* sx4 = reinterpret_cast<const float4*>(&st.sx[kk][cg * COLS]);
@@ -453,6 +457,7 @@ k_gemm_tc(const __grid_constant__ TcJob job, const __grid_constant__ CUtensorMap
                     // (every lane of a warp runs the same wait on the same barrier and gets the same answer)
                     ok = mbar_wait(sm, smem_u32(&sm->full[s]), u & 1, err, 5);  // the stage's scales
                     if (!ok) break;
+                    static_assert(UNIT == TC_KB_PER_STAGE, "the exact epilogue takes a whole stage per hand-over");
                     const uint32_t unit = g & 1u;                                // the half of tensor memory with its 4 blocks
                     ok = mbar_wait(sm, smem_u32(&sm->tmem_full[unit]), (g >> 1) & 1, err, 6);
                     if (!ok) break;
