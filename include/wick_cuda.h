@@ -213,7 +213,7 @@ int32_t wick_cuda_weight_create(int32_t dtype, const uint8_t* raw_host, uint32_t
 void wick_cuda_weight_destroy(wick_cuda_weight* w);
 
 /* quantize_f32_to_q8_0_neon over n rows of k (simd.rs:255-323; quantize_columns lfm2.rs:571-592):
- * scales [n][k/32] f32 (f16-rounded), quants [n][k] i8. */
+ * scales [n][k/32] f32 (f16-rounded), quants [n][k] i8.  x must be 16-byte aligned, quants 4-byte aligned. */
 int32_t wick_cuda_quantize_q8_0(const float* x_dev, uint32_t n, uint32_t k, float* scales_dev,
                                 int8_t* quants_dev, void* stream);
 /* gemv_q4_0_q8_0_neon / gemv_q8_0_q8_0_neon (simd.rs:328-415, :440-524): y[m]. */

@@ -129,6 +129,21 @@ __device__ __forceinline__ int8_t quantize_lane(float v, float* scale) {
     return (int8_t)__float2int_rn(__fmul_rn(v, id));
 }
 
+// The same quantiser with four consecutive elements per lane: a block is held by 8 consecutive lanes (lane & ~7 ..),
+// a warp carries four blocks.  Every lane of the warp must call it (full-mask shuffles); returns the four quants
+// packed little-endian.  One pair of IEEE divisions serves four elements instead of one.
+__device__ __forceinline__ uint32_t quantize_lane4(float4 v, float* scale) {
+    float a = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+    const float d = __fdiv_rn(a, 127.0f);
+    const float id = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+    *scale = __half2float(__float2half_rn(d));
+    const uint32_t q0 = (uint32_t)__float2int_rn(__fmul_rn(v.x, id)) & 0xFFu, q1 = (uint32_t)__float2int_rn(__fmul_rn(v.y, id)) & 0xFFu;
+    const uint32_t q2 = (uint32_t)__float2int_rn(__fmul_rn(v.z, id)) & 0xFFu, q3 = (uint32_t)__float2int_rn(__fmul_rn(v.w, id)) & 0xFFu;
+    return q0 | (q1 << 8) | (q2 << 16) | (q3 << 24);
+}
+
 // cpu_argmax ordering (wick/src/sampler.rs:8-19): total_cmp with NaN as -inf; packing the
 // index below the key makes "largest key, then largest index" a plain u64 max.
 __device__ __forceinline__ unsigned long long argmax_pack(float f, uint32_t idx) {

@@ -75,13 +75,14 @@ __global__ void __launch_bounds__(256) k_add_rmsnorm_quant(float* __restrict__ h
     __shared__ double red[32];
     const int row = blockIdx.x;
     float* h = hidden + (size_t)row * dim;
-    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
-        float v = h[i];
+    for (int i = threadIdx.x * 4; i < dim; i += blockDim.x * 4) {  // dim is a multiple of 32
+        float4 v = *reinterpret_cast<const float4*>(h + i);
         if (add) {
-            v = __fadd_rn(v, add[(size_t)row * dim + i]);  // cpu::add_inplace, cpu.rs:2230-2235
-            h[i] = v;
+            const float4 a = *reinterpret_cast<const float4*>(add + (size_t)row * dim + i);  // cpu::add_inplace, cpu.rs:2230-2235
+            v = make_float4(__fadd_rn(v.x, a.x), __fadd_rn(v.y, a.y), __fadd_rn(v.z, a.z), __fadd_rn(v.w, a.w));
+            *reinterpret_cast<float4*>(h + i) = v;
         }
-        xs[i] = v;
+        *reinterpret_cast<float4*>(xs + i) = v;
     }
     __syncthreads();
     double sum_sq = block_sum_sq_f64(xs, dim, red);
@@ -89,15 +90,26 @@ __global__ void __launch_bounds__(256) k_add_rmsnorm_quant(float* __restrict__ h
     float inv = (float)(1.0 / sqrt(mean + (double)eps));
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
     const int nb = dim / QK;
-    for (int b = warp; b < nb; b += nw) {
-        int i = b * QK + lane;
-        float v = __fmul_rn(__fmul_rn(xs[i], inv), weight[i]);
-        if (normed_out) normed_out[(size_t)row * dim + i] = v;
+    // four blocks per warp and pass: 8 lanes per block, 4 consecutive elements per lane
+    for (int b0 = warp * 4; b0 < nb; b0 += nw * 4) {
+        const int b = b0 + (lane >> 3);
+        const bool in = b < nb;
+        const int i = b * QK + (lane & 7) * 4;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (in) {
+            const float4 x = *reinterpret_cast<const float4*>(xs + i);
+            const float4 w = __ldg(reinterpret_cast<const float4*>(weight + i));
+            v = make_float4(__fmul_rn(__fmul_rn(x.x, inv), w.x), __fmul_rn(__fmul_rn(x.y, inv), w.y), __fmul_rn(__fmul_rn(x.z, inv), w.z),
+                            __fmul_rn(__fmul_rn(x.w, inv), w.w));
+            if (normed_out) *reinterpret_cast<float4*>(normed_out + (size_t)row * dim + i) = v;
+        }
         if (q8q) {
             float sc;
-            int8_t q = quantize_lane(v, &sc);
-            q8q[(size_t)row * dim + i] = q;
-            if (lane == 0) q8s[(size_t)row * nb + b] = sc;
+            const uint32_t q = quantize_lane4(v, &sc);
+            if (in) {
+                *reinterpret_cast<uint32_t*>(q8q + (size_t)row * dim + i) = q;
+                if ((lane & 7) == 0) q8s[(size_t)row * nb + b] = sc;
+            }
         }
     }
 }
@@ -125,19 +137,24 @@ void launch_rmsnorm(cudaStream_t st, float* x, const float* weight, int n, int d
 // ── plain Q8_0 quantisation of rows ────────────────────────────────────────
 __global__ void k_quant_rows(const float* __restrict__ x, size_t total_blocks, float* __restrict__ q8s,
                              int8_t* __restrict__ q8q) {
-    size_t gw = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    int lane = threadIdx.x & 31;
-    if (gw >= total_blocks) return;
+    // 8 lanes per block, 4 consecutive elements per lane; lanes past the end still take part in the shuffles
+    const size_t gt = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t b = gt >> 3;
+    const bool in = b < total_blocks;
+    const size_t i = gt * 4;
+    const float4 v = in ? *reinterpret_cast<const float4*>(x + i) : make_float4(0.f, 0.f, 0.f, 0.f);
     float sc;
-    int8_t q = quantize_lane(x[gw * QK + lane], &sc);
-    q8q[gw * QK + lane] = q;
-    if (lane == 0) q8s[gw] = sc;
+    const uint32_t q = quantize_lane4(v, &sc);
+    if (in) {
+        *reinterpret_cast<uint32_t*>(q8q + i) = q;
+        if ((threadIdx.x & 7) == 0) q8s[b] = sc;
+    }
 }
 
 void launch_quant_rows(cudaStream_t st, const float* x, int n, int k, float* q8s, int8_t* q8q) {
     size_t total = (size_t)n * (k / QK);
     if (!total) return;
-    unsigned grid = (unsigned)((total * 32 + 255) / 256);
+    unsigned grid = (unsigned)((total * 8 + 255) / 256);
     g_kernel_launches++;
     k_quant_rows<<<grid, 256, 0, st>>>(x, total, q8s, q8q);
 }
@@ -145,23 +162,29 @@ void launch_quant_rows(cudaStream_t st, const float* x, int n, int k, float* q8s
 // ── SwiGLU + quantise ──────────────────────────────────────────────────────
 __global__ void k_silu_mul_quant(const float* __restrict__ gate, const float* __restrict__ up, size_t total_blocks,
                                  float* __restrict__ q8s, int8_t* __restrict__ q8q, float* __restrict__ act_out) {
-    size_t gw = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    int lane = threadIdx.x & 31;
-    if (gw >= total_blocks) return;
-    size_t i = gw * QK + lane;
-    float a = silu_mul_elem(gate[i], up[i]);
-    if (act_out) act_out[i] = a;
+    const size_t gt = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t b = gt >> 3;
+    const bool in = b < total_blocks;
+    const size_t i = gt * 4;
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (in) {
+        const float4 g = *reinterpret_cast<const float4*>(gate + i), u = *reinterpret_cast<const float4*>(up + i);
+        a = make_float4(silu_mul_elem(g.x, u.x), silu_mul_elem(g.y, u.y), silu_mul_elem(g.z, u.z), silu_mul_elem(g.w, u.w));
+        if (act_out) *reinterpret_cast<float4*>(act_out + i) = a;
+    }
     float sc;
-    int8_t q = quantize_lane(a, &sc);
-    q8q[i] = q;
-    if (lane == 0) q8s[gw] = sc;
+    const uint32_t q = quantize_lane4(a, &sc);
+    if (in) {
+        *reinterpret_cast<uint32_t*>(q8q + i) = q;
+        if ((threadIdx.x & 7) == 0) q8s[b] = sc;
+    }
 }
 
 void launch_silu_mul_quant(cudaStream_t st, const float* gate, const float* up, int n, int dim, float* q8s, int8_t* q8q,
                            float* act_out) {
     size_t total = (size_t)n * (dim / QK);
     if (!total) return;
-    unsigned grid = (unsigned)((total * 32 + 255) / 256);
+    unsigned grid = (unsigned)((total * 8 + 255) / 256);
     g_kernel_launches++;
     k_silu_mul_quant<<<grid, 256, 0, st>>>(gate, up, total, q8s, q8q, act_out);
 }

@@ -1902,6 +1902,8 @@ void wick_cuda_weight_destroy(wick_cuda_weight* w) {
 int32_t wick_cuda_quantize_q8_0(const float* x_dev, uint32_t n, uint32_t k, float* scales_dev, int8_t* quants_dev, void* stream) {
     if (!x_dev || !scales_dev || !quants_dev) return fail(WICK_CUDA_ERR_BAD_ARG, "NULL argument");
     if (k % QK) return fail(WICK_CUDA_ERR_BAD_ARG, "quantize_q8_0: k must be divisible by 32");
+    if (((uintptr_t)x_dev & 15) || ((uintptr_t)quants_dev & 3))
+        return fail(WICK_CUDA_ERR_BAD_ARG, "quantize_q8_0: x must be 16-byte aligned and quants 4-byte aligned");
     launch_quant_rows((cudaStream_t)stream, x_dev, (int)n, (int)k, scales_dev, quants_dev);
     OP_END();
 }
