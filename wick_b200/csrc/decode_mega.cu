@@ -111,7 +111,15 @@ __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;"
 // chunks of (staging floats) / 16 rows, one memory round trip per chunk, so a larger staging area is fewer trips)
 __host__ __device__ __forceinline__ int xf_floats(const MegaParams& P) { return P.max_seq + 4 + 64 * 16 + P.xf_extra; }
 
+// Work split of one phase for one CTA (see plan_phase); computed once per launch into shared memory: it depends on
+// the phase and the CTA only, and working it out again in every phase of every token (two integer divisions per matrix,
+// a chain of dependent descriptor loads) cost each of the ~65 mat-vec phases of a token 0.2-0.3 us (2046 -> 2114 tok/s).
+struct Plan {
+    int lo, hi, rg, pad;
+};
+
 struct Smem {
+    Plan* plan;    // [n_phases]
     uint8_t* ring;
     float* xf;     // attention phase: normalised scores, then gathered V rows
     int8_t* xq;    // quantised phase input
@@ -162,6 +170,9 @@ __device__ __forceinline__ Smem carve(uint8_t* base, const MegaParams& P) {
     s.ph = (MegaPhase*)(base + o);
     o += (size_t)P.n_phases * sizeof(MegaPhase);
     s.layers = (MegaLayer*)(base + o);
+    o += (size_t)P.n_layers * sizeof(MegaLayer);
+    o = (o + 15) & ~(size_t)15;
+    s.plan = (Plan*)(base + o);
     return s;
 }
 
@@ -172,9 +183,6 @@ __device__ __forceinline__ int share(int i, int n, int d) { return (int)((unsign
 // Work split of one phase for one CTA: a contiguous run [lo, hi) of the phase's row groups
 // (all matrices of the phase concatenated), cut into stages of at most `rg` groups (one ring
 // slot each).  Stages are dealt to the consumer teams round-robin through their ring slot.
-struct Plan {
-    int lo, hi, rg;
-};
 __device__ __forceinline__ Plan plan_phase(const MegaPhase& ph, int cta, int ncta, int slot_bytes) {
     int gt = 0, gb = 1;
     for (int i = 0; i < (ph.pair ? 1 : ph.n_mat); i++) {  // a paired phase is split by the rows of ONE of its matrices
@@ -190,6 +198,7 @@ __device__ __forceinline__ Plan plan_phase(const MegaPhase& ph, int cta, int nct
     int rg = (p.hi - p.lo + NTEAMS - 1) / NTEAMS;  // spread a small phase over all teams
     rg = rg < 1 ? 1 : rg;
     p.rg = rg > cap ? cap : rg;
+    p.pad = 0;
     return p;
 }
 
@@ -204,7 +213,7 @@ __device__ unsigned long long producer(const MegaParams& P, const Smem& S, int c
         for (int pi = 0; pi < P.n_phases; pi++) {
             const MegaPhase& ph = S.ph[pi];
             if (ph.kind == MPH_ATTN || ph.kind == MPH_SCORES) continue;
-            Plan pl = plan_phase(ph, cta, ncta, P.slot_bytes);
+            const Plan pl = S.plan[pi];
             // stage list: per matrix its chunks in order; a paired phase alternates the two matrices chunk by chunk
             const int n_seq = ph.pair ? 1 : ph.n_mat, n_alt = ph.pair ? 2 : 1;
             int off = 0;
@@ -1050,7 +1059,7 @@ __device__ void consumer(const MegaParams& P, const Smem& S, int cta, int ncta) 
                 // gate / up as alternating stages: stage pair j goes to team j % NTEAMS, which keeps both
                 // slots until it has the two sums of each row and can apply SwiGLU (n_slots is a multiple of
                 // 2 * NTEAMS, so within the phase a slot always returns to the same team)
-                Plan pl = plan_phase(ph, cta, ncta, P.slot_bytes);
+                const Plan pl = S.plan[pi];
                 const DevWeight& wg = ph.mat[0].w;
                 const DevWeight& wu = ph.mat[1].w;
                 const int nb = wg.k / QK;
@@ -1105,7 +1114,7 @@ __device__ void consumer(const MegaParams& P, const Smem& S, int cta, int ncta) 
                     }
                 }
             } else if (ph.kind != MPH_ATTN && ph.kind != MPH_SCORES) {
-                Plan pl = plan_phase(ph, cta, ncta, P.slot_bytes);
+                const Plan pl = S.plan[pi];
                 int off = 0, nst = 0;
                 for (int mi = 0; mi < ph.n_mat; mi++) {
                     const MegaMat& M = ph.mat[mi];
@@ -1242,6 +1251,12 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) k_decode_mega(const MegaParam
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     __syncthreads();
+    for (int i = threadIdx.x; i < P.n_phases; i += blockDim.x) {
+        Plan pl{0, 0, 1, 0};
+        if (S.ph[i].kind != MPH_ATTN && S.ph[i].kind != MPH_SCORES) pl = plan_phase(S.ph[i], blockIdx.x, gridDim.x, P.slot_bytes);
+        S.plan[i] = pl;
+    }
+    __syncthreads();
     if (threadIdx.x < 32) {
         if (threadIdx.x == 0) {
             unsigned long long issued = producer(P, S, blockIdx.x, gridDim.x);
@@ -1273,6 +1288,8 @@ size_t mega_smem_bytes(const MegaParams& P) {
     o = (o + 15) & ~(size_t)15;
     o += 4 * 256 * 4 + 16;
     o += (size_t)P.n_phases * sizeof(MegaPhase) + (size_t)P.n_layers * sizeof(MegaLayer);
+    o = (o + 15) & ~(size_t)15;
+    o += (size_t)P.n_phases * sizeof(Plan);
     return o;
 }
 
