@@ -1032,8 +1032,13 @@ __device__ void consumer(const MegaParams& P, const Smem& S, int cta, int ncta) 
         for (int pi = 0; pi < P.n_phases; pi++) {
             const MegaPhase& ph = S.ph[pi];
             const uint32_t id_out = phase_id(P, t, pi);
+            // the descriptor fields the phase branches on, and its work split, are fetched here, ahead of the dependency
+            // wait (as register copies: through the reference every use after a barrier is another shared-memory load,
+            // and those loads sat between the prologue and the first stage)
+            const int kind = ph.kind, pair = ph.pair, n_mat = ph.n_mat, flag_out = ph.flag_out;
+            const Plan pl = S.plan[pi];
             float nw[MAXJ];
-            if (ph.kind == MPH_NORM) load_norm_w(c, ph, nw);
+            if (kind == MPH_NORM) load_norm_w(c, ph, nw);
             if ((t > 0 || pi > 0) && !ph.flag_in) grid_wait(c, (P.bar_base + (unsigned long long)t * P.n_phases + pi) * (unsigned long long)ncta);
             const bool prof = P.prof && cta == 0 && c.ct == 0 && t == P.n_tokens - 1;
             c.stamp = (prof && pi == P.prof_phase) ? P.prof + (size_t)P.n_phases * 4 : nullptr;
@@ -1044,7 +1049,7 @@ __device__ void consumer(const MegaParams& P, const Smem& S, int cta, int ncta) 
                 if (cta == 0 && c.ct == 0) P.ring[(step0 + t - 1) % (uint32_t)P.ring_len] = token;
             }
             if (pi == 1 && cta == 0 && c.ct == 0) P.argmax_acc[(t + 1) & 1] = 0;  // free for the next step
-            switch (ph.kind) {
+            switch (kind) {
                 case MPH_NORM: prologue_norm(c, ph, token, nw, phase_id(P, t, pi - 1)); break;
                 case MPH_CONV: prologue_conv(c, ph); break;
                 case MPH_SILU: prologue_silu(c, ph); break;
@@ -1055,11 +1060,10 @@ __device__ void consumer(const MegaParams& P, const Smem& S, int cta, int ncta) 
                 default: phase_attention<LONG>(c, ph, pos); break;
             }
             if (prof) P.prof[pi * 4 + 1] = globaltimer_ns();
-            if (ph.kind != MPH_ATTN && ph.kind != MPH_SCORES && ph.pair) {
+            if (kind != MPH_ATTN && kind != MPH_SCORES && pair) {
                 // gate / up as alternating stages: stage pair j goes to team j % NTEAMS, which keeps both
                 // slots until it has the two sums of each row and can apply SwiGLU (n_slots is a multiple of
                 // 2 * NTEAMS, so within the phase a slot always returns to the same team)
-                const Plan pl = S.plan[pi];
                 const DevWeight& wg = ph.mat[0].w;
                 const DevWeight& wu = ph.mat[1].w;
                 const int nb = wg.k / QK;
@@ -1113,10 +1117,9 @@ __device__ void consumer(const MegaParams& P, const Smem& S, int cta, int ncta) 
                         mbar_arrive(&S.empty[slot_b]);
                     }
                 }
-            } else if (ph.kind != MPH_ATTN && ph.kind != MPH_SCORES) {
-                const Plan pl = S.plan[pi];
+            } else if (kind != MPH_ATTN && kind != MPH_SCORES) {
                 int off = 0, nst = 0;
-                for (int mi = 0; mi < ph.n_mat; mi++) {
+                for (int mi = 0; mi < n_mat; mi++) {
                     const MegaMat& M = ph.mat[mi];
                     const DevWeight& w = M.w;
                     const int gm = w.groups(), nb = w.k / QK;
@@ -1165,7 +1168,7 @@ __device__ void consumer(const MegaParams& P, const Smem& S, int cta, int ncta) 
                                 if (M.epi == MEP_ADD) {
                                     const float hv = __fadd_rn(gi == tw ? resid[0] : resid[1], acc);
                                     M.y[row] = hv;
-                                    if (ph.flag_out) st_relaxed_u64(P.hidden_flagged + row, (unsigned long long)id_out << 32 | __float_as_uint(hv));
+                                    if (flag_out) st_relaxed_u64(P.hidden_flagged + row, (unsigned long long)id_out << 32 | __float_as_uint(hv));
                                 } else if (M.epi == MEP_STORE) {
                                     M.y[row] = acc;
                                 } else {
@@ -1202,7 +1205,7 @@ __device__ void consumer(const MegaParams& P, const Smem& S, int cta, int ncta) 
                 }
             }
             if (prof) P.prof[pi * 4 + 2] = globaltimer_ns();
-            if (ph.flag_out) {
+            if (flag_out) {
                 owed++;
             } else {
                 grid_arrive(c, 1 + owed);
