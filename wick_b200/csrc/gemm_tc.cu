@@ -43,7 +43,7 @@ constexpr int TC_KB_PER_STAGE = TC_KSTAGE / QK;  // 4 quantisation blocks per st
 // only refilled after the epilogue has finished with its scales, and the refill has to be back from L2 before
 // the MMA issuer needs it; with four stages that left about one microsecond, less than a loaded L2 round trip.
 template <int BN>
-__host__ __device__ constexpr int tc_stages() { return BN == 64 ? 8 : 6; }
+__host__ __device__ constexpr int tc_stages() { return BN <= 64 ? 8 : 6; }
 constexpr int TC_COL_GROUPS = 4;    // epilogue warps per TMEM lane quarter; each takes BN/4 columns
 constexpr int TC_EPI_WARPS = 4 * TC_COL_GROUPS;
 constexpr int TC_THREADS = 32 * (4 + TC_EPI_WARPS);
@@ -166,10 +166,19 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, int32_t* r) {
         : "r"(taddr)
         : "memory");
 }
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, int32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x8.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+        : "r"(taddr)
+        : "memory");
+}
 template <int COLS>
 __device__ __forceinline__ void tmem_ld(uint32_t taddr, int32_t* r) {
-    static_assert(COLS == 16 || COLS == 32, "one tcgen05.ld per k-block");
-    if constexpr (COLS == 16) tmem_ld16(taddr, r);
+    static_assert(COLS == 8 || COLS == 16 || COLS == 32, "one tcgen05.ld per k-block");
+    if constexpr (COLS == 8) tmem_ld8(taddr, r);
+    else if constexpr (COLS == 16) tmem_ld16(taddr, r);
     else tmem_ld32(taddr, r);
 }
 // Two f32 lanes per instruction (sm_100 packed f32x2 arithmetic), used by the fused-chain epilogue,
@@ -228,14 +237,15 @@ k_gemm_tc(const __grid_constant__ TcJob job, const __grid_constant__ CUtensorMap
     TcSmem<BN>* sm = reinterpret_cast<TcSmem<BN>*>((reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
     constexpr int NBUF = 512 / BN;
     constexpr int UNIT = NBUF / 2 < TC_KB_PER_STAGE ? NBUF / 2 : TC_KB_PER_STAGE;  // blocks per hand-over: two units in flight
-    static_assert(TC_KB_PER_STAGE % UNIT == 0 && NBUF == 2 * UNIT, "two hand-over units that tile a stage");
+    constexpr int NB2 = 2 * UNIT;  // buffers in use (32-column tiles leave half of tensor memory unused)
+    static_assert(TC_KB_PER_STAGE % UNIT == 0 && NBUF >= NB2, "two hand-over units that tile a stage");
     constexpr int TC_STAGES = tc_stages<BN>();
     constexpr int COLS = BN / TC_COL_GROUPS;  // columns per epilogue thread
     // EXACT: a column is (token, NEON lane group); the activation rows arrive masked to one lane group
     // each (tc_mask_expand), so a tile covers BN/4 tokens and the MMA yields the four lane partials
     constexpr int TOK = EXACT ? BN / 4 : BN;  // tokens per tile
     constexpr int XROWS = EXACT ? 4 : 1;      // rows of the activation operand per token
-    static_assert(!EXACT || (COLS == 16 && !SUMS), "exact epilogue: 4 tokens x 4 lane groups per thread");
+    static_assert(!EXACT || ((COLS == 16 || COLS == 8) && !SUMS), "exact epilogue: 4 (or 2) tokens x 4 lane groups per thread");
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nb = k / QK;
     const int k_stages = k / TC_KSTAGE;
@@ -303,7 +313,7 @@ k_gemm_tc(const __grid_constant__ TcJob job, const __grid_constant__ CUtensorMap
 #pragma unroll
                     for (int kk = 0; kk < TC_KB_PER_STAGE; kk++) {
                         const uint32_t j = g * TC_KB_PER_STAGE + kk;
-                        const uint32_t buf = j % NBUF;
+                        const uint32_t buf = j % NB2;
                         if (kk % UNIT == 0) {
                             // Buffers are handed over half of tensor memory (UNIT blocks) at a time: every hand-over
                             // costs each epilogue warp a barrier wait and an arrival, both long dependent steps of its
@@ -384,7 +394,7 @@ k_gemm_tc(const __grid_constant__ TcJob job, const __grid_constant__ CUtensorMap
 #pragma unroll(BN == 64 && !SUMS ? TC_KB_PER_STAGE : 1)
                     for (int kk = 0; kk < TC_KB_PER_STAGE; kk++) {
                         const uint32_t j = g * TC_KB_PER_STAGE + kk;
-                        const uint32_t buf = j % NBUF, un = j / UNIT;
+                        const uint32_t buf = j % NB2, un = j / UNIT;
                         if (kk % UNIT == 0) {
                             ok = mbar_wait(sm, smem_u32(&sm->tmem_full[un & 1u]), (un >> 1) & 1, err, 6);
                             if (!ok) break;
@@ -468,8 +478,14 @@ k_gemm_tc(const __grid_constant__ TcJob job, const __grid_constant__ CUtensorMap
                         int32_t SA[COLS], SB[COLS];
                         auto chains = [&](const int32_t (&S)[COLS], const int kk) {
                             const float sw = st.sw[kk][row_in_tile];
-                            const float4 x = *reinterpret_cast<const float4*>(&st.sx[kk][cg * TPT]);
-                            const float xs[4] = {x.x, x.y, x.z, x.w};
+                            float xs[TPT];
+                            if constexpr (TPT == 4) {
+                                const float4 x = *reinterpret_cast<const float4*>(&st.sx[kk][cg * TPT]);
+                                xs[0] = x.x, xs[1] = x.y, xs[2] = x.z, xs[3] = x.w;
+                            } else {
+                                const float2 x = *reinterpret_cast<const float2*>(&st.sx[kk][cg * TPT]);
+                                xs[0] = x.x, xs[1] = x.y;
+                            }
 #pragma unroll
                             for (int i = 0; i < TPT; i++) {
                                 const float d = __fmul_rn(sw, xs[i]);
@@ -721,10 +737,19 @@ void launch_tc_mask_expand(cudaStream_t st, const int8_t* xq, int n, int k, int8
 }
 
 cudaError_t launch_gemm_tc_exact(cudaStream_t st, const TcWeight* const* w, float* const* out, int count, const CUtensorMap& map_xm,
-                                 const float* x_scales, int n, uint32_t* err) {
+                                 const float* x_scales, int n, uint32_t* err, const CUtensorMap* map_xm_narrow) {
     if (n <= 0 || count <= 0) return cudaSuccess;
     if (count > 3) return cudaErrorInvalidValue;
     TcJob job;
+    // 8-token tiles while twice the 16-token tiles still fit one wave (few rows and a narrow matrix: the multi-sequence
+    // decode step): a tile's time is set by its K loop, so more, smaller tiles only pay when they run side by side
+    int row_tiles = 0;
+    for (int i = 0; i < count; i++) row_tiles += w[i]->m_pad / TC_BM;
+    if (map_xm_narrow && 2 * row_tiles * ((n + TC_EXACT_TOKENS - 1) / TC_EXACT_TOKENS) <= 148) {
+        cudaError_t e = fill_job(job, w, out, count, (n + TC_EXACT_TOKENS / 2 - 1) / (TC_EXACT_TOKENS / 2));
+        if (e != cudaSuccess) return e;
+        return launch_tc<2 * TC_EXACT_TOKENS, true>(st, job, *map_xm_narrow, x_scales, n, w[0]->k, nullptr, err);
+    }
     cudaError_t e = fill_job(job, w, out, count, (n + TC_EXACT_TOKENS - 1) / TC_EXACT_TOKENS);
     if (e != cudaSuccess) return e;
     return launch_tc<4 * TC_EXACT_TOKENS, true>(st, job, map_xm, x_scales, n, w[0]->k, nullptr, err);

@@ -55,8 +55,9 @@ cudaError_t launch_gemm_tc(cudaStream_t st, const TcWeight* const* w, float* con
 // as four columns; the epilogue keeps the reference's eight unfused chains per output.
 constexpr int TC_EXACT_TOKENS = 16;  // tokens per tile (64 MMA columns)
 void launch_tc_mask_expand(cudaStream_t st, const int8_t* xq, int n, int k, int8_t* xm);
-// map_xm: tc_make_activation_map(xm, 4 * rows_cap, k, 64, ..).
+// map_xm: tc_make_activation_map(xm, 4 * rows_cap, k, 64, ..); map_xm_narrow (optional): the same with 32 rows per box,
+// for the 8-token tiles small batches run with.
 cudaError_t launch_gemm_tc_exact(cudaStream_t st, const TcWeight* const* w, float* const* out, int count, const CUtensorMap& map_xm,
-                                 const float* x_scales, int n, uint32_t* err);
+                                 const float* x_scales, int n, uint32_t* err, const CUtensorMap* map_xm_narrow = nullptr);
 
 }  // namespace wick

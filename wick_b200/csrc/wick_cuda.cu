@@ -84,7 +84,7 @@ struct wick_cuda_model {
     int prefill_mode = WICK_CUDA_PREFILL_EXACT;
     CUtensorMap map_x_hs[2], map_x_is[2];  // activations [max_chunk][hs | is], box of 64 / 128 rows
     int8_t* q8m = nullptr;                  // lane-group-masked activations [4 * max_chunk][hs | is] (exact tensor-core GEMM)
-    CUtensorMap map_xm_hs, map_xm_is;
+    CUtensorMap map_xm_hs, map_xm_is, map_xm_hs32, map_xm_is32;  // boxes of 64 rows (16 tokens) and of 32 rows (8 tokens)
     float* normed_last = nullptr;  // output-normed hidden row of the last prefilled token
     float* rope_delta = nullptr;   // [head_dim]: cos then sin of the n_keep shift rotation
     uint32_t* tc_err = nullptr;
@@ -690,7 +690,8 @@ void run_gemms(wick_cuda_model* m, int n, std::initializer_list<GemmTarget> list
         cudaError_t e;
         if (tc_exact) {
             launch_tc_mask_expand(st, m->q8q, n, tw[0]->k, m->q8m);
-            e = launch_gemm_tc_exact(st, tw, outs, c, is_hs ? m->map_xm_hs : m->map_xm_is, m->q8s, n, m->tc_err);
+            e = launch_gemm_tc_exact(st, tw, outs, c, is_hs ? m->map_xm_hs : m->map_xm_is, m->q8s, n, m->tc_err,
+                                     is_hs ? &m->map_xm_hs32 : &m->map_xm_is32);
         } else {
             e = launch_gemm_tc(st, tw, outs, c, is_hs ? m->map_x_hs : m->map_x_is, m->q8s, n, nullptr, m->tc_err);
         }
@@ -811,6 +812,8 @@ int32_t ensure_tc(wick_cuda_model* m) {
     W_TRY(dev_alloc(m, &m->q8m, (size_t)4 * m->max_chunk * std::max(hs, is)));
     CU_TRY(tc_make_activation_map(m->q8m, 4 * m->max_chunk, hs, 64, &m->map_xm_hs));
     CU_TRY(tc_make_activation_map(m->q8m, 4 * m->max_chunk, is, 64, &m->map_xm_is));
+    CU_TRY(tc_make_activation_map(m->q8m, 4 * m->max_chunk, hs, 32, &m->map_xm_hs32));
+    CU_TRY(tc_make_activation_map(m->q8m, 4 * m->max_chunk, is, 32, &m->map_xm_is32));
     CU_TRY(cudaStreamSynchronize(m->stream));
     m->tc_built = true;
     return WICK_CUDA_OK;
@@ -1980,9 +1983,11 @@ int32_t wick_cuda_gemm_q8_tc_exact(wick_cuda_weight* w, const float* bs_dev, con
     launch_tc_mask_expand(st, bq_dev, (int)n, w->w.k, xm);
     CUtensorMap map_xm;
     CU_TRY(tc_make_activation_map(xm, 4 * (int)n, w->w.k, 64, &map_xm));
+    CUtensorMap map_xm32;
+    CU_TRY(tc_make_activation_map(xm, 4 * (int)n, w->w.k, 32, &map_xm32));
     const TcWeight* tw[1] = {&w->tc};
     float* outs[1] = {out_dev};
-    CU_TRY(launch_gemm_tc_exact(st, tw, outs, 1, map_xm, bs_dev, (int)n, w->tc_err));
+    CU_TRY(launch_gemm_tc_exact(st, tw, outs, 1, map_xm, bs_dev, (int)n, w->tc_err, &map_xm32));
     uint32_t code = 0;
     CU_TRY(cudaMemcpyAsync(&code, w->tc_err, 4, cudaMemcpyDeviceToHost, st));
     CU_TRY(cudaStreamSynchronize(st));
