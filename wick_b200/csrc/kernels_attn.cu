@@ -213,7 +213,7 @@ __device__ __forceinline__ bool fa_wait(uint64_t* bar, uint32_t parity, volatile
 template <int HD, int BQ, int MAXW>  // MAXW: the most consumer warps a launch of this instance has (4 or 8)
 __global__ void __launch_bounds__((MAXW + 1) * 32, MAXW == 4 ? (HD <= 64 ? WICK_FA_MIN_CTAS : 2) : 1) k_attention_flash(const float* __restrict__ q, const float* __restrict__ k_cache,
                                                           const float* __restrict__ v_cache, float* __restrict__ out, int n, int start_pos,
-                                                          int n_heads, int n_kv_heads, int qb, uint32_t* __restrict__ err) {
+                                                          int n_heads, int n_kv_heads, int qb, int wave_size, uint32_t* __restrict__ err) {
     constexpr int ROW = HD + 4;          // padded row, floats
     constexpr int DPL = HD / 4;          // output dims per lane
     extern __shared__ __align__(128) uint8_t fa_smem[];
@@ -226,10 +226,24 @@ __global__ void __launch_bounds__((MAXW + 1) * 32, MAXW == 4 ? (HD <= 64 ? WICK_
 
     const int group = n_heads / n_kv_heads;
     const int n_cw = group * (qb / (8 * BQ));  // consumer warps (<= MAXW)
-    const int kvh = blockIdx.x;
+    // Which (KV head, query block) this CTA takes.  All CTAs of a launch are resident together, 3 or 4 to an SM, and a
+    // CTA's work grows with its query block (causal), so the launch ends when the SM with the heaviest set ends.  The
+    // items are ranked by descending work and dealt to the block indices in waves of one block per SM, forwards in
+    // even waves and backwards in odd ones: with the usual placement (blocks b, b + #SMs, b + 2 #SMs, ... on one SM)
+    // every SM then holds about the same work.  Any placement is correct; only the balance depends on it.
+    const int n_qblocks = (n + qb - 1) / qb;
+    int kvh, qblock;
+    {
+        const int b = blockIdx.x, total = gridDim.x;
+        const int wave = b / wave_size, pos = b % wave_size;
+        const int lo = wave * wave_size, hi = min(lo + wave_size, total);
+        const int r = (wave & 1) ? hi - 1 - pos : lo + pos;
+        qblock = n_qblocks - 1 - r / n_kv_heads;
+        kvh = r % n_kv_heads;
+    }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int hs = n_heads * HD, kv_dim = n_kv_heads * HD;
-    const int j_first = blockIdx.y * qb;
+    const int j_first = qblock * qb;
     const int j_last = min(n, j_first + qb) - 1;
     const int cta_max = start_pos + j_last + 1;  // keys this CTA needs
     const int n_tiles = (cta_max + FLASH_TILE - 1) / FLASH_TILE;
@@ -492,11 +506,14 @@ static cudaError_t launch_flash_hd(cudaStream_t st, const float* q, const float*
         cudaFuncSetAttribute(k_attention_flash<HD, BQ, 8>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         carved[dev] = true;
     }
-    dim3 grid(n_kv_heads, (n + qb - 1) / qb);
+    static int sm_count[64] = {};
+    if (dev >= 0 && dev < 64 && sm_count[dev] == 0) cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
+    const int wave = (dev >= 0 && dev < 64 && sm_count[dev] > 0) ? sm_count[dev] : 148;
+    const unsigned grid = (unsigned)(n_kv_heads * ((n + qb - 1) / qb));
     const int threads = (n_cw + 1) * 32;
     g_kernel_launches++;
-    if (n_cw <= 4) k_attention_flash<HD, BQ, 4><<<grid, threads, smem, st>>>(q, k_cache, v_cache, out, n, start_pos, n_heads, n_kv_heads, qb, err);
-    else k_attention_flash<HD, BQ, 8><<<grid, threads, smem, st>>>(q, k_cache, v_cache, out, n, start_pos, n_heads, n_kv_heads, qb, err);
+    if (n_cw <= 4) k_attention_flash<HD, BQ, 4><<<grid, threads, smem, st>>>(q, k_cache, v_cache, out, n, start_pos, n_heads, n_kv_heads, qb, wave, err);
+    else k_attention_flash<HD, BQ, 8><<<grid, threads, smem, st>>>(q, k_cache, v_cache, out, n, start_pos, n_heads, n_kv_heads, qb, wave, err);
     return cudaSuccess;
 }
 
