@@ -990,13 +990,8 @@ __device__ __forceinline__ void stage_products(uint32_t* __restrict__ qs, const 
     }
 }
 
-template <int DT>
-__device__ __forceinline__ float group_chain_sum(const uint32_t* __restrict__ qs, int nb, int lane) {
-    const int p = lane >> 4;
-    const uint32_t* pp = DT == DT_Q4_0 ? qs + (lane & 15) : qs + lane;
-    constexpr int U = 8;
-    float acc = 0.0f;
-    int b = p;
+template <int DT, int U>
+__device__ __forceinline__ void chain_batches(const uint32_t* __restrict__ pp, int nb, int& b, float& acc) {
     for (; b + 2 * (U - 1) < nb; b += 2 * U) {
         float t[U];
 #pragma unroll
@@ -1004,6 +999,19 @@ __device__ __forceinline__ float group_chain_sum(const uint32_t* __restrict__ qs
 #pragma unroll
         for (int u = 0; u < U; u++) acc = __fadd_rn(acc, t[u]);
     }
+}
+
+// The chain of one (row, parity, lane group): its products in block order.  The additions are serial by contract; the
+// operand loads are not, so they are issued 32 at a time (then 8 at a time for what is left) ahead of the additions:
+// with 8 at a time the 32 terms of a 2048-long row took ~620 cycles, most of it shared-memory latency between batches.
+template <int DT>
+__device__ __forceinline__ float group_chain_sum(const uint32_t* __restrict__ qs, int nb, int lane) {
+    const int p = lane >> 4;
+    const uint32_t* pp = DT == DT_Q4_0 ? qs + (lane & 15) : qs + lane;
+    float acc = 0.0f;
+    int b = p;
+    chain_batches<DT, 32>(pp, nb, b, acc);
+    chain_batches<DT, 8>(pp, nb, b, acc);
     for (; b < nb; b += 2) acc = __fadd_rn(acc, __uint_as_float(DT == DT_Q4_0 ? pp[b * 16] : pp[(b >> 1) * 64]));
     return acc;
 }
