@@ -1092,7 +1092,7 @@ __device__ void consumer(const MegaParams& P, const Smem& S, int cta, int ncta) 
                     uint8_t* bases[2] = {S.ring + (size_t)slot_a * P.slot_bytes, S.ring + (size_t)slot_b * P.slot_bytes};
                     for (int half = 0; half < 2; half++) {
                         unsigned spins = 0;
-                        while (!*S.abort && !mbar_try_wait_for(&S.full[half ? slot_b : slot_a], half ? par_b : par_a, WAIT_NS)) {
+                        while (!mbar_try_wait_for(&S.full[half ? slot_b : slot_a], half ? par_b : par_a, WAIT_NS) && !*S.abort) {
                             if (++spins > SPIN_LIMIT) {
                                 atomicOr(&P.ctl->error, 4u);
                                 *S.abort = 1;
@@ -1133,6 +1133,8 @@ __device__ void consumer(const MegaParams& P, const Smem& S, int cta, int ncta) 
                     const int gm = w.groups(), nb = w.k / QK;
                     int a = (pl.lo > off ? pl.lo : off) - off, b = (pl.hi < off + gm ? pl.hi : off + gm) - off;
                     const uint32_t qgb = (uint32_t)w.q_group_bytes();
+                    const int epi = M.epi, wm = w.m;  // (register copies: read again after every barrier otherwise)
+                    float* const y = M.y;
                     for (int g0 = a; g0 < b; g0 += pl.rg, slot = slot + 1 == P.n_slots ? 0 : slot + 1, par ^= (slot == 0)) {
                         // a slot always belongs to the same team (n_slots is a multiple of NTEAMS), so a team
                         // never waits two uses of a slot ahead and mbarrier parity cannot alias
@@ -1140,7 +1142,7 @@ __device__ void consumer(const MegaParams& P, const Smem& S, int cta, int ncta) 
                         int ng = pl.rg < b - g0 ? pl.rg : b - g0;
                         if (c.stamp && nst < 4) c.stamp[nst * 4 + 0] = globaltimer_ns();
                         unsigned spins = 0;
-                        while (!*S.abort && !mbar_try_wait_for(&S.full[slot], par, WAIT_NS)) {
+                        while (!mbar_try_wait_for(&S.full[slot], par, WAIT_NS) && !*S.abort) {
                             if (++spins > SPIN_LIMIT) {
                                 atomicOr(&P.ctl->error, 4u);
                                 *S.abort = 1;
@@ -1158,11 +1160,11 @@ __device__ void consumer(const MegaParams& P, const Smem& S, int cta, int ncta) 
                         // residual-add epilogue: the old value of the row is fetched now, so that its latency runs
                         // under the chain step instead of after it (a warp owns at most two groups of a slot)
                         float resid[2] = {0.0f, 0.0f};
-                        if (M.epi == MEP_ADD && (c.lane & 19) == 0) {
+                        if (epi == MEP_ADD && (c.lane & 19) == 0) {
 #pragma unroll
                             for (int q = 0; q < 2; q++) {
                                 const int gi = tw + q * TEAM_WARPS, row = (g0 + gi) * 4 + ((c.lane >> 2) & 3);
-                                if (gi < ng && row < w.m) resid[q] = __ldcg(M.y + row);
+                                if (gi < ng && row < wm) resid[q] = __ldcg(y + row);
                             }
                         }
                         team_sync(team);
@@ -1172,15 +1174,15 @@ __device__ void consumer(const MegaParams& P, const Smem& S, int cta, int ncta) 
                             float acc = is_q4<DTK>(w.dtype) ? group_chain_sum<DT_Q4_0>(qs, nb, c.lane) : group_chain_sum<DT_Q8_0>(qs, nb, c.lane);
                             acc = reduce_row8(acc);
                             const int row = (g0 + gi) * 4 + ((c.lane >> 2) & 3);
-                            if ((c.lane & 19) == 0 && row < w.m) {
-                                if (M.epi == MEP_ADD) {
+                            if ((c.lane & 19) == 0 && row < wm) {
+                                if (epi == MEP_ADD) {
                                     const float hv = __fadd_rn(gi == tw ? resid[0] : resid[1], acc);
-                                    M.y[row] = hv;
+                                    y[row] = hv;
                                     if (flag_out) st_relaxed_u64(P.hidden_flagged + row, (unsigned long long)id_out << 32 | __float_as_uint(hv));
-                                } else if (M.epi == MEP_STORE) {
-                                    M.y[row] = acc;
+                                } else if (epi == MEP_STORE) {
+                                    y[row] = acc;
                                 } else {
-                                    if (!P.greedy) M.y[row] = acc;
+                                    if (!P.greedy) y[row] = acc;
                                     unsigned long long pk = argmax_pack(acc, (uint32_t)row);
                                     best = pk > best ? pk : best;
                                 }
